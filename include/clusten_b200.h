@@ -1,0 +1,148 @@
+/*
+ * clusten_b200.h -- C ABI of libclusten_b200.so
+ *
+ * B200 (sm_100a) implementation of AutoFocusFormer's CLUSTEN neighbourhood
+ * operators.  Every entry point takes plain device pointers and sizes, is
+ * asynchronous on the given CUDA stream, allocates nothing and returns a
+ * status code (0 = CLUSTEN_OK, negative = error, see clusten_status_string).
+ *
+ * Each function names the interface of apple/ml-autofocusformer that it
+ * replaces (path inside that project : line).
+ *
+ * Tensor layouts are the reference's, contiguous, last dimension fastest:
+ *   query/key/value/d_query/d_key/d_value/feat_out(AV)   [b, h, n, c]
+ *   attn / d_attn                                       [b, h, n, m]
+ *   nbhd_idx (QK, AV)                                   [b, n, m]    int64, values in [0, n)
+ *   weights / d_weights (WF)                            [b, n_, m, ic]
+ *   feat / d_feat (WF)                                  [b, n, c]
+ *   nbhd_idx (WF)                                       [b, n_, m]   int64, values in [0, n)
+ *   feat_new / d_feat_new (WF)                          [b, n_, ic, c]
+ * An index outside [0, n) is never dereferenced: the neighbour contributes
+ * zero (forward, gather-side gradients) and receives nothing (scatter-side
+ * gradients).  The reference does not check (clusten/src/clustenqk_cuda_kernel.cu:38).
+ *
+ * dtype selects the element type of every floating tensor of a call; sums
+ * are accumulated in fp32 (fp64 for CLUSTEN_F64) whatever the element type.
+ */
+#ifndef CLUSTEN_B200_H_
+#define CLUSTEN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define CLUSTEN_API __attribute__((visibility("default")))
+#else
+#define CLUSTEN_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types: the reference dispatches fp64/fp32/fp16
+ * (AT_DISPATCH_FLOATING_TYPES_AND_HALF, clusten/src/clustenqk_cuda_kernel.cu:78);
+ * bf16 is an addition. */
+enum {
+    CLUSTEN_F32 = 0,
+    CLUSTEN_F16 = 1,
+    CLUSTEN_BF16 = 2,
+    CLUSTEN_F64 = 3
+};
+
+enum {
+    CLUSTEN_OK = 0,
+    CLUSTEN_ERR_DTYPE = -1,       /* dtype is not one of the enum above */
+    CLUSTEN_ERR_SHAPE = -2,       /* a size is <= 0 or a product overflows int32 */
+    CLUSTEN_ERR_NULL = -3,        /* a required pointer is NULL */
+    CLUSTEN_ERR_ALIGN = -4,       /* a pointer is not aligned to its element size */
+    CLUSTEN_ERR_WORKSPACE = -5,   /* inverse-index buffer too small or not built for these sizes */
+    CLUSTEN_ERR_UNSUPPORTED = -6, /* size outside what the kernels handle (see the function) */
+    CLUSTEN_ERR_CUDA = -7         /* the CUDA runtime reported an error at launch */
+};
+
+/* Human-readable name of a status code; never NULL. */
+CLUSTEN_API const char* clusten_status_string(int status);
+
+/* Library version as major*10000 + minor*100 + patch. */
+CLUSTEN_API int clusten_version(void);
+
+/* Number of kernels this library has launched in this process (all threads). */
+CLUSTEN_API unsigned long long clusten_launch_count(void);
+
+/* ------------------------------------------------------------------------
+ * Inverse neighbour index.
+ *
+ * The scatter-side gradients (d_key, d_value, d_feat) are computed as a
+ * segmented reduction over, for every target token t, the list of
+ * (row, slot) pairs with nbhd_idx[b, row, slot] == t.  This replaces the
+ * reference's atomicAdd scatter (clusten/src/clustenqk_cuda_kernel.cu:125,
+ * clustenav_cuda_kernel.cu:121, clustenwf_cuda_kernel.cu:129) and makes the
+ * gradients bit-reproducible.  One inverse serves every backward call that
+ * uses the same nbhd_idx tensor.
+ *
+ *   n_rows    rows of nbhd_idx per batch element (n for QK/AV, n_ for WF)
+ *   n_targets number of tokens the indices point into (n)
+ * Limits: m <= 2048, n_targets <= 18000 (per-batch counters live in shared
+ * memory), n_rows * m < 2^31; otherwise CLUSTEN_ERR_UNSUPPORTED.
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API size_t clusten_inverse_bytes(int b, int n_rows, int m, int n_targets);
+
+CLUSTEN_API int clusten_inverse_build(const int64_t* nbhd_idx, int b, int n_rows, int m, int n_targets,
+                          void* inverse, size_t inverse_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
+ * QK: attn[b,h,i,j] = sum_c query[b,h,i,c] * key[b,h,nbhd_idx[b,i,j],c]
+ * replaces clusten_qk_forward (clusten/src/clustenqk_cuda.cpp:25-33, kernel
+ * clustenqk_cuda_kernel.cu:18-49).  key is [b,h,n,c]; the reference's
+ * pre-transposed [b,h,c,n] copy (clusten/clusten.py:30) is not needed.
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API int clusten_qk_forward(const void* query, const void* key, const int64_t* nbhd_idx, void* attn,
+                       int b, int h, int n, int m, int c, int dtype, void* stream);
+
+/* d_query[b,h,i,c] = sum_j key[b,h,idx,c] * d_attn[b,h,i,j]
+ * d_key[b,h,t,c]   = sum_{(i,j): idx[b,i,j]==t} query[b,h,i,c] * d_attn[b,h,i,j]
+ * replaces clusten_qk_backward (clustenqk_cuda.cpp:35-45, kernel :91-132).
+ * inverse: built by clusten_inverse_build(nbhd_idx, b, n, m, n, ...). */
+CLUSTEN_API int clusten_qk_backward(const void* d_attn, const void* query, const void* key,
+                        const int64_t* nbhd_idx, const void* inverse,
+                        void* d_query, void* d_key,
+                        int b, int h, int n, int m, int c, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * AV: feat[b,h,i,c] = sum_j attn[b,h,i,j] * value[b,h,nbhd_idx[b,i,j],c]
+ * replaces clusten_av_forward (clusten/src/clustenav_cuda.cpp:25-33, kernel
+ * clustenav_cuda_kernel.cu:18-50).
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API int clusten_av_forward(const void* attn, const void* value, const int64_t* nbhd_idx, void* feat,
+                       int b, int h, int n, int m, int c, int dtype, void* stream);
+
+/* d_attn[b,h,i,j] = sum_c value[b,h,idx,c] * d_feat[b,h,i,c]
+ * d_value[b,h,t,c] = sum_{(i,j): idx[b,i,j]==t} attn[b,h,i,j] * d_feat[b,h,i,c]
+ * replaces clusten_av_backward (clustenav_cuda.cpp:35-45, kernels :93-160). */
+CLUSTEN_API int clusten_av_backward(const void* d_feat, const void* attn, const void* value,
+                        const int64_t* nbhd_idx, const void* inverse,
+                        void* d_attn, void* d_value,
+                        int b, int h, int n, int m, int c, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * WF: feat_new[b,i,ic,c] = sum_j weights[b,i,j,ic] * feat[b,nbhd_idx[b,i,j],c]
+ * replaces clusten_wf_forward (clusten/src/clustenwf_cuda.cpp:25-33, kernel
+ * clustenwf_cuda_kernel.cu:18-53).  n_out = n_ (rows of weights / nbhd_idx).
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx, void* feat_new,
+                       int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream);
+
+/* d_weights[b,i,j,ic] = sum_c feat[b,idx,c] * d_feat_new[b,i,ic,c]
+ * d_feat[b,t,c] = sum_{(i,j): idx[b,i,j]==t} sum_ic d_feat_new[b,i,ic,c] * weights[b,i,j,ic]
+ * replaces clusten_wf_backward (clustenwf_cuda.cpp:35-45, kernels :96-169).
+ * inverse: built by clusten_inverse_build(nbhd_idx, b, n_out, m, n, ...). */
+CLUSTEN_API int clusten_wf_backward(const void* d_feat_new, const void* weights, const void* feat,
+                        const int64_t* nbhd_idx, const void* inverse,
+                        void* d_weights, void* d_feat,
+                        int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLUSTEN_B200_H_ */

@@ -1,0 +1,223 @@
+"""Tensor-level calls into libclusten_b200: one function per C entry point.
+
+Inputs must be contiguous CUDA tensors of one floating dtype plus an int64
+index tensor; outputs are allocated here with torch.empty (the kernels write
+every element) and the kernels run on torch's current stream.
+"""
+import collections
+import os
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16,
+           torch.float64: _lib.F64}
+
+
+def _dt(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"clusten: unsupported dtype {t.dtype}") from None
+
+
+def _chk(name, t, dtype=None, dim=None):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise RuntimeError(f"{name} must have {dim} dimensions, got {t.dim()}")
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+# ----------------------------------------------------------------------------- inverse index
+class _InverseCache:
+    """Inverse indices of the most recently used nbhd_idx tensors.
+
+    All blocks of a stage, and the QK and AV operators inside each block,
+    receive the same nbhd_idx tensor (models/aff_transformer.py:480-495 of the
+    reference), so one inverse serves many backward calls.  An entry keeps a
+    reference to its index tensor, which pins the storage: a later tensor can
+    only match an entry by being that very storage, unmodified.
+    """
+
+    def __init__(self, capacity):
+        self.capacity = capacity
+        self.entries = collections.OrderedDict()
+
+    @staticmethod
+    def _key(idx, n_targets):
+        return (idx.data_ptr(), tuple(idx.shape), idx.device.index, n_targets)
+
+    def get(self, idx, n_targets):
+        key = self._key(idx, n_targets)
+        ent = self.entries.get(key)
+        if ent is not None and ent[1] == idx._version and ent[0]._version == idx._version:
+            self.entries.move_to_end(key)
+            return ent[2]
+        return None
+
+    def put(self, idx, n_targets, inv):
+        key = self._key(idx, n_targets)
+        self.entries[key] = (idx, idx._version, inv)
+        self.entries.move_to_end(key)
+        while len(self.entries) > self.capacity:
+            self.entries.popitem(last=False)
+
+    def clear(self):
+        self.entries.clear()
+
+
+_cache = _InverseCache(int(os.environ.get("CLUSTEN_INVERSE_CACHE", "4")))
+
+
+def clear_inverse_cache():
+    """Drop every cached inverse index (and the index tensors they pin)."""
+    _cache.clear()
+
+
+def build_inverse(nbhd_idx, n_targets):
+    """Inverse of nbhd_idx [b, rows, m] over n_targets tokens -> opaque int32 buffer."""
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, rows, m = nbhd_idx.shape
+    lib = _lib.load()
+    nbytes = lib.clusten_inverse_bytes(b, rows, m, n_targets)
+    if nbytes == 0:
+        _lib.check(lib.clusten_inverse_build(None, b, rows, m, n_targets, None, 0, None))
+        raise RuntimeError("clusten: inverse index not available for these sizes")
+    inv = torch.empty(nbytes // 4, dtype=torch.int32, device=nbhd_idx.device)
+    with torch.cuda.device_of(nbhd_idx):
+        _lib.check(lib.clusten_inverse_build(nbhd_idx.data_ptr(), b, rows, m, n_targets, inv.data_ptr(),
+                                             nbytes, _stream(nbhd_idx)))
+    return inv
+
+
+def inverse_for(nbhd_idx, n_targets):
+    """Cached build_inverse."""
+    if _cache.capacity <= 0:
+        return build_inverse(nbhd_idx, n_targets)
+    inv = _cache.get(nbhd_idx, n_targets)
+    if inv is None:
+        inv = build_inverse(nbhd_idx, n_targets)
+        _cache.put(nbhd_idx, n_targets, inv)
+    return inv
+
+
+# ----------------------------------------------------------------------------- QK
+def qk_forward(query, key, nbhd_idx):
+    """attn[b,h,i,j] = <query[b,h,i], key[b,h,nbhd_idx[b,i,j]]>"""
+    _chk("query", query, dim=4)
+    _chk("key", key, query.dtype, 4)
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, h, n, c = query.shape
+    m = nbhd_idx.shape[2]
+    if key.shape != query.shape or nbhd_idx.shape[:2] != (b, n):
+        raise RuntimeError("clusten: QK shape mismatch")
+    attn = torch.empty((b, h, n, m), dtype=query.dtype, device=query.device)
+    with torch.cuda.device_of(query):
+        _lib.check(_lib.load().clusten_qk_forward(query.data_ptr(), key.data_ptr(), nbhd_idx.data_ptr(),
+                                                  attn.data_ptr(), b, h, n, m, c, _dt(query), _stream(query)))
+    return attn
+
+
+def qk_backward(d_attn, query, key, nbhd_idx, inverse=None):
+    _chk("d_attn", d_attn, query.dtype, 4)
+    _chk("query", query, dim=4)
+    _chk("key", key, query.dtype, 4)
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, h, n, c = query.shape
+    m = nbhd_idx.shape[2]
+    if d_attn.shape != (b, h, n, m) or key.shape != query.shape:
+        raise RuntimeError("clusten: QK backward shape mismatch")
+    if inverse is None:
+        inverse = inverse_for(nbhd_idx, n)
+    d_query = torch.empty_like(query)
+    d_key = torch.empty_like(key)
+    with torch.cuda.device_of(query):
+        _lib.check(_lib.load().clusten_qk_backward(
+            d_attn.data_ptr(), query.data_ptr(), key.data_ptr(), nbhd_idx.data_ptr(), inverse.data_ptr(),
+            d_query.data_ptr(), d_key.data_ptr(), b, h, n, m, c, _dt(query), _stream(query)))
+    return d_query, d_key
+
+
+# ----------------------------------------------------------------------------- AV
+def av_forward(attn, value, nbhd_idx):
+    """feat[b,h,i,:] = sum_j attn[b,h,i,j] * value[b,h,nbhd_idx[b,i,j],:]"""
+    _chk("attn", attn, dim=4)
+    _chk("v", value, attn.dtype, 4)
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, h, n, m = attn.shape
+    c = value.shape[3]
+    if value.shape[:3] != (b, h, n) or nbhd_idx.shape != (b, n, m):
+        raise RuntimeError("clusten: AV shape mismatch")
+    feat = torch.empty((b, h, n, c), dtype=attn.dtype, device=attn.device)
+    with torch.cuda.device_of(attn):
+        _lib.check(_lib.load().clusten_av_forward(attn.data_ptr(), value.data_ptr(), nbhd_idx.data_ptr(),
+                                                  feat.data_ptr(), b, h, n, m, c, _dt(attn), _stream(attn)))
+    return feat
+
+
+def av_backward(d_feat, attn, value, nbhd_idx, inverse=None):
+    _chk("d_feat", d_feat, attn.dtype, 4)
+    _chk("attn", attn, dim=4)
+    _chk("v", value, attn.dtype, 4)
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, h, n, m = attn.shape
+    c = value.shape[3]
+    if d_feat.shape != value.shape or nbhd_idx.shape != (b, n, m):
+        raise RuntimeError("clusten: AV backward shape mismatch")
+    if inverse is None:
+        inverse = inverse_for(nbhd_idx, n)
+    d_attn = torch.empty_like(attn)
+    d_value = torch.empty_like(value)
+    with torch.cuda.device_of(attn):
+        _lib.check(_lib.load().clusten_av_backward(
+            d_feat.data_ptr(), attn.data_ptr(), value.data_ptr(), nbhd_idx.data_ptr(), inverse.data_ptr(),
+            d_attn.data_ptr(), d_value.data_ptr(), b, h, n, m, c, _dt(attn), _stream(attn)))
+    return d_attn, d_value
+
+
+# ----------------------------------------------------------------------------- WF
+def wf_forward(weights, feat, nbhd_idx):
+    """feat_new[b,i,ic,:] = sum_j weights[b,i,j,ic] * feat[b,nbhd_idx[b,i,j],:]"""
+    _chk("weights", weights, dim=4)
+    _chk("feat", feat, weights.dtype, 3)
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, n_out, m, ic = weights.shape
+    n, c = feat.shape[1], feat.shape[2]
+    if feat.shape[0] != b or nbhd_idx.shape != (b, n_out, m):
+        raise RuntimeError("clusten: WF shape mismatch")
+    feat_new = torch.empty((b, n_out, ic, c), dtype=weights.dtype, device=weights.device)
+    with torch.cuda.device_of(weights):
+        _lib.check(_lib.load().clusten_wf_forward(
+            weights.data_ptr(), feat.data_ptr(), nbhd_idx.data_ptr(), feat_new.data_ptr(),
+            b, n_out, n, m, ic, c, _dt(weights), _stream(weights)))
+    return feat_new
+
+
+def wf_backward(d_feat_new, weights, feat, nbhd_idx, inverse=None):
+    _chk("d_feat_new", d_feat_new, weights.dtype, 4)
+    _chk("weights", weights, dim=4)
+    _chk("feat", feat, weights.dtype, 3)
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, n_out, m, ic = weights.shape
+    n, c = feat.shape[1], feat.shape[2]
+    if d_feat_new.shape != (b, n_out, ic, c) or nbhd_idx.shape != (b, n_out, m):
+        raise RuntimeError("clusten: WF backward shape mismatch")
+    if inverse is None:
+        inverse = inverse_for(nbhd_idx, n)
+    d_weights = torch.empty_like(weights)
+    d_feat = torch.empty_like(feat)
+    with torch.cuda.device_of(weights):
+        _lib.check(_lib.load().clusten_wf_backward(
+            d_feat_new.data_ptr(), weights.data_ptr(), feat.data_ptr(), nbhd_idx.data_ptr(),
+            inverse.data_ptr(), d_weights.data_ptr(), d_feat.data_ptr(),
+            b, n_out, n, m, ic, c, _dt(weights), _stream(weights)))
+    return d_weights, d_feat

@@ -1,0 +1,229 @@
+// extern "C" entry points of libclusten_b200.so: argument checks and the
+// choice between the tiled and the shape-agnostic kernels.  Declarations and
+// the reference interfaces they replace are in include/clusten_b200.h.
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+#include "tiled.cuh"
+
+namespace clusten {
+
+static std::atomic<unsigned long long> g_launches{0};
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int check_launch() { return cudaGetLastError() == cudaSuccess ? CLUSTEN_OK : CLUSTEN_ERR_CUDA; }
+
+int sm_count() {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lk(mu);
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+namespace {
+
+bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
+
+// sizes common to QK and AV
+int check_attn_args(int b, int h, int n, int m, int c, int dtype) {
+    if (dtype_size(dtype) == 0) return CLUSTEN_ERR_DTYPE;
+    if (b <= 0 || h <= 0 || n <= 0 || m <= 0 || c <= 0) return CLUSTEN_ERR_SHAPE;
+    const long long lim = 0x7fffffffLL;
+    if ((long long)b * h > lim || (long long)n * m > lim || (long long)n * c > lim) return CLUSTEN_ERR_SHAPE;
+    return CLUSTEN_OK;
+}
+
+int check_wf_args(int b, int n_out, int n, int m, int ic, int c, int dtype) {
+    if (dtype_size(dtype) == 0) return CLUSTEN_ERR_DTYPE;
+    if (b <= 0 || n_out <= 0 || n <= 0 || m <= 0 || ic <= 0 || c <= 0) return CLUSTEN_ERR_SHAPE;
+    const long long lim = 0x7fffffffLL;
+    if ((long long)n_out * m * ic > lim || (long long)n * c > lim || (long long)n_out * ic * c > lim)
+        return CLUSTEN_ERR_SHAPE;
+    return CLUSTEN_OK;
+}
+
+int check_inverse_args(int b, int n_rows, int m, int nt) {
+    if (b <= 0 || n_rows <= 0 || m <= 0 || nt <= 0) return CLUSTEN_ERR_SHAPE;
+    if (m > 2048 || nt > kInvMaxTargets || (long long)n_rows * m >= 0x7fffffffLL) return CLUSTEN_ERR_UNSUPPORTED;
+    return CLUSTEN_OK;
+}
+
+#define CLUSTEN_REQUIRE_PTR(p, a)                       \
+    do {                                                \
+        if ((p) == nullptr) return CLUSTEN_ERR_NULL;    \
+        if (!aligned((p), (a))) return CLUSTEN_ERR_ALIGN; \
+    } while (0)
+
+}  // namespace
+}  // namespace clusten
+
+using namespace clusten;
+
+extern "C" {
+
+const char* clusten_status_string(int status) {
+    switch (status) {
+        case CLUSTEN_OK: return "CLUSTEN_OK";
+        case CLUSTEN_ERR_DTYPE: return "CLUSTEN_ERR_DTYPE: unknown element type";
+        case CLUSTEN_ERR_SHAPE: return "CLUSTEN_ERR_SHAPE: a size is not positive or too large";
+        case CLUSTEN_ERR_NULL: return "CLUSTEN_ERR_NULL: a required pointer is NULL";
+        case CLUSTEN_ERR_ALIGN: return "CLUSTEN_ERR_ALIGN: a pointer is not aligned to its element size";
+        case CLUSTEN_ERR_WORKSPACE: return "CLUSTEN_ERR_WORKSPACE: inverse-index buffer too small";
+        case CLUSTEN_ERR_UNSUPPORTED: return "CLUSTEN_ERR_UNSUPPORTED: size outside the supported range";
+        case CLUSTEN_ERR_CUDA: return "CLUSTEN_ERR_CUDA: the CUDA runtime reported an error";
+        default: return "CLUSTEN: unknown status";
+    }
+}
+
+int clusten_version(void) { return 100; }
+
+unsigned long long clusten_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+size_t clusten_inverse_bytes(int b, int n_rows, int m, int n_targets) {
+    if (check_inverse_args(b, n_rows, m, n_targets) != CLUSTEN_OK) return 0;
+    return inverse_ints(b, n_rows, m, n_targets) * sizeof(int);
+}
+
+int clusten_inverse_build(const int64_t* nbhd_idx, int b, int n_rows, int m, int n_targets, void* inverse,
+                          size_t inverse_bytes, void* stream) {
+    const int st = check_inverse_args(b, n_rows, m, n_targets);
+    if (st != CLUSTEN_OK) return st;
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(inverse, 16);
+    if (inverse_bytes < inverse_ints(b, n_rows, m, n_targets) * sizeof(int)) return CLUSTEN_ERR_WORKSPACE;
+    return launch_inverse_build(nbhd_idx, b, n_rows, m, n_targets, inverse, (cudaStream_t)stream);
+}
+
+int clusten_qk_forward(const void* query, const void* key, const int64_t* nbhd_idx, void* attn, int b, int h,
+                       int n, int m, int c, int dtype, void* stream) {
+    const int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(query, es);
+    CLUSTEN_REQUIRE_PTR(key, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(attn, es);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (tiled_dot_supported(dtype, query, key, attn, n, m, c))
+        return launch_tiled_dot(dtype, key, query, nbhd_idx, attn, b, h, n, m, s);
+    return launch_gather_dot(dtype, key, query, nbhd_idx, attn, b * h, h, n, n, m, 1, c, s);
+}
+
+int clusten_qk_backward(const void* d_attn, const void* query, const void* key, const int64_t* nbhd_idx,
+                        const void* inverse, void* d_query, void* d_key, int b, int h, int n, int m, int c,
+                        int dtype, void* stream) {
+    int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    st = check_inverse_args(b, n, m, n);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(d_attn, es);
+    CLUSTEN_REQUIRE_PTR(query, es);
+    CLUSTEN_REQUIRE_PTR(key, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(inverse, 16);
+    CLUSTEN_REQUIRE_PTR(d_query, es);
+    CLUSTEN_REQUIRE_PTR(d_key, es);
+    cudaStream_t s = (cudaStream_t)stream;
+    const InverseView inv = inverse_view(inverse, b, n, m, n);
+    // d_query: weighted sum of gathered keys
+    if (tiled_sum_supported(dtype, d_attn, key, d_query, n, m, c))
+        st = launch_tiled_sum(dtype, d_attn, key, nbhd_idx, d_query, b, h, n, m, s);
+    else
+        st = launch_gather_sum(dtype, d_attn, key, nbhd_idx, d_query, b * h, h, n, n, m, 1, c, s);
+    if (st != CLUSTEN_OK) return st;
+    // d_key: segmented reduction of d_attn * query over the inverse index
+    if (tiled_scatter_supported(dtype, d_attn, query, d_key, n, m, c))
+        return launch_tiled_scatter(dtype, d_attn, query, nbhd_idx, inv, d_key, b, h, n, m, s);
+    return launch_scatter_sum(dtype, d_attn, query, nbhd_idx, inv, d_key, b * h, h, n, n, m, 1, c, s);
+}
+
+int clusten_av_forward(const void* attn, const void* value, const int64_t* nbhd_idx, void* feat, int b, int h,
+                       int n, int m, int c, int dtype, void* stream) {
+    const int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(attn, es);
+    CLUSTEN_REQUIRE_PTR(value, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(feat, es);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (tiled_sum_supported(dtype, attn, value, feat, n, m, c))
+        return launch_tiled_sum(dtype, attn, value, nbhd_idx, feat, b, h, n, m, s);
+    return launch_gather_sum(dtype, attn, value, nbhd_idx, feat, b * h, h, n, n, m, 1, c, s);
+}
+
+int clusten_av_backward(const void* d_feat, const void* attn, const void* value, const int64_t* nbhd_idx,
+                        const void* inverse, void* d_attn, void* d_value, int b, int h, int n, int m, int c,
+                        int dtype, void* stream) {
+    int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    st = check_inverse_args(b, n, m, n);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(d_feat, es);
+    CLUSTEN_REQUIRE_PTR(attn, es);
+    CLUSTEN_REQUIRE_PTR(value, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(inverse, 16);
+    CLUSTEN_REQUIRE_PTR(d_attn, es);
+    CLUSTEN_REQUIRE_PTR(d_value, es);
+    cudaStream_t s = (cudaStream_t)stream;
+    const InverseView inv = inverse_view(inverse, b, n, m, n);
+    // d_attn: dot of each gathered value row with the row's d_feat
+    if (tiled_dot_supported(dtype, d_feat, value, d_attn, n, m, c))
+        st = launch_tiled_dot(dtype, value, d_feat, nbhd_idx, d_attn, b, h, n, m, s);
+    else
+        st = launch_gather_dot(dtype, value, d_feat, nbhd_idx, d_attn, b * h, h, n, n, m, 1, c, s);
+    if (st != CLUSTEN_OK) return st;
+    // d_value: segmented reduction of attn * d_feat over the inverse index
+    if (tiled_scatter_supported(dtype, attn, d_feat, d_value, n, m, c))
+        return launch_tiled_scatter(dtype, attn, d_feat, nbhd_idx, inv, d_value, b, h, n, m, s);
+    return launch_scatter_sum(dtype, attn, d_feat, nbhd_idx, inv, d_value, b * h, h, n, n, m, 1, c, s);
+}
+
+int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx, void* feat_new, int b,
+                       int n_out, int n, int m, int ic, int c, int dtype, void* stream) {
+    const int st = check_wf_args(b, n_out, n, m, ic, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(weights, es);
+    CLUSTEN_REQUIRE_PTR(feat, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(feat_new, es);
+    return launch_gather_sum(dtype, weights, feat, nbhd_idx, feat_new, b, 1, n_out, n, m, ic, c,
+                             (cudaStream_t)stream);
+}
+
+int clusten_wf_backward(const void* d_feat_new, const void* weights, const void* feat, const int64_t* nbhd_idx,
+                        const void* inverse, void* d_weights, void* d_feat, int b, int n_out, int n, int m,
+                        int ic, int c, int dtype, void* stream) {
+    int st = check_wf_args(b, n_out, n, m, ic, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    st = check_inverse_args(b, n_out, m, n);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(d_feat_new, es);
+    CLUSTEN_REQUIRE_PTR(weights, es);
+    CLUSTEN_REQUIRE_PTR(feat, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(inverse, 16);
+    CLUSTEN_REQUIRE_PTR(d_weights, es);
+    CLUSTEN_REQUIRE_PTR(d_feat, es);
+    cudaStream_t s = (cudaStream_t)stream;
+    const InverseView inv = inverse_view(inverse, b, n_out, m, n);
+    st = launch_gather_dot(dtype, feat, d_feat_new, nbhd_idx, d_weights, b, 1, n_out, n, m, ic, c, s);
+    if (st != CLUSTEN_OK) return st;
+    return launch_scatter_sum(dtype, weights, d_feat_new, nbhd_idx, inv, d_feat, b, 1, n_out, n, m, ic, c, s);
+}
+
+}  // extern "C"

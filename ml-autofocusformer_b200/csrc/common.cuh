@@ -1,0 +1,121 @@
+// Shared device/host helpers of libclusten_b200: element-type traits, vector
+// loads, the inverse-index layout and the launch bookkeeping.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/clusten_b200.h"
+
+namespace clusten {
+
+// ---------------------------------------------------------------- element types
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    using acc_t = float;
+    static __device__ __forceinline__ float up(float x) { return x; }
+    static __device__ __forceinline__ float down(float x) { return x; }
+};
+template <> struct Elem<double> {
+    using acc_t = double;
+    static __device__ __forceinline__ double up(double x) { return x; }
+    static __device__ __forceinline__ double down(double x) { return x; }
+};
+template <> struct Elem<__half> {
+    using acc_t = float;
+    static __device__ __forceinline__ float up(__half x) { return __half2float(x); }
+    static __device__ __forceinline__ __half down(float x) { return __float2half_rn(x); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    using acc_t = float;
+    static __device__ __forceinline__ float up(__nv_bfloat16 x) { return __bfloat162float(x); }
+    static __device__ __forceinline__ __nv_bfloat16 down(float x) { return __float2bfloat16_rn(x); }
+};
+
+// V consecutive elements moved with one load/store instruction.
+template <typename T, int V> struct alignas(sizeof(T) * V) Vec { T v[V]; };
+
+template <typename T, int V>
+__device__ __forceinline__ Vec<T, V> ldg_vec(const T* p) {
+    return *reinterpret_cast<const Vec<T, V>*>(p);
+}
+template <typename T, int V>
+__device__ __forceinline__ void st_vec(T* p, const Vec<T, V>& x) {
+    *reinterpret_cast<Vec<T, V>*>(p) = x;
+}
+
+// ---------------------------------------------------------------- inverse index
+// Layout of the buffer filled by clusten_inverse_build (all int32):
+//   [0, 64)                       header: magic, b, n_rows, m, n_targets, #out-of-range indices
+//   rowptr  [b][n_targets + 1]    segment start of target t inside its batch element's entries
+//   seglen  [b][n_targets]        entries in the segment (<= rowptr[t+1]-rowptr[t])
+//   entries [b][n_rows * m]       row * m + slot of one (row, slot) with nbhd_idx == t.
+// A target that occurs several times in one row gets ONE entry, row * m with
+// kDupFlag set; the consumer then scans that row of nbhd_idx for all its
+// slots.  Segments are ordered by row, so every reduction order is fixed.
+constexpr int kInvHeaderInts = 64;
+constexpr uint32_t kInvMagic = 0x434c5354u;
+constexpr uint32_t kDupFlag = 0x80000000u;
+constexpr int kInvMaxTargets = 18000;
+
+struct InverseView {
+    const int* rowptr;    // [b][nt + 1]
+    const int* seglen;    // [b][nt]
+    const int* entries;   // [b][n_rows * m]
+};
+
+__host__ __device__ inline size_t inv_align(size_t x) { return (x + 63) & ~size_t(63); }
+
+inline size_t inverse_ints(int b, int n_rows, int m, int nt) {
+    return kInvHeaderInts + inv_align(size_t(b) * (nt + 1)) + inv_align(size_t(b) * nt) +
+           inv_align(size_t(b) * n_rows * m);
+}
+
+inline InverseView inverse_view(const void* buf, int b, int n_rows, int m, int nt) {
+    const int* p = static_cast<const int*>(buf);
+    InverseView v;
+    v.rowptr = p + kInvHeaderInts;
+    v.seglen = v.rowptr + inv_align(size_t(b) * (nt + 1));
+    v.entries = v.seglen + inv_align(size_t(b) * nt);
+    return v;
+}
+
+// ---------------------------------------------------------------- launches
+void note_launch();               // counts one kernel launch (api.cu)
+int check_launch();               // cudaGetLastError -> CLUSTEN_OK / CLUSTEN_ERR_CUDA
+int sm_count();                   // multiprocessors of the current device (cached per device)
+
+template <typename T> struct DtypeOf;
+template <> struct DtypeOf<float> { static constexpr int value = CLUSTEN_F32; };
+template <> struct DtypeOf<__half> { static constexpr int value = CLUSTEN_F16; };
+template <> struct DtypeOf<__nv_bfloat16> { static constexpr int value = CLUSTEN_BF16; };
+template <> struct DtypeOf<double> { static constexpr int value = CLUSTEN_F64; };
+
+inline int dtype_size(int dtype) {
+    switch (dtype) {
+        case CLUSTEN_F32: return 4;
+        case CLUSTEN_F16: return 2;
+        case CLUSTEN_BF16: return 2;
+        case CLUSTEN_F64: return 8;
+        default: return 0;
+    }
+}
+
+// ---------------------------------------------------------------- generic kernels (generic.cu)
+// out[bb, row, ic, :] = sum_j W[bb, row, j, ic] * X[bb, idx[bb / heads, row, j], :]
+int launch_gather_sum(int dtype, const void* W, const void* X, const int64_t* idx, void* out,
+                      int nb, int heads, int n_rows, int n_src, int m, int ic, int c, cudaStream_t s);
+// out[bb, row, j, ic] = sum_c X[bb, idx[bb / heads, row, j], c] * Y[bb, row, ic, c]
+int launch_gather_dot(int dtype, const void* X, const void* Y, const int64_t* idx, void* out,
+                      int nb, int heads, int n_rows, int n_src, int m, int ic, int c, cudaStream_t s);
+// out[bb, t, :] = sum_{(row, j): idx[bb / heads, row, j] == t} sum_ic W[bb, row, j, ic] * X[bb, row, ic, :]
+int launch_scatter_sum(int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
+                       void* out, int nb, int heads, int n_rows, int n_tgt, int m, int ic, int c,
+                       cudaStream_t s);
+
+// inverse.cu
+int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s);
+
+}  // namespace clusten

@@ -1,0 +1,170 @@
+// Inverse neighbour index: for every target token the list of (row, slot)
+// pairs of nbhd_idx that point at it, ordered by row.  It turns the
+// reference's atomicAdd scatter for d_key / d_value / d_feat
+// (clusten/src/clustenqk_cuda_kernel.cu:125, clustenav_cuda_kernel.cu:121,
+// clustenwf_cuda_kernel.cu:129) into a gather with a fixed summation order.
+//
+// One CTA per batch element.  Counters live in shared memory; the only
+// atomics are integer adds and ORs, whose results do not depend on the order
+// in which they are applied, so the buffer contents are deterministic.
+#include "common.cuh"
+
+namespace clusten {
+
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+
+__global__ void __launch_bounds__(kThreads)
+inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int* __restrict__ header,
+                     int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries) {
+    extern __shared__ int sm[];
+    int* base = sm;                                              // running write position of target t
+    unsigned* mask = reinterpret_cast<unsigned*>(sm + nt);       // rows of the current group that hit t
+    unsigned* dupm = reinterpret_cast<unsigned*>(sm + 2 * nt);   // rows that hit t more than once
+    __shared__ int warp_tot[kWarps];
+
+    const int b = blockIdx.x;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const long long E = (long long)n_rows * m;
+    const int64_t* ib = idx + (long long)b * E;
+    int* rp = rowptr + (long long)b * (nt + 1);
+    int* ent = entries + (long long)b * E;
+
+    if (b == 0 && tid == 0) {
+        header[0] = (int)kInvMagic;
+        header[1] = gridDim.x;
+        header[2] = n_rows;
+        header[3] = m;
+        header[4] = nt;
+    }
+    for (int t = tid; t < nt; t += kThreads) {
+        base[t] = 0;
+        mask[t] = 0u;
+        dupm[t] = 0u;
+    }
+    __syncthreads();
+
+    // pass 1: how often each target is referenced (upper bound of its segment length)
+    int oob = 0;
+    for (long long e = tid; e < E; e += kThreads) {
+        const long long tk = ib[e];
+        if (tk >= 0 && tk < nt) atomicAdd(&base[(int)tk], 1);
+        else ++oob;
+    }
+    if (oob) atomicAdd(&header[5], oob);
+    __syncthreads();
+
+    // exclusive scan of the counts -> segment starts
+    {
+        const int per = (nt + kThreads - 1) / kThreads;
+        const int lo = min(tid * per, nt);
+        const int hi = min(lo + per, nt);
+        int local = 0;
+        for (int t = lo; t < hi; ++t) local += base[t];
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += y;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_tot[lane];
+            int wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += y;
+            }
+            warp_tot[lane] = wi - w;   // exclusive
+        }
+        __syncthreads();
+        int run = warp_tot[warp] + incl - local;
+        for (int t = lo; t < hi; ++t) {
+            const int cnt = base[t];
+            base[t] = run;
+            rp[t] = run;
+            run += cnt;
+        }
+        if (hi == nt && lo < nt) rp[nt] = run;
+        if (nt == 0 && tid == 0) rp[0] = 0;
+    }
+    __syncthreads();
+
+    // pass 2: 32 rows at a time, one warp per row.  Within a group the position of
+    // row r inside target t's segment is the number of lower rows of the group that
+    // also hit t, read off a 32-bit row mask.
+    const unsigned bit = 1u << warp;
+    for (int g0 = 0; g0 < n_rows; g0 += kWarps) {
+        const int row = g0 + warp;
+        const bool live = row < n_rows;
+        const int64_t* irow = ib + (long long)row * m;
+        unsigned long long win = 0ull, last = 0ull;   // per 32-slot pass: this lane placed the entry / closes the group
+        if (live) {
+            for (int p = 0, j = lane; j < m; ++p, j += 32) {
+                const long long tk = irow[j];
+                if (tk >= 0 && tk < nt) {
+                    const unsigned old = atomicOr(&mask[(int)tk], bit);
+                    if (old & bit) atomicOr(&dupm[(int)tk], bit);
+                    else win |= 1ull << p;
+                }
+            }
+        }
+        __syncthreads();
+        if (live) {
+            for (int p = 0, j = lane; j < m; ++p, j += 32) {
+                if (!((win >> p) & 1ull)) continue;
+                const int tk = (int)irow[j];
+                const unsigned mk = mask[tk];
+                const int pos = base[tk] + __popc(mk & (bit - 1u));
+                const bool dup = (dupm[tk] & bit) != 0u;
+                ent[pos] = dup ? (int)(kDupFlag | (unsigned)(row * m)) : (row * m + j);
+                if ((mk >> warp) == 1u) last |= 1ull << p;
+            }
+        }
+        __syncthreads();
+        if (live) {
+            for (int p = 0, j = lane; j < m; ++p, j += 32) {
+                if (!((last >> p) & 1ull)) continue;
+                const int tk = (int)irow[j];
+                base[tk] += __popc(mask[tk]);
+                mask[tk] = 0u;
+                dupm[tk] = 0u;
+            }
+        }
+        __syncthreads();
+    }
+
+    int* sl = seglen + (long long)b * nt;
+    for (int t = tid; t < nt; t += kThreads) sl[t] = base[t] - rp[t];
+}
+
+}  // namespace
+
+int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s) {
+    int* p = static_cast<int*>(buf);
+    InverseView v = inverse_view(buf, b, n_rows, m, nt);
+    if (cudaMemsetAsync(p, 0, kInvHeaderInts * sizeof(int), s) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    const size_t smem = size_t(3) * nt * sizeof(int);
+    if (smem > 48 * 1024) {
+        if (cudaFuncSetAttribute(inverse_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return CLUSTEN_ERR_CUDA;
+        }
+    }
+    inverse_build_kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
+                                                   const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
+    note_launch();
+    return check_launch();
+}
+
+}  // namespace clusten

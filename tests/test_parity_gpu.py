@@ -1,0 +1,270 @@
+"""Parity of the CUDA operators (called through the C ABI) with the oracle on the
+same seeded inputs.  Integer/index work must be exact; floating results are
+compared with max|x - ref| / max|ref| against the fp64 oracle evaluated on the
+dtype-rounded inputs, tolerance per dtype in helpers.TOL (fp32 1e-5, bf16 2e-2)."""
+import pytest
+import torch
+
+import workloads
+from helpers import TOL, assert_close, exact, rel_err
+from oracle import formula, ref_cuda
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.fixture(scope="module")
+def ops(lib):
+    from clusten import ops as _ops
+    return _ops
+
+
+def _attention_case(regime, b, h, n, m, c, dtype, seed):
+    if regime == "model" and (m % 8 or n < 8):
+        regime = "random"
+    idx = workloads.make_index(regime, b, n, m, seed).to(DEV)
+    t = workloads.attention_operands(b, h, n, m, c, dtype, seed + 1)
+    return (idx,) + tuple(x.to(DEV) for x in t)
+
+
+# (b, h, n, m, c): cluster-structured stages, the reference tests' shape, a padded stage (n % 8 != 0),
+# m = n = 49 (every token is a neighbour), m = 144, head dims other than 32, n < m
+ATT_SHAPES = [
+    (2, 2, 392, 48, 32),
+    (3, 4, 196, 48, 32),
+    (2, 3, 73, 48, 32),
+    (2, 2, 49, 49, 32),
+    (1, 2, 160, 144, 32),
+    (2, 2, 64, 16, 16),
+    (1, 1, 40, 9, 24),
+    (1, 2, 96, 24, 64),
+    (1, 1, 5, 12, 7),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: str(d).split(".")[-1])
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+@pytest.mark.parametrize("shape", ATT_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_qk_av_forward_backward(ops, shape, regime, dtype):
+    b, h, n, m, c = shape
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case(regime, b, h, n, m, c, dtype, 100 + n)
+    out = ops.qk_forward(q, k, idx)
+    assert out.dtype == dtype and out.is_contiguous()
+    assert_close(out, exact("qk", "forward", q, k, idx), dtype, "qk forward")
+    dq, dk = ops.qk_backward(g_attn, q, k, idx)
+    rq, rk = exact("qk", "backward", g_attn, q, k, idx)
+    assert_close(dq, rq, dtype, "d_query")
+    assert_close(dk, rk, dtype, "d_key")
+
+    feat = ops.av_forward(attn, v, idx)
+    assert_close(feat, exact("av", "forward", attn, v, idx), dtype, "av forward")
+    da, dv = ops.av_backward(g_feat, attn, v, idx)
+    ra, rv = exact("av", "backward", g_feat, attn, v, idx)
+    assert_close(da, ra, dtype, "d_attn")
+    assert_close(dv, rv, dtype, "d_value")
+
+
+def test_fp64_is_accepted(ops):
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case("random", 2, 2, 64, 16, 32, torch.float64, 5)
+    assert_close(ops.qk_forward(q, k, idx), exact("qk", "forward", q, k, idx), torch.float64, "qk f64")
+    da, dv = ops.av_backward(g_feat, attn, v, idx)
+    ra, rv = exact("av", "backward", g_feat, attn, v, idx)
+    assert_close(da, ra, torch.float64, "d_attn f64")
+    assert_close(dv, rv, torch.float64, "d_value f64")
+
+
+# (b, n_out, n, m, ic, c)
+WF_SHAPES = [
+    (2, 98, 392, 48, 1, 64),
+    (2, 98, 392, 48, 4, 64),
+    (3, 64, 196, 48, 4, 32),
+    (2, 36, 184, 48, 4, 128),
+    (1, 14, 73, 48, 4, 256),
+    (1, 20, 100, 16, 3, 24),
+    (1, 7, 30, 5, 2, 9),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: str(d).split(".")[-1])
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+@pytest.mark.parametrize("shape", WF_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_wf_forward_backward(ops, shape, regime, dtype):
+    b, n_out, n, m, ic, c = shape
+    if regime == "model" and m % 8:
+        regime = "random"
+    if regime == "random":
+        idx = workloads.random_rows(b, n_out, n, m, 7).to(DEV)
+    else:
+        idx = workloads.select_rows(workloads.make_index(regime, b, n, m, 9), n_out, 10).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, dtype, 11))
+    out = ops.wf_forward(w, feat, idx)
+    assert out.shape == (b, n_out, ic, c) and out.dtype == dtype
+    assert_close(out, exact("wf", "forward", w, feat, idx), dtype, "wf forward")
+    dw, df = ops.wf_backward(g, w, feat, idx)
+    rw, rf = exact("wf", "backward", g, w, feat, idx)
+    assert_close(dw, rw, dtype, "d_weights")
+    assert_close(df, rf, dtype, "d_feat")
+
+
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+def test_inverse_index_is_exact(ops, regime):
+    """Every (row, slot) appears exactly once under its target, rows ascending; repeated
+    targets of a row are folded into one flagged entry."""
+    b, n, m = 3, 203, 48
+    idx = workloads.make_index(regime if regime != "model" else "model", b, n, m, 21)
+    if regime == "random":
+        idx[:, :, -3:] = 0          # padded-stage pattern: several slots of a row point at token 0
+    inv = ops.build_inverse(idx.to(DEV), n).cpu()
+    hdr = inv[:64]
+    assert hdr[1] == b and hdr[2] == n and hdr[3] == m and hdr[4] == n and hdr[5] == 0
+    pad = lambda x: (x + 63) // 64 * 64
+    o = 64
+    rowptr = inv[o:o + b * (n + 1)].view(b, n + 1); o += pad(b * (n + 1))
+    seglen = inv[o:o + b * n].view(b, n); o += pad(b * n)
+    entries = inv[o:o + b * n * m].view(b, n * m)
+    for bi in range(b):
+        counts = torch.bincount(idx[bi].flatten(), minlength=n)
+        assert torch.equal(rowptr[bi, 1:] - rowptr[bi, :-1], counts.int())
+        for t in range(n):
+            seg = entries[bi, rowptr[bi, t]:rowptr[bi, t] + seglen[bi, t]].long()
+            flagged = seg < 0
+            rows = torch.where(flagged, (seg & 0x7fffffff) // m, seg // m)
+            want_rows = (idx[bi] == t).any(1).nonzero().flatten()
+            assert torch.equal(rows, want_rows), (bi, t)
+            mult = (idx[bi][rows] == t).sum(1)
+            assert torch.equal(flagged, mult > 1)
+            slots = seg[~flagged] % m
+            assert (idx[bi][rows[~flagged], slots] == t).all()
+
+
+def test_out_of_range_indices_are_ignored(ops):
+    b, h, n, m, c = 1, 2, 64, 16, 32
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case("random", b, h, n, m, c, torch.float32, 31)
+    bad = idx.clone()
+    bad[0, ::3, 5] = n + 7
+    bad[0, 1::3, 2] = -1
+    mask = ((bad >= 0) & (bad < n)).float().unsqueeze(1)             # [b,1,n,m]
+    safe = bad.clamp(0, n - 1)
+    ref = formula.qk(q, k, safe) * mask
+    assert_close(ops.qk_forward(q, k, bad), ref, torch.float32, "qk with bad indices")
+    ref = formula.av(attn * mask, v, safe)
+    assert_close(ops.av_forward(attn, v, bad), ref, torch.float32, "av with bad indices")
+    da, dv = ops.av_backward(g_feat, attn, v, bad)
+    _, ra, rv = formula.forward_backward("av", attn * mask, v, safe, g_feat)
+    assert_close(da, ra * mask, torch.float32, "d_attn with bad indices")
+    assert_close(dv, rv, torch.float32, "d_value with bad indices")
+    assert ops.build_inverse(bad, n)[5].item() == int((mask == 0).sum())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def test_backward_is_bit_reproducible(ops, dtype):
+    """No atomics on floating data: two runs give identical bits, also with repeated indices."""
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case("random", 4, 4, 196, 48, 32, dtype, 41)
+    idx[:, :, -5:] = 0
+    first = ops.qk_backward(g_attn, q, k, idx) + ops.av_backward(g_feat, attn, v, idx)
+    ops.clear_inverse_cache()
+    again = ops.qk_backward(g_attn, q, k, idx) + ops.av_backward(g_feat, attn, v, idx)
+    for a, b_ in zip(first, again):
+        assert torch.equal(a, b_)
+
+
+def test_autograd_functions_on_model_style_views(ops):
+    """The operators as the model calls them (models/aff_transformer.py:117-120,145-154 of the
+    reference): q/k/v are permuted views of Linear outputs, attn a [..., :-1] slice."""
+    from clusten import CLUSTENAVFunction, CLUSTENQKFunction, CLUSTENWFFunction
+    torch.manual_seed(3)
+    b, h, n, m, c = 2, 4, 200, 48, 32
+    idx = workloads.model_like_rows(b, n, m, 51).to(DEV)
+    qlin = torch.randn(b, n, h * c, device=DEV, requires_grad=True)
+    kvlin = torch.randn(b, n, 2 * h * c, device=DEV, requires_grad=True)
+
+    def run(qk_fn, av_fn):
+        q = qlin.reshape(b, n, h, c).permute(0, 2, 1, 3)
+        kv = kvlin.view(b, n, h, 2, c).permute(3, 0, 2, 1, 4)
+        key, v = kv[0], kv[1]
+        attn = qk_fn(q, key, idx)
+        attn = torch.cat([attn, attn.new_zeros(b, h, n, 1)], -1).softmax(-1)[..., :-1]
+        feat = av_fn(attn, v, idx).permute(0, 2, 1, 3).reshape(b, n, h * c)
+        loss = (feat * torch.linspace(-1, 1, h * c, device=DEV)).sum()
+        gq, gkv = torch.autograd.grad(loss, [qlin, kvlin])
+        return feat, gq, gkv
+
+    got = run(CLUSTENQKFunction.apply, CLUSTENAVFunction.apply)
+    want = run(formula.qk, formula.av)
+    for g_, w_, name in zip(got, want, ["feat", "grad q", "grad kv"]):
+        assert rel_err(g_, w_) < 2e-5, name
+
+    w = torch.randn(b, 50, m, 4, device=DEV, requires_grad=True)
+    f = torch.randn(b, n, 64, device=DEV, dtype=torch.float16, requires_grad=True)   # cast to weights' dtype
+    idx_w = workloads.select_rows(idx, 50, 52)
+    out = CLUSTENWFFunction.apply(w, f, idx_w)
+    assert out.dtype == torch.float32 and out.shape == (b, 50, 4, 64)
+    gw, gf = torch.autograd.grad(out.square().sum(), [w, f])
+    ref = formula.wf(w, f.float(), idx_w)
+    rgw, rgf = torch.autograd.grad(ref.square().sum(), [w, f])
+    assert rel_err(out, ref) < 2e-5 and rel_err(gw, rgw) < 2e-5 and rel_err(gf, rgf) < 2e-3
+    assert gf.dtype == torch.float16
+    with torch.no_grad():
+        assert torch.equal(CLUSTENWFFunction.apply(w, f, idx_w), out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["float32", "float16"])
+def test_against_the_reference_cuda_extension(ops, dtype):
+    """The reference's own kernels (compiled unmodified into oracle/_ref) on the same inputs."""
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref is not built")
+    tol = 1e-5 if dtype == torch.float32 else 1e-2   # the reference accumulates fp16 sums in fp16
+    b, h, n, m, c = 4, 4, 196, 48, 32
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case("random", b, h, n, m, c, dtype, 61)
+    assert rel_err(ops.qk_forward(q, k, idx), ref_cuda.qk_forward(q, k, idx)) < tol
+    for mine, ref in zip(ops.qk_backward(g_attn, q, k, idx), ref_cuda.qk_backward(g_attn, q, k, idx)):
+        assert rel_err(mine, ref) < tol
+    assert rel_err(ops.av_forward(attn, v, idx), ref_cuda.av_forward(attn, v, idx)) < tol
+    for mine, ref in zip(ops.av_backward(g_feat, attn, v, idx), ref_cuda.av_backward(g_feat, attn, v, idx)):
+        assert rel_err(mine, ref) < tol
+    n_out, ic, cw = 64, 4, 32
+    idx_w = workloads.random_rows(b, n_out, n, m, 62).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, cw, dtype, 63))
+    assert rel_err(ops.wf_forward(w, feat, idx_w), ref_cuda.wf_forward(w, feat, idx_w)) < tol
+    for mine, ref in zip(ops.wf_backward(g, w, feat, idx_w), ref_cuda.wf_backward(g, w, feat, idx_w)):
+        assert rel_err(mine, ref) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def test_full_size_adjoint_identities(ops, dtype):
+    """Stage-1 shapes of the benchmark (b=128, h=2, n=3136, m=48, c=32; WF n_=784, c=64, ic=4),
+    where the oracle is too slow: each operator is bilinear, so <op(x, y), g> must equal
+    <x, grad_x> and <y, grad_y>, which ties forward, both gradients and the inverse index
+    together at full size."""
+    b, h, n, m, c = 128, 2, 3136, 48, 32
+    idx = workloads.shared_cluster_rows(b, n, m, 71, DEV)
+    q, k, v, attn, g_attn, g_feat = workloads.attention_operands(b, h, n, m, c, dtype, 72, DEV)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+
+    def dot(x, y):
+        return (x.double() * y.double()).sum().item()
+
+    out = ops.qk_forward(q, k, idx)
+    dq, dk = ops.qk_backward(g_attn, q, k, idx)
+    lhs = dot(out, g_attn)
+    assert abs(dot(q, dq) - lhs) <= tol * abs(lhs) and abs(dot(k, dk) - lhs) <= tol * abs(lhs)
+    feat = ops.av_forward(attn, v, idx)
+    da, dv = ops.av_backward(g_feat, attn, v, idx)
+    lhs = dot(feat, g_feat)
+    assert abs(dot(attn, da) - lhs) <= tol * abs(lhs) and abs(dot(v, dv) - lhs) <= tol * abs(lhs)
+    # spot-check a slice of the batch against the gather formulation evaluated on the GPU
+    sl = slice(5, 7)
+    ref = formula.av(attn[sl].float(), v[sl].float(), idx[sl])
+    assert rel_err(feat[sl], ref) <= TOL[dtype]
+
+    n_out, ic, cw = 784, 4, 64
+    idx_w = workloads.select_rows(idx, n_out, 73)
+    w, f, g = workloads.merge_operands(b, n_out, n, m, ic, cw, dtype, 74, DEV)
+    out = ops.wf_forward(w, f, idx_w)
+    dw, df = ops.wf_backward(g, w, f, idx_w)
+    lhs = dot(out, g)
+    assert abs(dot(w, dw) - lhs) <= tol * abs(lhs) and abs(dot(f, df) - lhs) <= tol * abs(lhs)
+    ref = formula.wf(w[sl].float(), f[sl].float(), idx_w[sl])
+    assert rel_err(out[sl], ref) <= TOL[dtype]
