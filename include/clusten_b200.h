@@ -70,6 +70,16 @@ CLUSTEN_API int clusten_version(void);
 /* Number of kernels this library has launched in this process (all threads). */
 CLUSTEN_API unsigned long long clusten_launch_count(void);
 
+/* Per-kernel timing for benchmarks.  While enabled, every kernel launch of the
+ * library is bracketed by two CUDA events recorded on the launch stream.
+ * clusten_timing_collect synchronises those events, writes one line per kernel
+ * name, "name launches total_ms\n", into buf (at most buf_bytes - 1 characters,
+ * NUL-terminated), clears the record and returns the number of lines, or a
+ * negative status.  Timing allocates CUDA events; leave it off in production.
+ * No counterpart in the reference. */
+CLUSTEN_API int clusten_timing_enable(int on);
+CLUSTEN_API int clusten_timing_collect(char* buf, size_t buf_bytes);
+
 /* ------------------------------------------------------------------------
  * Inverse neighbour index.
  *

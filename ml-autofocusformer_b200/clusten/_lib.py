@@ -18,6 +18,8 @@ SIGNATURES = {
     "clusten_status_string": (ctypes.c_char_p, [_i]),
     "clusten_version": (_i, []),
     "clusten_launch_count": (ctypes.c_ulonglong, []),
+    "clusten_timing_enable": (_i, [_i]),
+    "clusten_timing_collect": (_i, [ctypes.c_char_p, _sz]),
     "clusten_inverse_bytes": (_sz, [_i, _i, _i, _i]),
     "clusten_inverse_build": (_i, [_p, _i, _i, _i, _i, _p, _sz, _p]),
     "clusten_qk_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
@@ -56,6 +58,23 @@ def check(status):
     if status != 0:
         msg = load().clusten_status_string(status).decode()
         raise RuntimeError(f"clusten: {msg} (status {status})")
+
+
+def timing_enable(on):
+    check(load().clusten_timing_enable(1 if on else 0))
+
+
+def timing_collect():
+    """{kernel name: (launches, total_ms)} recorded since the last call; clears the record."""
+    buf = ctypes.create_string_buffer(1 << 16)
+    n = load().clusten_timing_collect(buf, len(buf))
+    if n < 0:
+        check(n)
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.split()
+        out[name] = (int(cnt), float(ms))
+    return out
 
 
 def launch_count():

@@ -2,7 +2,12 @@
 // choice between the tiled and the shape-agnostic kernels.  Declarations and
 // the reference interfaces they replace are in include/clusten_b200.h.
 #include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
 #include <mutex>
+#include <string>
+#include <vector>
 
 #include "common.cuh"
 #include "tiled.cuh"
@@ -12,6 +17,36 @@ namespace clusten {
 static std::atomic<unsigned long long> g_launches{0};
 
 void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ---- optional per-kernel timing -------------------------------------------------------------
+namespace {
+struct TimedLaunch {
+    const char* name;
+    cudaEvent_t start, stop;
+};
+std::atomic<int> g_timing{0};
+std::mutex g_timing_mu;
+std::vector<TimedLaunch> g_timed;
+}  // namespace
+
+ScopedKernelTimer::ScopedKernelTimer(const char* name, cudaStream_t s) : slot(-1), stream(s) {
+    if (!g_timing.load(std::memory_order_relaxed)) return;
+    TimedLaunch t{name, nullptr, nullptr};
+    if (cudaEventCreate(&t.start) != cudaSuccess || cudaEventCreate(&t.stop) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    cudaEventRecord(t.start, s);
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    slot = (int)g_timed.size();
+    g_timed.push_back(t);
+}
+
+ScopedKernelTimer::~ScopedKernelTimer() {
+    if (slot < 0) return;
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    cudaEventRecord(g_timed[slot].stop, stream);
+}
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? CLUSTEN_OK : CLUSTEN_ERR_CUDA; }
 
@@ -86,6 +121,52 @@ const char* clusten_status_string(int status) {
 
 int clusten_version(void) { return 100; }
 
+int clusten_timing_enable(int on) {
+    g_timing.store(on ? 1 : 0, std::memory_order_relaxed);
+    return CLUSTEN_OK;
+}
+
+int clusten_timing_collect(char* buf, size_t buf_bytes) {
+    if (buf == nullptr || buf_bytes == 0) return CLUSTEN_ERR_NULL;
+    std::vector<TimedLaunch> taken;
+    {
+        std::lock_guard<std::mutex> lk(g_timing_mu);
+        taken.swap(g_timed);
+    }
+    std::map<std::string, std::pair<long long, double>> acc;
+    std::vector<std::string> order;
+    int status = CLUSTEN_OK;
+    for (auto& t : taken) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(t.stop) != cudaSuccess || cudaEventElapsedTime(&ms, t.start, t.stop) != cudaSuccess) {
+            cudaGetLastError();
+            status = CLUSTEN_ERR_CUDA;
+        } else {
+            auto it = acc.find(t.name);
+            if (it == acc.end()) {
+                order.push_back(t.name);
+                acc[t.name] = {1, ms};
+            } else {
+                it->second.first += 1;
+                it->second.second += ms;
+            }
+        }
+        cudaEventDestroy(t.start);
+        cudaEventDestroy(t.stop);
+    }
+    if (status != CLUSTEN_OK) return status;
+    std::string out;
+    char line[256];
+    for (auto& name : order) {
+        snprintf(line, sizeof line, "%s %lld %.6f\n", name.c_str(), acc[name].first, acc[name].second);
+        out += line;
+    }
+    const size_t n = out.size() < buf_bytes - 1 ? out.size() : buf_bytes - 1;
+    memcpy(buf, out.data(), n);
+    buf[n] = 0;
+    return (int)order.size();
+}
+
 unsigned long long clusten_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 size_t clusten_inverse_bytes(int b, int n_rows, int m, int n_targets) {
@@ -115,7 +196,7 @@ int clusten_qk_forward(const void* query, const void* key, const int64_t* nbhd_i
     cudaStream_t s = (cudaStream_t)stream;
     if (tiled_dot_supported(dtype, query, key, attn, n, m, c))
         return launch_tiled_dot(dtype, key, query, nbhd_idx, attn, b, h, n, m, s);
-    return launch_gather_dot(dtype, key, query, nbhd_idx, attn, b * h, h, n, n, m, 1, c, s);
+    return launch_gather_dot("qk_forward", dtype, key, query, nbhd_idx, attn, b * h, h, n, n, m, 1, c, s);
 }
 
 int clusten_qk_backward(const void* d_attn, const void* query, const void* key, const int64_t* nbhd_idx,
@@ -139,12 +220,12 @@ int clusten_qk_backward(const void* d_attn, const void* query, const void* key, 
     if (tiled_sum_supported(dtype, d_attn, key, d_query, n, m, c))
         st = launch_tiled_sum(dtype, d_attn, key, nbhd_idx, d_query, b, h, n, m, s);
     else
-        st = launch_gather_sum(dtype, d_attn, key, nbhd_idx, d_query, b * h, h, n, n, m, 1, c, s);
+        st = launch_gather_sum("qk_d_query", dtype, d_attn, key, nbhd_idx, d_query, b * h, h, n, n, m, 1, c, s);
     if (st != CLUSTEN_OK) return st;
     // d_key: segmented reduction of d_attn * query over the inverse index
     if (tiled_scatter_supported(dtype, d_attn, query, d_key, n, m, c))
         return launch_tiled_scatter(dtype, d_attn, query, nbhd_idx, inv, d_key, b, h, n, m, s);
-    return launch_scatter_sum(dtype, d_attn, query, nbhd_idx, inv, d_key, b * h, h, n, n, m, 1, c, s);
+    return launch_scatter_sum("qk_d_key", dtype, d_attn, query, nbhd_idx, inv, d_key, b * h, h, n, n, m, 1, c, s);
 }
 
 int clusten_av_forward(const void* attn, const void* value, const int64_t* nbhd_idx, void* feat, int b, int h,
@@ -159,7 +240,7 @@ int clusten_av_forward(const void* attn, const void* value, const int64_t* nbhd_
     cudaStream_t s = (cudaStream_t)stream;
     if (tiled_sum_supported(dtype, attn, value, feat, n, m, c))
         return launch_tiled_sum(dtype, attn, value, nbhd_idx, feat, b, h, n, m, s);
-    return launch_gather_sum(dtype, attn, value, nbhd_idx, feat, b * h, h, n, n, m, 1, c, s);
+    return launch_gather_sum("av_forward", dtype, attn, value, nbhd_idx, feat, b * h, h, n, n, m, 1, c, s);
 }
 
 int clusten_av_backward(const void* d_feat, const void* attn, const void* value, const int64_t* nbhd_idx,
@@ -183,12 +264,12 @@ int clusten_av_backward(const void* d_feat, const void* attn, const void* value,
     if (tiled_dot_supported(dtype, d_feat, value, d_attn, n, m, c))
         st = launch_tiled_dot(dtype, value, d_feat, nbhd_idx, d_attn, b, h, n, m, s);
     else
-        st = launch_gather_dot(dtype, value, d_feat, nbhd_idx, d_attn, b * h, h, n, n, m, 1, c, s);
+        st = launch_gather_dot("av_d_attn", dtype, value, d_feat, nbhd_idx, d_attn, b * h, h, n, n, m, 1, c, s);
     if (st != CLUSTEN_OK) return st;
     // d_value: segmented reduction of attn * d_feat over the inverse index
     if (tiled_scatter_supported(dtype, attn, d_feat, d_value, n, m, c))
         return launch_tiled_scatter(dtype, attn, d_feat, nbhd_idx, inv, d_value, b, h, n, m, s);
-    return launch_scatter_sum(dtype, attn, d_feat, nbhd_idx, inv, d_value, b * h, h, n, n, m, 1, c, s);
+    return launch_scatter_sum("av_d_value", dtype, attn, d_feat, nbhd_idx, inv, d_value, b * h, h, n, n, m, 1, c, s);
 }
 
 int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx, void* feat_new, int b,
@@ -200,7 +281,7 @@ int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbh
     CLUSTEN_REQUIRE_PTR(feat, es);
     CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
     CLUSTEN_REQUIRE_PTR(feat_new, es);
-    return launch_gather_sum(dtype, weights, feat, nbhd_idx, feat_new, b, 1, n_out, n, m, ic, c,
+    return launch_gather_sum("wf_forward", dtype, weights, feat, nbhd_idx, feat_new, b, 1, n_out, n, m, ic, c,
                              (cudaStream_t)stream);
 }
 
@@ -221,9 +302,9 @@ int clusten_wf_backward(const void* d_feat_new, const void* weights, const void*
     CLUSTEN_REQUIRE_PTR(d_feat, es);
     cudaStream_t s = (cudaStream_t)stream;
     const InverseView inv = inverse_view(inverse, b, n_out, m, n);
-    st = launch_gather_dot(dtype, feat, d_feat_new, nbhd_idx, d_weights, b, 1, n_out, n, m, ic, c, s);
+    st = launch_gather_dot("wf_d_weights", dtype, feat, d_feat_new, nbhd_idx, d_weights, b, 1, n_out, n, m, ic, c, s);
     if (st != CLUSTEN_OK) return st;
-    return launch_scatter_sum(dtype, weights, d_feat_new, nbhd_idx, inv, d_feat, b, 1, n_out, n, m, ic, c, s);
+    return launch_scatter_sum("wf_d_feat", dtype, weights, d_feat_new, nbhd_idx, inv, d_feat, b, 1, n_out, n, m, ic, c, s);
 }
 
 }  // extern "C"

@@ -84,6 +84,14 @@ inline InverseView inverse_view(const void* buf, int b, int n_rows, int m, int n
 
 // ---------------------------------------------------------------- launches
 void note_launch();               // counts one kernel launch (api.cu)
+
+// Brackets one kernel launch with CUDA events when timing is enabled (api.cu).
+struct ScopedKernelTimer {
+    ScopedKernelTimer(const char* name, cudaStream_t s);
+    ~ScopedKernelTimer();
+    int slot;
+    cudaStream_t stream;
+};
 int check_launch();               // cudaGetLastError -> CLUSTEN_OK / CLUSTEN_ERR_CUDA
 int sm_count();                   // multiprocessors of the current device (cached per device)
 
@@ -105,13 +113,13 @@ inline int dtype_size(int dtype) {
 
 // ---------------------------------------------------------------- generic kernels (generic.cu)
 // out[bb, row, ic, :] = sum_j W[bb, row, j, ic] * X[bb, idx[bb / heads, row, j], :]
-int launch_gather_sum(int dtype, const void* W, const void* X, const int64_t* idx, void* out,
+int launch_gather_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out,
                       int nb, int heads, int n_rows, int n_src, int m, int ic, int c, cudaStream_t s);
 // out[bb, row, j, ic] = sum_c X[bb, idx[bb / heads, row, j], c] * Y[bb, row, ic, c]
-int launch_gather_dot(int dtype, const void* X, const void* Y, const int64_t* idx, void* out,
+int launch_gather_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out,
                       int nb, int heads, int n_rows, int n_src, int m, int ic, int c, cudaStream_t s);
 // out[bb, t, :] = sum_{(row, j): idx[bb / heads, row, j] == t} sum_ic W[bb, row, j, ic] * X[bb, row, ic, :]
-int launch_scatter_sum(int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
+int launch_scatter_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
                        void* out, int nb, int heads, int n_rows, int n_tgt, int m, int ic, int c,
                        cudaStream_t s);
 

@@ -249,12 +249,13 @@ int grid_for(long long rows) {
 }
 
 template <typename T>
-int gather_sum_t(const void* W, const void* X, const int64_t* idx, void* out, int nb, int heads, int n_rows,
+int gather_sum_t(const char* label, const void* W, const void* X, const int64_t* idx, void* out, int nb, int heads, int n_rows,
                  int n_src, int m, int ic, int c, cudaStream_t s) {
     const int v = pick_vec(c, sizeof(T), {X, out});
     const int grid = grid_for((long long)nb * n_rows);
     const int step = (ic % 4 == 0) ? 4 : 1;
     for (int ic0 = 0; ic0 < ic; ic0 += step) {
+        ScopedKernelTimer timer(label, s);
 #define CLUSTEN_GS(VV, II)                                                                              \
     gather_sum_kernel<T, VV, II><<<grid, kThreads, 0, s>>>((const T*)W, (const T*)X, idx, (T*)out, nb, \
                                                            heads, n_rows, n_src, m, ic, ic0, c)
@@ -272,12 +273,13 @@ int gather_sum_t(const void* W, const void* X, const int64_t* idx, void* out, in
 }
 
 template <typename T>
-int gather_dot_t(const void* X, const void* Y, const int64_t* idx, void* out, int nb, int heads, int n_rows,
+int gather_dot_t(const char* label, const void* X, const void* Y, const int64_t* idx, void* out, int nb, int heads, int n_rows,
                  int n_src, int m, int ic, int c, cudaStream_t s) {
     const int v = pick_vec(c, sizeof(T), {X, Y});
     const int grid = grid_for((long long)nb * n_rows);
     const int step = (ic % 4 == 0) ? 4 : 1;
     for (int ic0 = 0; ic0 < ic; ic0 += step) {
+        ScopedKernelTimer timer(label, s);
 #define CLUSTEN_GD(VV, II)                                                                              \
     gather_dot_kernel<T, VV, II><<<grid, kThreads, 0, s>>>((const T*)X, (const T*)Y, idx, (T*)out, nb, \
                                                            heads, n_rows, n_src, m, ic, ic0, c)
@@ -295,10 +297,11 @@ int gather_dot_t(const void* X, const void* Y, const int64_t* idx, void* out, in
 }
 
 template <typename T>
-int scatter_sum_t(const void* W, const void* X, const int64_t* idx, const InverseView& inv, void* out, int nb,
+int scatter_sum_t(const char* label, const void* W, const void* X, const int64_t* idx, const InverseView& inv, void* out, int nb,
                   int heads, int n_rows, int n_tgt, int m, int ic, int c, cudaStream_t s) {
     const int v = pick_vec(c, sizeof(T), {X, out});
     const int grid = grid_for((long long)nb * n_tgt);
+    ScopedKernelTimer timer(label, s);
 #define CLUSTEN_SS(VV)                                                                                  \
     scatter_sum_kernel<T, VV><<<grid, kThreads, 0, s>>>((const T*)W, (const T*)X, idx, inv, (T*)out, nb, \
                                                         heads, n_rows, n_tgt, m, ic, c)
@@ -319,20 +322,20 @@ int scatter_sum_t(const void* W, const void* X, const int64_t* idx, const Invers
         default: return CLUSTEN_ERR_DTYPE;                                       \
     }
 
-int launch_gather_sum(int dtype, const void* W, const void* X, const int64_t* idx, void* out, int nb, int heads,
+int launch_gather_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out, int nb, int heads,
                       int n_rows, int n_src, int m, int ic, int c, cudaStream_t s) {
-    CLUSTEN_DISPATCH(dtype, gather_sum_t, W, X, idx, out, nb, heads, n_rows, n_src, m, ic, c, s)
+    CLUSTEN_DISPATCH(dtype, gather_sum_t, label, W, X, idx, out, nb, heads, n_rows, n_src, m, ic, c, s)
 }
 
-int launch_gather_dot(int dtype, const void* X, const void* Y, const int64_t* idx, void* out, int nb, int heads,
+int launch_gather_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out, int nb, int heads,
                       int n_rows, int n_src, int m, int ic, int c, cudaStream_t s) {
-    CLUSTEN_DISPATCH(dtype, gather_dot_t, X, Y, idx, out, nb, heads, n_rows, n_src, m, ic, c, s)
+    CLUSTEN_DISPATCH(dtype, gather_dot_t, label, X, Y, idx, out, nb, heads, n_rows, n_src, m, ic, c, s)
 }
 
-int launch_scatter_sum(int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
+int launch_scatter_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
                        void* out, int nb, int heads, int n_rows, int n_tgt, int m, int ic, int c,
                        cudaStream_t s) {
-    CLUSTEN_DISPATCH(dtype, scatter_sum_t, W, X, idx, inv, out, nb, heads, n_rows, n_tgt, m, ic, c, s)
+    CLUSTEN_DISPATCH(dtype, scatter_sum_t, label, W, X, idx, inv, out, nb, heads, n_rows, n_tgt, m, ic, c, s)
 }
 
 }  // namespace clusten

@@ -161,6 +161,7 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
             return CLUSTEN_ERR_CUDA;
         }
     }
+    ScopedKernelTimer timer("inverse_build", s);
     inverse_build_kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
                                                    const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
     note_launch();
