@@ -195,7 +195,7 @@ int clusten_qk_forward(const void* query, const void* key, const int64_t* nbhd_i
     CLUSTEN_REQUIRE_PTR(attn, es);
     cudaStream_t s = (cudaStream_t)stream;
     if (tiled_dot_supported(dtype, query, key, attn, n, m, c))
-        return launch_tiled_dot(dtype, key, query, nbhd_idx, attn, b, h, n, m, s);
+        return launch_tiled_dot("qk_forward", dtype, key, query, nbhd_idx, attn, b, h, n, m, s);
     return launch_gather_dot("qk_forward", dtype, key, query, nbhd_idx, attn, b * h, h, n, n, m, 1, c, s);
 }
 
@@ -218,13 +218,13 @@ int clusten_qk_backward(const void* d_attn, const void* query, const void* key, 
     const InverseView inv = inverse_view(inverse, b, n, m, n);
     // d_query: weighted sum of gathered keys
     if (tiled_sum_supported(dtype, d_attn, key, d_query, n, m, c))
-        st = launch_tiled_sum(dtype, d_attn, key, nbhd_idx, d_query, b, h, n, m, s);
+        st = launch_tiled_sum("qk_d_query", dtype, d_attn, key, nbhd_idx, d_query, b, h, n, m, s);
     else
         st = launch_gather_sum("qk_d_query", dtype, d_attn, key, nbhd_idx, d_query, b * h, h, n, n, m, 1, c, s);
     if (st != CLUSTEN_OK) return st;
     // d_key: segmented reduction of d_attn * query over the inverse index
     if (tiled_scatter_supported(dtype, d_attn, query, d_key, n, m, c))
-        return launch_tiled_scatter(dtype, d_attn, query, nbhd_idx, inv, d_key, b, h, n, m, s);
+        return launch_tiled_scatter("qk_d_key", dtype, d_attn, query, nbhd_idx, inv, d_key, b, h, n, m, s);
     return launch_scatter_sum("qk_d_key", dtype, d_attn, query, nbhd_idx, inv, d_key, b * h, h, n, n, m, 1, c, s);
 }
 
@@ -239,7 +239,7 @@ int clusten_av_forward(const void* attn, const void* value, const int64_t* nbhd_
     CLUSTEN_REQUIRE_PTR(feat, es);
     cudaStream_t s = (cudaStream_t)stream;
     if (tiled_sum_supported(dtype, attn, value, feat, n, m, c))
-        return launch_tiled_sum(dtype, attn, value, nbhd_idx, feat, b, h, n, m, s);
+        return launch_tiled_sum("av_forward", dtype, attn, value, nbhd_idx, feat, b, h, n, m, s);
     return launch_gather_sum("av_forward", dtype, attn, value, nbhd_idx, feat, b * h, h, n, n, m, 1, c, s);
 }
 
@@ -262,13 +262,13 @@ int clusten_av_backward(const void* d_feat, const void* attn, const void* value,
     const InverseView inv = inverse_view(inverse, b, n, m, n);
     // d_attn: dot of each gathered value row with the row's d_feat
     if (tiled_dot_supported(dtype, d_feat, value, d_attn, n, m, c))
-        st = launch_tiled_dot(dtype, value, d_feat, nbhd_idx, d_attn, b, h, n, m, s);
+        st = launch_tiled_dot("av_d_attn", dtype, value, d_feat, nbhd_idx, d_attn, b, h, n, m, s);
     else
         st = launch_gather_dot("av_d_attn", dtype, value, d_feat, nbhd_idx, d_attn, b * h, h, n, n, m, 1, c, s);
     if (st != CLUSTEN_OK) return st;
     // d_value: segmented reduction of attn * d_feat over the inverse index
     if (tiled_scatter_supported(dtype, attn, d_feat, d_value, n, m, c))
-        return launch_tiled_scatter(dtype, attn, d_feat, nbhd_idx, inv, d_value, b, h, n, m, s);
+        return launch_tiled_scatter("av_d_value", dtype, attn, d_feat, nbhd_idx, inv, d_value, b, h, n, m, s);
     return launch_scatter_sum("av_d_value", dtype, attn, d_feat, nbhd_idx, inv, d_value, b * h, h, n, n, m, 1, c, s);
 }
 

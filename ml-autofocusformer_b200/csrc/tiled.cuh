@@ -6,17 +6,17 @@ namespace clusten {
 
 // gather-sum:  out[b,h,i,:] = sum_j W[b,h,i,j] * X[b,h,idx[b,i,j],:]      (AV forward, d_query)
 bool tiled_sum_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c);
-int launch_tiled_sum(int dtype, const void* W, const void* X, const int64_t* idx, void* out, int b, int h, int n,
+int launch_tiled_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out, int b, int h, int n,
                      int m, cudaStream_t s);
 
 // gather-dot:  out[b,h,i,j] = <X[b,h,idx[b,i,j],:], Y[b,h,i,:]>           (QK forward, d_attn)
 bool tiled_dot_supported(int dtype, const void* Y, const void* X, const void* out, int n, int m, int c);
-int launch_tiled_dot(int dtype, const void* X, const void* Y, const int64_t* idx, void* out, int b, int h, int n,
+int launch_tiled_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out, int b, int h, int n,
                      int m, cudaStream_t s);
 
 // scatter-sum: out[b,h,t,:] = sum_{idx[b,i,j]==t} W[b,h,i,j] * X[b,h,i,:]   (d_key, d_value)
 bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c);
-int launch_tiled_scatter(int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
+int launch_tiled_scatter(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
                          void* out, int b, int h, int n, int m, cudaStream_t s);
 
 }  // namespace clusten
