@@ -1,4 +1,4 @@
-// Tiled CLUSTEN kernels for head_dim 32 (QK / AV, forward and backward).
+// Tiled scatter-side kernel for head_dim 32 (d_key, d_value); the gather side is in tiled_fwd.cu.
 //
 // A CTA takes a tile of 8 consecutive rows (one cluster of AutoFocusFormer) of one
 // batch element and all heads.  The neighbour indices of the tile are read once,
@@ -39,7 +39,6 @@ constexpr int kYLD = 36;       // row stride of the staged Y tile (floats)
 constexpr int kMaxWarps = 4;
 constexpr unsigned kFull = 0xffffffffu;
 constexpr unsigned short kSkip = 0xffffu;
-constexpr unsigned short kRowDup = 0x8000u;   // the neighbour occurs again later in the same row
 
 // ----------------------------------------------------------------------------- shared memory
 struct Smem {
@@ -192,72 +191,6 @@ __device__ int dedup_edges(Smem* sm, int E) {
     return sm->misc[0];
 }
 
-// Rows of a tile may name the same neighbour more than once.  The first occurrence keeps the
-// slot and is flagged kRowDup (its weight becomes the sum over the row's occurrences, taken in
-// column order); later occurrences are skipped.  cells: [kT][U] ints in the warp area.
-__device__ void mark_row_duplicates(Smem* sm, int E, int JC, int U) {
-    const int tid = threadIdx.x, nth = blockDim.x;
-    int* cells = reinterpret_cast<int*>(warp_area(sm, 0));
-    for (int x = tid; x < E; x += nth) {
-        const unsigned short s = sm->slot[x];
-        if (s != kSkip) cells[(x / JC) * U + s] = INT_MAX;
-    }
-    __syncthreads();
-    for (int x = tid; x < E; x += nth) {
-        const unsigned short s = sm->slot[x];
-        if (s != kSkip) atomicMin(&cells[(x / JC) * U + s], x);
-    }
-    __syncthreads();
-    for (int x = tid; x < E; x += nth) {
-        const unsigned short s = sm->slot[x];
-        if (s != kSkip && (cells[(x / JC) * U + s] & 0xffff) != x) {
-            atomicOr(&cells[(x / JC) * U + s], 0x10000);
-            sm->slot[x] = kSkip;
-        }
-    }
-    __syncthreads();
-    for (int x = tid; x < E; x += nth) {
-        const unsigned short s = sm->slot[x];
-        if (s != kSkip && (cells[(x / JC) * U + s] & 0x10000)) sm->slot[x] = s | kRowDup;
-    }
-    __syncthreads();
-}
-
-// Read the [rows x JC] block of nbhd_idx that starts at (i0, j0) into tok (row-major, JC wide) and
-// detect the case "all 8 rows identical".  Returns true in that case, with slot / uniq / misc[0] set.
-__device__ bool load_index_block(Smem* sm, const int64_t* __restrict__ idx_b, int n_rows, int n_src, int m,
-                                 int i0, int j0, int JC) {
-    const int tid = threadIdx.x, nth = blockDim.x;
-    const int E = kT * JC;
-    for (int x = tid; x < E; x += nth) {
-        const int q = x / JC, jj = x - q * JC;
-        int t = -1;
-        if (i0 + q < n_rows) {
-            const long long v = idx_b[(long long)(i0 + q) * m + j0 + jj];
-            if (v >= 0 && v < n_src) t = (int)v;
-        }
-        sm->tok[x] = t;
-    }
-    __syncthreads();
-    int same = 1;
-    for (int x = tid; x < E; x += nth) {
-        const int jj = x % JC;
-        const int t = sm->tok[x];
-        if (t != sm->tok[jj] || t < 0) same = 0;
-    }
-    same = __syncthreads_and(same);
-    if (same) {
-        for (int x = tid; x < E; x += nth) {
-            const int jj = x % JC;
-            sm->slot[x] = (unsigned short)jj;
-            if (x < JC) sm->uniq[x] = sm->tok[x];
-        }
-        if (tid == 0) sm->misc[0] = JC;
-        __syncthreads();
-    }
-    return same != 0;
-}
-
 // Stage rows uniq[u0 .. u0+rows4) of X (one head, [n_src][32]) into Xs, 16-byte chunks XOR-swizzled
 // by the row number; rows past U are zero-filled.  One warp.
 template <typename T>
@@ -292,209 +225,6 @@ __device__ __forceinline__ void sum_product(const float* __restrict__ Wd, const 
             const float4 x = *reinterpret_cast<const float4*>(Xs + r * kC + ((ci ^ (r & 7)) << 2));
             acc[0].x += wa[k] * x.x; acc[0].y += wa[k] * x.y; acc[0].z += wa[k] * x.z; acc[0].w += wa[k] * x.w;
             acc[1].x += wb[k] * x.x; acc[1].y += wb[k] * x.y; acc[1].z += wb[k] * x.z; acc[1].w += wb[k] * x.w;
-        }
-    }
-}
-
-// S[2qi+a][8k+ui] = <Ys[2qi+a][:], Xs[8k+ui][:]> for k < kmax, written to Sb (row stride kWLD)
-__device__ __forceinline__ void dot_product(const float* __restrict__ Ys, const float* __restrict__ Xs,
-                                            float* __restrict__ Sb, int kmax, int qi, int ui) {
-    float acc[2][kUC / 8];
-#pragma unroll
-    for (int k = 0; k < kUC / 8; ++k) acc[0][k] = acc[1][k] = 0.f;
-    const float* y0p = Ys + (2 * qi) * kYLD;
-    const float* y1p = y0p + kYLD;
-#pragma unroll
-    for (int c4 = 0; c4 < kC / 4; ++c4) {
-        const float4 y0 = *reinterpret_cast<const float4*>(y0p + c4 * 4);
-        const float4 y1 = *reinterpret_cast<const float4*>(y1p + c4 * 4);
-        const int off = (c4 ^ ui) << 2;
-#pragma unroll
-        for (int k = 0; k < kUC / 8; ++k) {
-            if (k < kmax) {
-                const float4 x = *reinterpret_cast<const float4*>(Xs + (8 * k + ui) * kC + off);
-                acc[0][k] += y0.x * x.x + y0.y * x.y + y0.z * x.z + y0.w * x.w;
-                acc[1][k] += y1.x * x.x + y1.y * x.y + y1.z * x.z + y1.w * x.w;
-            }
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < kUC / 8; ++k) {
-        if (k < kmax) {
-            Sb[(2 * qi) * kWLD + 8 * k + ui] = acc[0][k];
-            Sb[(2 * qi + 1) * kWLD + 8 * k + ui] = acc[1][k];
-        }
-    }
-}
-
-// ----------------------------------------------------------------------------- tiled_sum
-// out[bb, i, :] = sum_j W[bb, i, j] * X[bb, idx[b, i, j], :]
-template <typename T>
-__global__ void __launch_bounds__(32 * kMaxWarps)
-tiled_sum_kernel(const T* __restrict__ W, const T* __restrict__ X, const int64_t* __restrict__ idx,
-                 T* __restrict__ out, int heads, int n, int m, int tiles, int tiles_per_cta) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    Smem* sm = reinterpret_cast<Smem*>(smem_raw);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int qi = lane >> 3, ci = lane & 7;
-    float* Xs = warp_area(sm, warp);
-    float* Wd = Xs + kUC * kC;
-
-    const int groups = (tiles + tiles_per_cta - 1) / tiles_per_cta;
-    const int b = blockIdx.x / groups;
-    const int tile0 = (blockIdx.x - b * groups) * tiles_per_cta;
-    const int64_t* idx_b = idx + (long long)b * n * m;
-
-    for (int tile = tile0; tile < min(tile0 + tiles_per_cta, tiles); ++tile) {
-        const int i0 = tile * kT;
-        for (int j0 = 0; j0 < m; j0 += kEC / kT) {
-            const int JC = min(m - j0, kEC / kT);
-            const int E = kT * JC;
-            const bool first = j0 == 0;
-            const bool shared_rows = load_index_block(sm, idx_b, n, n, m, i0, j0, JC);
-            int U;
-            if (shared_rows) {
-                U = JC;
-            } else {
-                U = dedup_edges(sm, E);
-                if (U < E) mark_row_duplicates(sm, E, JC, U);   // U == E: every edge has its own slot
-            }
-            for (int g = warp; g < heads; g += nwarps) {
-                const long long bb = (long long)b * heads + g;
-                const T* Wh = W + (bb * n) * m;
-                const T* Xh = X + (bb * n) * kC;
-                // weights of this lane's edges (edge x = lane + 32 k)
-                float wreg[kEPL];
-#pragma unroll
-                for (int k = 0; k < kEPL; ++k) {
-                    const int x = lane + 32 * k;
-                    float w = 0.f;
-                    if (x < E) {
-                        const unsigned short s = sm->slot[x];
-                        if (s != kSkip) {
-                            const int q = x / JC, jj = x - q * JC;
-                            const T* wrow = Wh + (long long)(i0 + q) * m + j0;
-                            w = ld1(wrow + jj);
-                            if (s & kRowDup) {
-                                const int t = sm->tok[x];
-                                for (int j2 = jj + 1; j2 < JC; ++j2)
-                                    if (sm->tok[q * JC + j2] == t) w += ld1(wrow + j2);
-                            }
-                        }
-                    }
-                    wreg[k] = w;
-                }
-                float4 acc[2];
-                acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int u0 = 0; u0 < U; u0 += kUC) {
-                    const int Uc = min(kUC, U - u0);
-                    const int rows4 = (Uc + 3) & ~3;
-                    __syncwarp();
-                    stage_rows<T>(Xs, Xh, sm->uniq, u0, U, rows4, lane);
-                    for (int z = lane; z < kT * kWLD / 4; z += 32)
-                        reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    __syncwarp();
-#pragma unroll
-                    for (int k = 0; k < kEPL; ++k) {
-                        const int x = lane + 32 * k;
-                        if (x < E) {
-                            const unsigned short s = sm->slot[x];
-                            const int sl = (s & 0x7fff) - u0;
-                            if (s != kSkip && sl >= 0 && sl < Uc) Wd[(x / JC) * kWLD + sl] = wreg[k];
-                        }
-                    }
-                    __syncwarp();
-                    sum_product(Wd, Xs, rows4, qi, ci, acc);
-                }
-#pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    const int i = i0 + 2 * qi + a;
-                    if (i < n) {
-                        T* o = out + (bb * n + i) * kC + ci * 4;
-                        float4 v = acc[a];
-                        if (!first) {
-                            const float4 old = ld4(o);
-                            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                        }
-                        st4(o, v);
-                    }
-                }
-            }
-            __syncthreads();
-        }
-    }
-}
-
-// ----------------------------------------------------------------------------- tiled_dot
-// out[bb, i, j] = <X[bb, idx[b, i, j], :], Y[bb, i, :]>
-template <typename T>
-__global__ void __launch_bounds__(32 * kMaxWarps)
-tiled_dot_kernel(const T* __restrict__ X, const T* __restrict__ Y, const int64_t* __restrict__ idx,
-                 T* __restrict__ out, int heads, int n, int m, int tiles, int tiles_per_cta) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    Smem* sm = reinterpret_cast<Smem*>(smem_raw);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int qi = lane >> 3, ui = lane & 7;
-    float* Xs = warp_area(sm, warp);
-    float* Sb = Xs + kUC * kC;
-    float* Ys = Sb + kT * kWLD;
-
-    const int groups = (tiles + tiles_per_cta - 1) / tiles_per_cta;
-    const int b = blockIdx.x / groups;
-    const int tile0 = (blockIdx.x - b * groups) * tiles_per_cta;
-    const int64_t* idx_b = idx + (long long)b * n * m;
-
-    for (int tile = tile0; tile < min(tile0 + tiles_per_cta, tiles); ++tile) {
-        const int i0 = tile * kT;
-        for (int j0 = 0; j0 < m; j0 += kEC / kT) {
-            const int JC = min(m - j0, kEC / kT);
-            const int E = kT * JC;
-            const bool shared_rows = load_index_block(sm, idx_b, n, n, m, i0, j0, JC);
-            const int U = shared_rows ? JC : dedup_edges(sm, E);
-            for (int g = warp; g < heads; g += nwarps) {
-                const long long bb = (long long)b * heads + g;
-                const T* Xh = X + (bb * n) * kC;
-                const T* Yh = Y + (bb * n) * kC;
-                T* Oh = out + (bb * n) * m;
-                __syncwarp();
-                // Y tile: 8 rows x 32 channels, 64 chunks of 4
-#pragma unroll
-                for (int z = lane; z < kT * kC / 4; z += 32) {
-                    const int q = z >> 3, ch = z & 7;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (i0 + q < n) v = ld4(Yh + (long long)(i0 + q) * kC + ch * 4);
-                    *reinterpret_cast<float4*>(Ys + q * kYLD + ch * 4) = v;
-                }
-                float oreg[kEPL];
-#pragma unroll
-                for (int k = 0; k < kEPL; ++k) oreg[k] = 0.f;
-                for (int u0 = 0; u0 < U; u0 += kUC) {
-                    const int Uc = min(kUC, U - u0);
-                    __syncwarp();
-                    stage_rows<T>(Xs, Xh, sm->uniq, u0, U, (Uc + 3) & ~3, lane);
-                    __syncwarp();
-                    dot_product(Ys, Xs, Sb, (Uc + 7) >> 3, qi, ui);
-                    __syncwarp();
-#pragma unroll
-                    for (int k = 0; k < kEPL; ++k) {
-                        const int x = lane + 32 * k;
-                        if (x < E) {
-                            const unsigned short s = sm->slot[x];
-                            const int sl = (int)s - u0;
-                            if (s != kSkip && sl >= 0 && sl < Uc) oreg[k] = Sb[(x / JC) * kWLD + sl];
-                        }
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < kEPL; ++k) {
-                    const int x = lane + 32 * k;
-                    if (x < E) {
-                        const int q = x / JC, jj = x - q * JC;
-                        if (i0 + q < n) Oh[(long long)(i0 + q) * m + j0 + jj] = Elem<T>::down(oreg[k]);
-                    }
-                }
-            }
-            __syncthreads();
         }
     }
 }
@@ -650,32 +380,6 @@ int prepare(K kernel, size_t smem) {
 }
 
 template <typename T>
-int tiled_sum_t(const char* label, const void* W, const void* X, const int64_t* idx, void* out, int b, int h,
-                int n, int m, cudaStream_t s) {
-    const LaunchShape ls = launch_shape(b, h, n);
-    int st = prepare(tiled_sum_kernel<T>, ls.smem);
-    if (st != CLUSTEN_OK) return st;
-    ScopedKernelTimer timer(label, s);
-    tiled_sum_kernel<T><<<ls.grid, 32 * ls.warps, ls.smem, s>>>((const T*)W, (const T*)X, idx, (T*)out, h, n, m,
-                                                               ls.tiles, ls.tiles_per_cta);
-    note_launch();
-    return check_launch();
-}
-
-template <typename T>
-int tiled_dot_t(const char* label, const void* X, const void* Y, const int64_t* idx, void* out, int b, int h,
-                int n, int m, cudaStream_t s) {
-    const LaunchShape ls = launch_shape(b, h, n);
-    int st = prepare(tiled_dot_kernel<T>, ls.smem);
-    if (st != CLUSTEN_OK) return st;
-    ScopedKernelTimer timer(label, s);
-    tiled_dot_kernel<T><<<ls.grid, 32 * ls.warps, ls.smem, s>>>((const T*)X, (const T*)Y, idx, (T*)out, h, n, m,
-                                                               ls.tiles, ls.tiles_per_cta);
-    note_launch();
-    return check_launch();
-}
-
-template <typename T>
 int tiled_scatter_t(const char* label, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
                     void* out, int b, int h, int n, int m, cudaStream_t s) {
     const LaunchShape ls = launch_shape(b, h, n);
@@ -697,23 +401,6 @@ int tiled_scatter_t(const char* label, const void* W, const void* X, const int64
         case CLUSTEN_BF16: return FN<__nv_bfloat16>(__VA_ARGS__);                 \
         default: return CLUSTEN_ERR_DTYPE;                                        \
     }
-
-bool tiled_sum_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c) {
-    return common_supported(dtype, {X, out}, n, m, c) && reinterpret_cast<uintptr_t>(W) % 4 == 0;
-}
-int launch_tiled_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out,
-                     int b, int h, int n, int m, cudaStream_t s) {
-    CLUSTEN_TILED_DISPATCH(dtype, tiled_sum_t, label, W, X, idx, out, b, h, n, m, s)
-}
-
-bool tiled_dot_supported(int dtype, const void* Y, const void* X, const void* out, int n, int m, int c) {
-    (void)out;
-    return common_supported(dtype, {X, Y}, n, m, c);
-}
-int launch_tiled_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out,
-                     int b, int h, int n, int m, cudaStream_t s) {
-    CLUSTEN_TILED_DISPATCH(dtype, tiled_dot_t, label, X, Y, idx, out, b, h, n, m, s)
-}
 
 bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c) {
     (void)W;
