@@ -29,7 +29,8 @@ constexpr int kC = 32;           // channels per head
 constexpr int kMmax = 48;        // neighbours per row handled here
 constexpr int kE = kT * kMmax;   // edges per tile
 constexpr int kUC = 48;          // distinct neighbour rows staged at a time
-constexpr int kWLD = 52;         // row stride (floats) of the weight / score tile
+constexpr int kWLD = 52;         // row stride (floats) of the score tile
+constexpr int kWLD2 = 100;       // row stride (floats) of the weight tile, every weight stored twice
 constexpr int kYLD = 36;         // row stride (floats) of the staged Y tile
 constexpr int kRing = 3;         // index tiles in flight
 constexpr int kBMW = 256;        // bitmap words: token ids of a tile may span 8192
@@ -51,10 +52,15 @@ struct Smem {
     int warp_tot[kMaxWarps];
 };
 
-// per warp: two operand buffers {X rows, weight or Y tile} and one score tile
+// per warp: two buffers of neighbour rows, and
+//   tiled_sum: one weight tile [8][kWLD2] (each weight twice, for the two-wide FMA)
+//   tiled_dot: two Y tiles [8][kYLD] and one score tile [8][kWLD]
 constexpr int kXFloats = kUC * kC;                  // 1536
-constexpr int kOpFloats = kT * kWLD;                // 416 (>= kT * kYLD)
-__host__ __device__ constexpr int warp_floats(int mode) { return 2 * (kXFloats + kOpFloats) + (mode == 1 ? kT * kWLD : 0); }
+constexpr int kWFloats = kT * kWLD2;                // 800
+constexpr int kYFloats = kT * kYLD;                 // 288
+__host__ __device__ constexpr int warp_floats(int mode) {
+    return 2 * kXFloats + (mode == 0 ? kWFloats : 2 * kYFloats + kT * kWLD);
+}
 
 constexpr size_t kSmemHead = (sizeof(Smem) + 15) & ~size_t(15);
 inline size_t smem_bytes(int warps, int mode) {
@@ -109,25 +115,29 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
 }
 
 // ----------------------------------------------------------------------------- products
-// acc[a] += Wd[2qi+a][u] * Xs[u][4ci..], u < rows4 (multiple of 4); Xs chunks swizzled by row
-__device__ __forceinline__ void sum_product(const float* __restrict__ Wd, const float* __restrict__ Xs, int rows4,
-                                            int qi, int ci, float4 (&acc)[2]) {
-    const float* w0p = Wd + (2 * qi) * kWLD;
-    const float* w1p = w0p + kWLD;
-#pragma unroll 3
-    for (int u = 0; u < rows4; u += 4) {
-        const float4 w0 = *reinterpret_cast<const float4*>(w0p + u);
-        const float4 w1 = *reinterpret_cast<const float4*>(w1p + u);
-        const float wa[4] = {w0.x, w0.y, w0.z, w0.w};
-        const float wb[4] = {w1.x, w1.y, w1.z, w1.w};
+// acc[a] += Wd[2qi+a][u] * Xs[u][4ci..4ci+3] for u < rows8 (multiple of 8).  Wd holds every weight
+// twice (row stride kWLD2) so that one two-wide FMA updates a channel pair; Xs chunks are swizzled
+// by the row number, swz[k] = ((ci ^ k) << 2).
+__device__ __forceinline__ void sum_product(const float* __restrict__ Wd, const float* __restrict__ Xs, int rows8,
+                                            int qi, const int (&swz)[8], float2 (&acc)[2][2]) {
+    const float* w0p = Wd + (2 * qi) * kWLD2;
+    const float* w1p = w0p + kWLD2;
+    for (int u = 0; u < rows8; u += 8) {
+        const float* xr = Xs + u * kC;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int r = u + k;
-            const float4 x = *reinterpret_cast<const float4*>(Xs + r * kC + ((ci ^ (r & 7)) << 2));
-            acc[0].x = fmaf(wa[k], x.x, acc[0].x); acc[0].y = fmaf(wa[k], x.y, acc[0].y);
-            acc[0].z = fmaf(wa[k], x.z, acc[0].z); acc[0].w = fmaf(wa[k], x.w, acc[0].w);
-            acc[1].x = fmaf(wb[k], x.x, acc[1].x); acc[1].y = fmaf(wb[k], x.y, acc[1].y);
-            acc[1].z = fmaf(wb[k], x.z, acc[1].z); acc[1].w = fmaf(wb[k], x.w, acc[1].w);
+        for (int k = 0; k < 8; k += 2) {
+            const float4 wa = *reinterpret_cast<const float4*>(w0p + 2 * (u + k));   // {w_k, w_k, w_k+1, w_k+1}
+            const float4 wb = *reinterpret_cast<const float4*>(w1p + 2 * (u + k));
+            const float4 x0 = *reinterpret_cast<const float4*>(xr + k * kC + swz[k]);
+            const float4 x1 = *reinterpret_cast<const float4*>(xr + (k + 1) * kC + swz[k + 1]);
+            acc[0][0] = __ffma2_rn(make_float2(wa.x, wa.y), make_float2(x0.x, x0.y), acc[0][0]);
+            acc[0][1] = __ffma2_rn(make_float2(wa.x, wa.y), make_float2(x0.z, x0.w), acc[0][1]);
+            acc[1][0] = __ffma2_rn(make_float2(wb.x, wb.y), make_float2(x0.x, x0.y), acc[1][0]);
+            acc[1][1] = __ffma2_rn(make_float2(wb.x, wb.y), make_float2(x0.z, x0.w), acc[1][1]);
+            acc[0][0] = __ffma2_rn(make_float2(wa.z, wa.w), make_float2(x1.x, x1.y), acc[0][0]);
+            acc[0][1] = __ffma2_rn(make_float2(wa.z, wa.w), make_float2(x1.z, x1.w), acc[0][1]);
+            acc[1][0] = __ffma2_rn(make_float2(wb.z, wb.w), make_float2(x1.x, x1.y), acc[1][0]);
+            acc[1][1] = __ffma2_rn(make_float2(wb.z, wb.w), make_float2(x1.z, x1.w), acc[1][1]);
         }
     }
 }
@@ -328,9 +338,12 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
     const int lane = tid & 31, warp = tid >> 5, nwarps = nth >> 5;
     const int qi = lane >> 3, ci = lane & 7;
     float* wbase = reinterpret_cast<float*>(smem_raw + kSmemHead) + size_t(warp) * warp_floats(MODE);
-    float* Xbuf[2] = {wbase, wbase + kXFloats + kOpFloats};
-    float* Obuf[2] = {wbase + kXFloats, wbase + 2 * kXFloats + kOpFloats};
-    float* Sb = wbase + 2 * (kXFloats + kOpFloats);
+    float* const Xb0 = wbase;
+    float* const Xb1 = wbase + kXFloats;
+    float* const Wd = wbase + 2 * kXFloats;                 // MODE 0: weight tile
+    float* const Yb0 = wbase + 2 * kXFloats;                // MODE 1: Y tiles and score tile
+    float* const Yb1 = Yb0 + kYFloats;
+    float* const Sb = Yb1 + kYFloats;
     constexpr bool kAsync = std::is_same<T, float>::value;
 
     const int groups = (tiles + tiles_per_cta - 1) / tiles_per_cta;
@@ -340,72 +353,93 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
     const int64_t* idx_b = idx + (long long)b * n * m;
     const int E = kT * m;
     const int m4 = m >> 2;
-    const bool vec_ok = (m & 3) == 0;          // weight rows can be moved in 16-byte pieces
+    const bool vec_ok = (m & 7) == 0;          // rows move in 16-byte pieces and the product runs 8 neighbours at a time
+    const bool idx16 = (E & 1) == 0 && (reinterpret_cast<uintptr_t>(idx_b) & 15) == 0;
 
-    // per-lane constants: edge x = lane + 32k -> (row, column); weight chunk z = lane + 32k -> (row, chunk)
-    unsigned char eq[kEPL], ej[kEPL];
+    int swz[8];
 #pragma unroll
-    for (int k = 0; k < kEPL; ++k) {
-        const int x = lane + 32 * k;
-        eq[k] = (unsigned char)(x / m);
-        ej[k] = (unsigned char)(x - (x / m) * m);
-    }
-    unsigned char wq[3], wc[3];
+    for (int k = 0; k < 8; ++k) swz[k] = (ci ^ k) << 2;
+    const int sw_even = (ci ^ qi) << 2, sw_odd = sw_even ^ 16;   // swizzle of row qi + 4k, k even / odd
+    // weight / score chunk z = lane + 32k of a tile -> (row, 16-byte chunk)
+    int wq[3], wc[3];
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
         const int z = lane + 32 * k;
         const int d = m4 > 0 ? m4 : 1;
-        wq[k] = (unsigned char)(z / d);
-        wc[k] = (unsigned char)(z - (z / d) * d);
+        wq[k] = z / d;
+        wc[k] = z - wq[k] * d;
     }
+    const int col0 = (2 * tid) % m, col_step = (2 * nth) % m;   // column of entry pair 2 * (tid + k * nth)
 
-    const int col0 = tid % m, col_step = nth % m;   // column of edge x = tid + k * nth, without a division
-
-    auto issue_index = [&](int tile) {          // all threads: raw indices of `tile` -> ring
+    // ---- raw indices of `tile` -> ring (all threads; always commits one group)
+    auto issue_index = [&](int tile) {
         if (tile < tile_end) {
             long long* dst = sm->ring[tile % kRing];
-            const int64_t* src = idx_b + (long long)tile * kT * m;
-            const int valid = min(kT, n - tile * kT) * m;
-            for (int x = tid; x < E; x += nth) {
-                if (x < valid) cp_async8_ca(dst + x, src + x);
-                else dst[x] = -1;
+            const int64_t* src = idx_b + (long long)tile * E;
+            if (tile * kT + kT <= n && idx16) {
+                for (int x = 2 * tid; x < E; x += 2 * nth) cp_async16_ca(dst + x, src + x);
+            } else {
+                const int valid = min(kT, n - tile * kT) * m;
+                for (int x = tid; x < E; x += nth) {
+                    if (x < valid) cp_async8_ca(dst + x, src + x);
+                    else dst[x] = -1;
+                }
             }
         }
         cp_async_commit();
     };
 
-    // operands of (tile, head g) when the tile's rows are identical: X rows by column, A tile verbatim
-    auto issue_operands = [&](int tile, int g, int buf) {
-        const long long* row0 = sm->ring[tile % kRing];
-        const long long bb = (long long)b * heads + g;
-        const T* Xh = X + (bb * n) * kC;
-        float* Xs = Xbuf[buf];
-        float* Os = Obuf[buf];
-        const int i0 = tile * kT;
-        if constexpr (kAsync) {
-#pragma unroll
-            for (int k = 0; k < kUC / 4; ++k) {
-                const int r = qi + 4 * k;
-                if (r < m) {
-                    const int t = (int)row0[r];
-                    cp_async16_ca(Xs + r * kC + ((ci ^ (r & 7)) << 2), Xh + (long long)t * kC + ci * 4);
-                }
-            }
-            if (MODE == 0) {
-                const T* Wt = A + (bb * n + i0) * m;
-#pragma unroll
-                for (int k = 0; k < 3; ++k)
-                    if (lane + 32 * k < kT * m4)
-                        cp_async16_cg(Os + wq[k] * kWLD + wc[k] * 4, Wt + (int)wq[k] * m + wc[k] * 4);
-            } else {
-                const T* Yt = A + (bb * n + i0) * kC;
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const int z = lane + 32 * k;
-                    cp_async16_cg(Os + (z >> 3) * kYLD + (z & 7) * 4, Yt + z * 4);
-                }
-            }
+    // ---- are the 8 rows of `tile` identical, in range, and the tile complete?  (all threads)
+    auto rows_identical = [&](int tile) -> bool {
+        const int4* r = reinterpret_cast<const int4*>(sm->ring[tile % kRing]);   // {lo, hi, lo, hi}
+        int same = (tile * kT + kT <= n && vec_ok) ? 1 : 0;
+        int col = col0;
+        for (int x = tid; 2 * x < E; x += nth) {
+            const int4 v = r[x];
+            const int4 ref = r[col >> 1];
+            if (v.x != ref.x || v.z != ref.z || (v.y | v.w) != 0 || (unsigned)v.x >= (unsigned)n ||
+                (unsigned)v.z >= (unsigned)n)
+                same = 0;
+            col += col_step;
+            if (col >= m) col -= m;
         }
+        return __syncthreads_and(same) != 0;
+    };
+
+    // ---- neighbour rows of (tile, head g), identical-rows case: row r of the tile's first index row
+    auto issue_rows = [&](int tile, int g, float* Xs) {
+        const int* row0 = reinterpret_cast<const int*>(sm->ring[tile % kRing]);
+        const T* Xh = X + (((long long)b * heads + g) * n) * kC + ci * 4;
+        float* dst = Xs + qi * kC;
+#pragma unroll
+        for (int k = 0; k < kUC / 4; ++k) {
+            const int r = qi + 4 * k;
+            if (r < m) cp_async16_ca(dst + 4 * k * kC + ((k & 1) ? sw_odd : sw_even), Xh + (long long)row0[2 * r] * kC);
+        }
+    };
+    auto issue_y = [&](int tile, int g, float* Ys) {
+        const T* Yt = A + (((long long)b * heads + g) * n + tile * kT) * kC;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int z = lane + 32 * k;
+            cp_async16_cg(Ys + (z >> 3) * kYLD + (z & 7) * 4, Yt + z * 4);
+        }
+    };
+    // weight tile: global -> registers (early) -> shared, every weight twice (late)
+    auto load_w = [&](int tile, int g, float4 (&wr)[3]) {
+        const T* Wt = A + (((long long)b * heads + g) * n + tile * kT) * m;
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+            if (lane + 32 * k < kT * m4) wr[k] = ld4(Wt + wq[k] * m + wc[k] * 4);
+    };
+    auto store_w = [&](const float4 (&wr)[3]) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+            if (lane + 32 * k < kT * m4) {
+                float* d = Wd + wq[k] * kWLD2 + wc[k] * 8;
+                *reinterpret_cast<float4*>(d) = make_float4(wr[k].x, wr[k].x, wr[k].y, wr[k].y);
+                *reinterpret_cast<float4*>(d + 4) = make_float4(wr[k].z, wr[k].z, wr[k].w, wr[k].w);
+            }
     };
 
     // ------------------------------------------------------------------ prologue
@@ -413,23 +447,19 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
     issue_index(tile_begin + 1);
     cp_async_wait<1>();
     __syncthreads();
-    auto rows_identical = [&](int tile) -> bool {      // all threads; tile < tile_end
-        const long long* r = sm->ring[tile % kRing];
-        int same = (tile * kT + kT <= n && vec_ok) ? 1 : 0;
-        int col = col0;
-        for (int x = tid; x < E; x += nth) {
-            const long long v = r[x];
-            if (v != r[col] || v < 0 || v >= n) same = 0;
-            col += col_step;
-            if (col >= m) col -= m;
-        }
-        return __syncthreads_and(same) != 0;
-    };
-    bool cur_same = tile_begin < tile_end ? rows_identical(tile_begin) : false;
+    bool cur_same = rows_identical(tile_begin);
     int buf = 0;
-    bool have_prefetch = false;                        // operands of this warp's next task are in flight
-    if (cur_same && kAsync && warp < heads) {
-        issue_operands(tile_begin, warp, buf);
+    bool have_prefetch = false;            // operands of this warp's next task are under way
+    float4 wnext[3];
+    wnext[0] = wnext[1] = wnext[2] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (cur_same && kAsync) {
+        issue_rows(tile_begin, warp, Xb0);
+        if (MODE == 0) {
+            load_w(tile_begin, warp, wnext);
+            store_w(wnext);
+        } else {
+            issue_y(tile_begin, warp, Yb0);
+        }
         have_prefetch = true;
     }
     cp_async_commit();
@@ -438,11 +468,11 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         const int i0 = tile * kT;
         // ---- look ahead: indices of tile+2 start moving, tile+1 is classified
         issue_index(tile + 2);
-        cp_async_wait<1>();                            // everything but the newest group has landed
+        cp_async_wait<1>();                // everything but the newest group has landed
         __syncthreads();
         bool next_same = false;
         if (tile + 1 < tile_end) next_same = rows_identical(tile + 1);
-        if (lane * 16 < E && tile + 4 < tile_end && tid < 32) prefetch_l2(idx_b + (long long)(tile + 4) * kT * m + lane * 16);
+        if (tid * 16 < E && tile + 4 < tile_end) prefetch_l2(idx_b + (long long)(tile + 4) * E + tid * 16);
 
         int U = m;
         if (!cur_same) {
@@ -454,19 +484,24 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         for (int g = warp; g < heads; g += nwarps) {
             const long long bb = (long long)b * heads + g;
             const T* Xh = X + (bb * n) * kC;
-            float* Xs = Xbuf[buf];
-            float* Os = Obuf[buf];
-            // ---- operands of the task after this one
+            float* Xs = buf ? Xb1 : Xb0;
+            float* Xn = buf ? Xb0 : Xb1;
+            float* Ys = buf ? Yb1 : Yb0;
+            float* Yn = buf ? Yb0 : Yb1;
+            // ---- start moving the operands of the task after this one
             const bool had = have_prefetch;
             have_prefetch = false;
+            int nt = -1, ng = 0;
             if (kAsync) {
                 if (g + nwarps < heads) {
-                    if (cur_same) {
-                        issue_operands(tile, g + nwarps, buf ^ 1);
-                        have_prefetch = true;
-                    }
+                    if (cur_same) { nt = tile; ng = g + nwarps; }
                 } else if (next_same) {
-                    issue_operands(tile + 1, warp, buf ^ 1);
+                    nt = tile + 1; ng = warp;
+                }
+                if (nt >= 0) {
+                    issue_rows(nt, ng, Xn);
+                    if (MODE == 0) load_w(nt, ng, wnext);
+                    else issue_y(nt, ng, Yn);
                     have_prefetch = true;
                 }
             }
@@ -475,52 +510,65 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
             if (cur_same) {
                 // ================= identical rows: slot = column
                 if (kAsync) {
-                    if (!had) {                         // nothing was in flight for this task
-                        issue_operands(tile, g, buf);
+                    if (!had) {                         // nothing was under way for this task
+                        float4 wnow[3];
+                        issue_rows(tile, g, Xs);
+                        if (MODE == 0) {
+                            load_w(tile, g, wnow);
+                            __syncwarp();
+                            store_w(wnow);
+                        } else {
+                            issue_y(tile, g, Ys);
+                        }
                         cp_async_commit();
                         cp_async_wait<0>();
                     } else if (first_task) {
-                        cp_async_wait<2>();             // pending: indices two tiles ahead, next task's operands
+                        cp_async_wait<2>();             // may still fly: indices two tiles ahead, next task's operands
                     } else {
                         cp_async_wait<1>();
                     }
                 } else {
                     __syncwarp();
-                    const long long* row0 = sm->ring[tile % kRing];
-#pragma unroll 4
-                    for (int r = qi; r < m; r += 4)
-                        st4(Xs + r * kC + ((ci ^ (r & 7)) << 2), ld4(Xh + (long long)row0[r] * kC + ci * 4));
-                    if (MODE == 0) {
-                        const T* Wt = A + (bb * n + i0) * m;
+                    const int* row0 = reinterpret_cast<const int*>(sm->ring[tile % kRing]);
 #pragma unroll
-                        for (int k = 0; k < 3; ++k)
-                            if (lane + 32 * k < kT * m4)
-                                st4(Os + wq[k] * kWLD + wc[k] * 4, ld4(Wt + (int)wq[k] * m + wc[k] * 4));
+                    for (int k = 0; k < kUC / 4; ++k) {
+                        const int r = qi + 4 * k;
+                        if (r < m)
+                            st4(Xs + r * kC + ((k & 1) ? sw_odd : sw_even),
+                                ld4(Xh + (long long)row0[2 * r] * kC + ci * 4));
+                    }
+                    if (MODE == 0) {
+                        float4 wnow[3];
+                        load_w(tile, g, wnow);
+                        store_w(wnow);
                     } else {
                         const T* Yt = A + (bb * n + i0) * kC;
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
                             const int z = lane + 32 * k;
-                            st4(Os + (z >> 3) * kYLD + (z & 7) * 4, ld4(Yt + z * 4));
+                            st4(Ys + (z >> 3) * kYLD + (z & 7) * 4, ld4(Yt + z * 4));
                         }
                     }
                 }
                 __syncwarp();
                 if (MODE == 0) {
-                    float4 acc[2];
-                    acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    sum_product(Os, Xs, m, qi, ci, acc);
+                    float2 acc[2][2];
+                    acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = make_float2(0.f, 0.f);
+                    sum_product(Wd, Xs, m, qi, swz, acc);
 #pragma unroll
                     for (int a = 0; a < 2; ++a)
-                        st4(out + (bb * n + i0 + 2 * qi + a) * kC + ci * 4, acc[a]);
+                        st4(out + (bb * n + i0 + 2 * qi + a) * kC + ci * 4,
+                            make_float4(acc[a][0].x, acc[a][0].y, acc[a][1].x, acc[a][1].y));
+                    __syncwarp();                              // the weight tile is free again
+                    if (have_prefetch) store_w(wnext);
                 } else {
-                    dot_product(Os, Xs, Sb, (m + 7) >> 3, qi, ci);
+                    dot_product(Ys, Xs, Sb, (m + 7) >> 3, qi, ci);
                     __syncwarp();
                     T* Ot = out + (bb * n + i0) * m;
 #pragma unroll
                     for (int k = 0; k < 3; ++k)
                         if (lane + 32 * k < kT * m4)
-                            st4(Ot + (int)wq[k] * m + wc[k] * 4, ld4(Sb + wq[k] * kWLD + wc[k] * 4));
+                            st4(Ot + wq[k] * m + wc[k] * 4, ld4(Sb + wq[k] * kWLD + wc[k] * 4));
                     __syncwarp();
                 }
             } else {
@@ -535,7 +583,7 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         if (x < E) {
                             const unsigned short s = sm->slot[x];
                             if (s != kSkip) {
-                                const int q = eq[k], jj = ej[k];
+                                const int q = x / m, jj = x - q * m;
                                 const T* wrow = Wh + (long long)(i0 + q) * m;
                                 w = Elem<T>::up(wrow[jj]);
                                 if (s & kRowDup) {
@@ -547,15 +595,15 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         }
                         wreg[k] = w;
                     }
-                    float4 acc[2];
-                    acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float2 acc[2][2];
+                    acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = make_float2(0.f, 0.f);
                     for (int u0 = 0; u0 < U; u0 += kUC) {
                         const int Uc = min(kUC, U - u0);
-                        const int rows4 = (Uc + 3) & ~3;
+                        const int rows8 = (Uc + 7) & ~7;
                         __syncwarp();
-                        stage_rows_sync<T>(Xs, Xh, sm->uniq, u0, U, rows4, lane);
-                        for (int z = lane; z < kT * kWLD / 4; z += 32)
-                            reinterpret_cast<float4*>(Os)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        stage_rows_sync<T>(Xs, Xh, sm->uniq, u0, U, rows8, lane);
+                        for (int z = lane; z < kWFloats / 4; z += 32)
+                            reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                         __syncwarp();
 #pragma unroll
                         for (int k = 0; k < kEPL; ++k) {
@@ -563,17 +611,23 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                             if (x < E) {
                                 const unsigned short s = sm->slot[x];
                                 const int sl = (s & 0x7fff) - u0;
-                                if (s != kSkip && sl >= 0 && sl < Uc) Os[eq[k] * kWLD + sl] = wreg[k];
+                                if (s != kSkip && sl >= 0 && sl < Uc)
+                                    *reinterpret_cast<float2*>(Wd + (x / m) * kWLD2 + 2 * sl) =
+                                        make_float2(wreg[k], wreg[k]);
                             }
                         }
                         __syncwarp();
-                        sum_product(Os, Xs, rows4, qi, ci, acc);
+                        sum_product(Wd, Xs, rows8, qi, swz, acc);
                     }
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
                         const int i = i0 + 2 * qi + a;
-                        if (i < n) st4(out + (bb * n + i) * kC + ci * 4, acc[a]);
+                        if (i < n)
+                            st4(out + (bb * n + i) * kC + ci * 4,
+                                make_float4(acc[a][0].x, acc[a][0].y, acc[a][1].x, acc[a][1].y));
                     }
+                    __syncwarp();
+                    if (have_prefetch) store_w(wnext);
                 } else {
                     const T* Yh = A + (bb * n) * kC;
                     T* Oh = out + (bb * n) * m;
@@ -584,7 +638,7 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         const int q = z >> 3;
                         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (i0 + q < n) v = ld4(Yh + (long long)(i0 + q) * kC + (z & 7) * 4);
-                        st4(Os + q * kYLD + (z & 7) * 4, v);
+                        st4(Ys + q * kYLD + (z & 7) * 4, v);
                     }
                     float oreg[kEPL];
 #pragma unroll
@@ -594,7 +648,7 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         __syncwarp();
                         stage_rows_sync<T>(Xs, Xh, sm->uniq, u0, U, (Uc + 3) & ~3, lane);
                         __syncwarp();
-                        dot_product(Os, Xs, Sb, (Uc + 7) >> 3, qi, ci);
+                        dot_product(Ys, Xs, Sb, (Uc + 7) >> 3, qi, ci);
                         __syncwarp();
 #pragma unroll
                         for (int k = 0; k < kEPL; ++k) {
@@ -602,15 +656,15 @@ tiled_gather_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                             if (x < E) {
                                 const unsigned short s = sm->slot[x];
                                 const int sl = (int)s - u0;
-                                if (s != kSkip && sl >= 0 && sl < Uc) oreg[k] = Sb[eq[k] * kWLD + sl];
+                                if (s != kSkip && sl >= 0 && sl < Uc) oreg[k] = Sb[(x / m) * kWLD + sl];
                             }
                         }
                     }
 #pragma unroll
                     for (int k = 0; k < kEPL; ++k) {
                         const int x = lane + 32 * k;
-                        if (x < E && i0 + eq[k] < n)
-                            Oh[(long long)(i0 + eq[k]) * m + ej[k]] = Elem<T>::down(oreg[k]);
+                        const int q = x / m;
+                        if (x < E && i0 + q < n) Oh[(long long)(i0 + q) * m + (x - q * m)] = Elem<T>::down(oreg[k]);
                     }
                 }
             }
