@@ -70,6 +70,13 @@ CLUSTEN_API int clusten_version(void);
 /* Number of kernels this library has launched in this process (all threads). */
 CLUSTEN_API unsigned long long clusten_launch_count(void);
 
+/* Device status word.  The pipelined kernels bound every wait on a shared-memory
+ * barrier; a wait that runs out sets bit 0 and the kernel returns early (its
+ * output is then incomplete).  This call synchronises with the device, stores
+ * the word in *status (0 = healthy) and clears it when clear != 0.
+ * No counterpart in the reference. */
+CLUSTEN_API int clusten_device_status(int* status, int clear);
+
 /* Per-kernel timing for benchmarks.  While enabled, every kernel launch of the
  * library is bracketed by two CUDA events recorded on the launch stream.
  * clusten_timing_collect synchronises those events, writes one line per kernel

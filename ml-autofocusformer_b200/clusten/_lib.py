@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libclusten_b200.so")
+# CLUSTEN_B200_LIB selects another build of the library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("CLUSTEN_B200_LIB") or os.path.join(_HERE, "libclusten_b200.so")
 
 F32, F16, BF16, F64 = 0, 1, 2, 3
 
@@ -18,6 +19,7 @@ SIGNATURES = {
     "clusten_status_string": (ctypes.c_char_p, [_i]),
     "clusten_version": (_i, []),
     "clusten_launch_count": (ctypes.c_ulonglong, []),
+    "clusten_device_status": (_i, [ctypes.POINTER(ctypes.c_int), _i]),
     "clusten_timing_enable": (_i, [_i]),
     "clusten_timing_collect": (_i, [ctypes.c_char_p, _sz]),
     "clusten_inverse_bytes": (_sz, [_i, _i, _i, _i]),
@@ -58,6 +60,13 @@ def check(status):
     if status != 0:
         msg = load().clusten_status_string(status).decode()
         raise RuntimeError(f"clusten: {msg} (status {status})")
+
+
+def device_status(clear=True):
+    """Device status word of the library (0 = healthy); synchronises with the device."""
+    v = ctypes.c_int(0)
+    check(load().clusten_device_status(ctypes.byref(v), 1 if clear else 0))
+    return v.value
 
 
 def timing_enable(on):

@@ -121,6 +121,11 @@ const char* clusten_status_string(int status) {
 
 int clusten_version(void) { return 100; }
 
+int clusten_device_status(int* status, int clear) {
+    if (status == nullptr) return CLUSTEN_ERR_NULL;
+    return read_device_status(status, clear != 0);
+}
+
 int clusten_timing_enable(int on) {
     g_timing.store(on ? 1 : 0, std::memory_order_relaxed);
     return CLUSTEN_OK;

@@ -111,6 +111,11 @@ inline int dtype_size(int dtype) {
     }
 }
 
+// ---------------------------------------------------------------- device status word
+// Bits a kernel ORs into the library's device status word when it has to give up.
+constexpr int kErrPipelineTimeout = 1;   // a bounded wait on a shared-memory barrier ran out
+int read_device_status(int* status, bool clear);   // tiled_fwd.cu; synchronises the device
+
 // ---------------------------------------------------------------- generic kernels (generic.cu)
 // out[bb, row, ic, :] = sum_j W[bb, row, j, ic] * X[bb, idx[bb / heads, row, j], :]
 int launch_gather_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out,
