@@ -37,7 +37,7 @@ constexpr int kMmax = 48;          // neighbours per row handled here
 constexpr int kE = kT * kMmax;     // edges per tile
 constexpr int kUC = 48;            // distinct neighbour rows per stage
 constexpr int kWLD = 52;           // row stride (floats) of the score tile
-constexpr int kWLD2 = 100;         // row stride (floats) of the weight tile, every weight stored twice
+constexpr int kOLD = 36;           // row stride (floats) of the output tile
 constexpr int kYLD = 36;           // row stride (floats) of the fp32 Y tile
 constexpr int kBMW = 256;          // bitmap words: token ids of a tile may span 8192
 constexpr int kWarps = 4;          // warps per CTA (independent of each other)
@@ -48,23 +48,28 @@ constexpr unsigned short kSkip = 0xffffu;
 // ----------------------------------------------------------------------------- shared memory (per warp)
 //   X    neighbour rows [48][32] fp32; its front doubles as landing area of the tile's int64 indices
 //   Xraw (16-bit inputs) the rows as loaded, converted to fp32 into X
-//   Op   tiled_sum: weight tile [8][kWLD2];  tiled_dot: Y tile [8][kYLD] + score tile [8][kWLD];
+//   Op   tiled_sum: weight tile [8][kWLD], later the output tile [8][kOLD];
+//        tiled_dot: Y tile [8][kYLD] + score tile [8][kWLD];
 //        doubles as bitmap scratch while a tile is de-duplicated
 //   lut  edge -> slot,  uniq  slot -> source row
 template <typename T, int MODE> struct WarpSmem {
     static constexpr bool kIsFloat = std::is_same<T, float>::value;
     static constexpr int kX = kUC * kC * 4;
     static constexpr int kXraw = kIsFloat ? 0 : kUC * kC * (int)sizeof(T);
-    static constexpr int kOp = MODE == 0 ? kT * kWLD2 * 4 : (kT * kYLD + kT * kWLD) * 4;
+    static constexpr int kOp = MODE == 0 ? kT * kWLD * 4 : (kT * kYLD + kT * kWLD) * 4;
     static constexpr int kLut = kE * 2;
     static constexpr int kTotal = kX + kXraw + kOp + 2 * kLut;
 };
-static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= (kT * kYLD + kT * kWLD) * 4, "bitmap scratch must fit in Op");
+static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= kT * kWLD * 4, "bitmap scratch must fit in Op");
+static_assert(kT * kOLD <= kT * kWLD, "output tile must fit in Op");
 
 // ----------------------------------------------------------------------------- PTX helpers
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16_ca(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async16_cg(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
 }
 __device__ __forceinline__ void cp_async8_ca(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_u32(dst)), "l"(src));
@@ -103,84 +108,205 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = r;
 }
 
-// ----------------------------------------------------------------------------- products
-// acc[a] += Wd[2qi+a][u] * Xs[u][4ci..4ci+3] for u < rows8 (multiple of 8).  Wd holds every weight
-// twice (row stride kWLD2) so that one two-wide FMA updates a channel pair; Xs chunks are swizzled
-// by the row number, swz[k] = ((ci ^ k) << 2).
-__device__ __forceinline__ void sum_product(const float* __restrict__ Wd, const float* __restrict__ Xs, int rows8,
-                                            int qi, const int (&swz)[8], float2 (&acc)[2][2]) {
-    const float* w0p = Wd + (2 * qi) * kWLD2;
-    const float* w1p = w0p + kWLD2;
-    for (int u = 0; u < rows8; u += 8) {
-        const float* xr = Xs + u * kC;
+// ----------------------------------------------------------------------------- products on the tensor cores
+// mma.sync m16n8k8 with TF32 operands and FP32 accumulation.  FP32 inputs are split into a high
+// part (upper 19 bits) and the exact remainder and multiplied in three passes (lo*hi, hi*lo,
+// hi*hi), which keeps the result within a few 1e-7 of an FP32 product; FP16 / BF16 inputs are
+// exactly representable in TF32, so one pass gives exact products.  Fragment layout (PTX ISA,
+// m16n8k8): g = lane / 4, t = lane % 4;  A: a0=(g,t) a1=(g+8,t) a2=(g,t+4) a3=(g+8,t+4);
+// B: b0=(t,g) b1=(t+4,g);  D: d0=(g,2t) d1=(g,2t+1) d2=(g+8,2t) d3=(g+8,2t+1).
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void split_tf32(float x, unsigned& hi, unsigned& lo) {
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
+}
+template <bool SPLIT, int NA>
+__device__ __forceinline__ void mma_block(float (&d)[4], const float (&a)[4], const float (&b)[2]) {
+    unsigned ah[4], bh[2];
+    if (SPLIT) {
+        unsigned al[4], bl[2];
 #pragma unroll
-        for (int k = 0; k < 8; k += 2) {
-            const float4 wa = *reinterpret_cast<const float4*>(w0p + 2 * (u + k));   // {w_k, w_k, w_k+1, w_k+1}
-            const float4 wb = *reinterpret_cast<const float4*>(w1p + 2 * (u + k));
-            const float4 x0 = *reinterpret_cast<const float4*>(xr + k * kC + swz[k]);
-            const float4 x1 = *reinterpret_cast<const float4*>(xr + (k + 1) * kC + swz[k + 1]);
-            acc[0][0] = __ffma2_rn(make_float2(wa.x, wa.y), make_float2(x0.x, x0.y), acc[0][0]);
-            acc[0][1] = __ffma2_rn(make_float2(wa.x, wa.y), make_float2(x0.z, x0.w), acc[0][1]);
-            acc[1][0] = __ffma2_rn(make_float2(wb.x, wb.y), make_float2(x0.x, x0.y), acc[1][0]);
-            acc[1][1] = __ffma2_rn(make_float2(wb.x, wb.y), make_float2(x0.z, x0.w), acc[1][1]);
-            acc[0][0] = __ffma2_rn(make_float2(wa.z, wa.w), make_float2(x1.x, x1.y), acc[0][0]);
-            acc[0][1] = __ffma2_rn(make_float2(wa.z, wa.w), make_float2(x1.z, x1.w), acc[0][1]);
-            acc[1][0] = __ffma2_rn(make_float2(wb.z, wb.w), make_float2(x1.x, x1.y), acc[1][0]);
-            acc[1][1] = __ffma2_rn(make_float2(wb.z, wb.w), make_float2(x1.z, x1.w), acc[1][1]);
+        for (int i = 0; i < 4; ++i) split_tf32(a[i], ah[i], al[i]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) split_tf32(b[i], bh[i], bl[i]);
+        mma_tf32(d, al, bh);
+        mma_tf32(d, ah, bl);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ah[i] = __float_as_uint(a[i]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) bh[i] = __float_as_uint(b[i]);
+    }
+    mma_tf32(d, ah, bh);
+}
+
+// Fragment loads use 32-bit shared-memory addresses that are fixed per warp (computed once per kernel)
+// plus compile-time offsets.
+// Per-warp addresses for tiled_sum:  D[c][q] += sum_u Xs[u][c] * Wd[q][u].
+// Xs rows are [32] floats with the 16-byte chunks of row r stored at chunk ^ ((r & 3) << 1); Wd has row
+// stride kWLD.  With g = lane / 4, t = lane % 4 the B fragment comes from Wd row g, column u0 + t (+4) and
+// the A fragment from staged row u0 + t (+4), channel 16 mt + 8 h + g.
+struct SumAddr {
+    unsigned w;          // &Wd[g][t]
+    unsigned x[2][2];    // &Xs[t][16 mt + 8 h + g] (swizzled for rows with (row & 3) == t)
+};
+__device__ __forceinline__ SumAddr make_sum_addr(const float* Wd, const float* Xs, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    SumAddr a;
+    a.w = smem_u32(Wd + g * kWLD + t);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c = 16 * mt + 8 * h + g;
+            a.x[mt][h] = smem_u32(Xs + t * kC + ((((c >> 2) ^ (t << 1)) << 2) + (c & 3)));
+        }
+    return a;
+}
+
+#define CLUSTEN_LDS(dst, addr, off) asm volatile("ld.shared.f32 %0, [%1+" #off "];\n" : "=f"(dst) : "r"(addr))
+
+template <int KS>
+__device__ __forceinline__ void sum_load(const SumAddr& sa, float (&b)[2], float (&a)[2][4]) {
+    // byte offsets: column / row u0 = 8 KS
+    asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(b[0]) : "r"(sa.w), "n"(KS * 8 * 4));
+    asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(b[1]) : "r"(sa.w), "n"((KS * 8 + 4) * 4));
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][0]) : "r"(sa.x[mt][0]), "n"(KS * 8 * kC * 4));
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][1]) : "r"(sa.x[mt][1]), "n"(KS * 8 * kC * 4));
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][2]) : "r"(sa.x[mt][0]), "n"((KS * 8 + 4) * kC * 4));
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][3]) : "r"(sa.x[mt][1]), "n"((KS * 8 + 4) * kC * 4));
+    }
+}
+
+template <bool SPLIT, int KS>
+__device__ __forceinline__ void sum_steps(const SumAddr& sa, int rows8, float (&acc)[2][4], float (&b)[2],
+                                          float (&a)[2][4]) {
+    // operands of step KS are in (a, b); fetch those of step KS + 1 before multiplying
+    if constexpr (KS < kUC / 8) {
+        if (KS * 8 < rows8) {
+            float bn[2], an[2][4];
+            if constexpr (KS + 1 < kUC / 8) {
+                if ((KS + 1) * 8 < rows8) sum_load<KS + 1>(sa, bn, an);
+            }
+            mma_block<SPLIT, 0>(acc[0], a[0], b);
+            mma_block<SPLIT, 0>(acc[1], a[1], b);
+            if constexpr (KS + 1 < kUC / 8) sum_steps<SPLIT, KS + 1>(sa, rows8, acc, bn, an);
         }
     }
 }
 
-// Sb[2qi+a][8k+ui] = <Ys[2qi+a][:], Xs[8k+ui][:]> for k < kmax; two-wide FMAs over channel pairs
-__device__ __forceinline__ void dot_product(const float* __restrict__ Ys, const float* __restrict__ Xs,
-                                            float* __restrict__ Sb, int kmax, int qi, int ui) {
-    constexpr int K = kUC / 8;
-    float2 acc[2][K];
+template <bool SPLIT>
+__device__ __forceinline__ void sum_product_mma(const SumAddr& sa, int rows8, float (&acc)[2][4]) {
+    if (rows8 > 0) {
+        float b[2], a[2][4];
+        sum_load<0>(sa, b, a);
+        sum_steps<SPLIT, 0>(sa, rows8, acc, b, a);
+    }
+}
+
+// Per-warp addresses for tiled_dot:  Sb[q][u] = sum_c Xs[u][c] * Ys[q][c].
+// Xs chunks of row r are stored at chunk ^ (r & 7); Ys has row stride kYLD; Sb row stride kWLD.
+// A fragment: staged rows 16 mt + g (+8), channels k0 + t (+4);  B fragment: Ys row g, channels k0 + t (+4).
+struct DotAddr {
+    unsigned y;          // &Ys[g][t]
+    unsigned x[8];       // &Xs[g][chunk c4 (swizzled with row & 7 == g)] + t
+    unsigned s;          // &Sb[2 t][g]
+};
+__device__ __forceinline__ DotAddr make_dot_addr(const float* Ys, const float* Xs, const float* Sb, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    DotAddr a;
+    a.y = smem_u32(Ys + g * kYLD + t);
 #pragma unroll
-    for (int k = 0; k < K; ++k) acc[0][k] = acc[1][k] = make_float2(0.f, 0.f);
-    const float* y0p = Ys + (2 * qi) * kYLD;
-    const float* y1p = y0p + kYLD;
-#pragma unroll 2
-    for (int c4 = 0; c4 < kC / 4; ++c4) {
-        const float4 y0 = *reinterpret_cast<const float4*>(y0p + c4 * 4);
-        const float4 y1 = *reinterpret_cast<const float4*>(y1p + c4 * 4);
-        const int off = (c4 ^ ui) << 2;
+    for (int c4 = 0; c4 < 8; ++c4) a.x[c4] = smem_u32(Xs + g * kC + ((c4 ^ g) << 2) + t);
+    a.s = smem_u32(Sb + (2 * t) * kWLD + g);
+    return a;
+}
+
+template <bool SPLIT>
+__device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
+    float acc[kUC / 16][4];
 #pragma unroll
-        for (int k = 0; k < K; ++k) {
-            if (k < kmax) {
-                const float4 x = *reinterpret_cast<const float4*>(Xs + (8 * k + ui) * kC + off);
-                acc[0][k] = __ffma2_rn(make_float2(y0.x, y0.y), make_float2(x.x, x.y), acc[0][k]);
-                acc[0][k] = __ffma2_rn(make_float2(y0.z, y0.w), make_float2(x.z, x.w), acc[0][k]);
-                acc[1][k] = __ffma2_rn(make_float2(y1.x, y1.y), make_float2(x.x, x.y), acc[1][k]);
-                acc[1][k] = __ffma2_rn(make_float2(y1.z, y1.w), make_float2(x.z, x.w), acc[1][k]);
+    for (int mt = 0; mt < kUC / 16; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < kC / 8; ++ks) {
+        // channels 8 ks + t and 8 ks + 4 + t
+        float bb[2];
+        if (ks == 0) { CLUSTEN_LDS(bb[0], da.y, 0); CLUSTEN_LDS(bb[1], da.y, 16); }
+        if (ks == 1) { CLUSTEN_LDS(bb[0], da.y, 32); CLUSTEN_LDS(bb[1], da.y, 48); }
+        if (ks == 2) { CLUSTEN_LDS(bb[0], da.y, 64); CLUSTEN_LDS(bb[1], da.y, 80); }
+        if (ks == 3) { CLUSTEN_LDS(bb[0], da.y, 96); CLUSTEN_LDS(bb[1], da.y, 112); }
+#pragma unroll
+        for (int mt = 0; mt < kUC / 16; ++mt) {
+            if (mt < mtiles) {
+                float a[4];
+                // rows 16 mt + g and + 8: byte offsets 16 mt * 128 and + 8 * 128
+                if (mt == 0) {
+                    CLUSTEN_LDS(a[0], da.x[2 * ks], 0);     CLUSTEN_LDS(a[1], da.x[2 * ks], 1024);
+                    CLUSTEN_LDS(a[2], da.x[2 * ks + 1], 0); CLUSTEN_LDS(a[3], da.x[2 * ks + 1], 1024);
+                } else if (mt == 1) {
+                    CLUSTEN_LDS(a[0], da.x[2 * ks], 2048);     CLUSTEN_LDS(a[1], da.x[2 * ks], 3072);
+                    CLUSTEN_LDS(a[2], da.x[2 * ks + 1], 2048); CLUSTEN_LDS(a[3], da.x[2 * ks + 1], 3072);
+                } else {
+                    CLUSTEN_LDS(a[0], da.x[2 * ks], 4096);     CLUSTEN_LDS(a[1], da.x[2 * ks], 5120);
+                    CLUSTEN_LDS(a[2], da.x[2 * ks + 1], 4096); CLUSTEN_LDS(a[3], da.x[2 * ks + 1], 5120);
+                }
+                mma_block<SPLIT, 0>(acc[mt], a, bb);
             }
         }
     }
+    // D fragment -> Sb[q][u]: d0=(u=16mt+g, q=2t) d1=(u, 2t+1) d2=(u+8, 2t) d3=(u+8, 2t+1)
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-        if (k < kmax) {
-            Sb[(2 * qi) * kWLD + 8 * k + ui] = acc[0][k].x + acc[0][k].y;
-            Sb[(2 * qi + 1) * kWLD + 8 * k + ui] = acc[1][k].x + acc[1][k].y;
+    for (int mt = 0; mt < kUC / 16; ++mt) {
+        if (mt < mtiles) {
+            if (mt == 0) {
+                asm volatile("st.shared.f32 [%0+0], %1;\n" ::"r"(da.s), "f"(acc[0][0]));
+                asm volatile("st.shared.f32 [%0+208], %1;\n" ::"r"(da.s), "f"(acc[0][1]));
+                asm volatile("st.shared.f32 [%0+32], %1;\n" ::"r"(da.s), "f"(acc[0][2]));
+                asm volatile("st.shared.f32 [%0+240], %1;\n" ::"r"(da.s), "f"(acc[0][3]));
+            } else if (mt == 1) {
+                asm volatile("st.shared.f32 [%0+64], %1;\n" ::"r"(da.s), "f"(acc[1][0]));
+                asm volatile("st.shared.f32 [%0+272], %1;\n" ::"r"(da.s), "f"(acc[1][1]));
+                asm volatile("st.shared.f32 [%0+96], %1;\n" ::"r"(da.s), "f"(acc[1][2]));
+                asm volatile("st.shared.f32 [%0+304], %1;\n" ::"r"(da.s), "f"(acc[1][3]));
+            } else {
+                asm volatile("st.shared.f32 [%0+128], %1;\n" ::"r"(da.s), "f"(acc[2][0]));
+                asm volatile("st.shared.f32 [%0+336], %1;\n" ::"r"(da.s), "f"(acc[2][1]));
+                asm volatile("st.shared.f32 [%0+160], %1;\n" ::"r"(da.s), "f"(acc[2][2]));
+                asm volatile("st.shared.f32 [%0+368], %1;\n" ::"r"(da.s), "f"(acc[2][3]));
+            }
         }
     }
 }
+static_assert(kWLD * 4 == 208 && kC * 4 == 128 && kUC == 48, "byte offsets above are written out for these sizes");
 
 // ----------------------------------------------------------------------------- producer: tile analysis
 // Are the 8 rows of the tile identical, in range, and the tile complete?  One warp.
+// col0 = (2 * lane) % m and col_step = 64 % m are the column of the lane's first entry pair and its
+// advance per pass (computed once per kernel).
 __device__ __forceinline__ bool rows_identical(const long long* ring, int E, int m, int n, bool complete,
-                                               int lane) {
-    const int4* r = reinterpret_cast<const int4*>(ring);      // {lo, hi, lo, hi} of two entries
+                                               int lane, int col0, int col_step) {
+    const int4* r = reinterpret_cast<const int4*>(ring) + lane;      // {lo, hi, lo, hi} of two entries
+    const int4* r0 = reinterpret_cast<const int4*>(ring);
     bool same = complete && (m & 7) == 0;
-    int col = (2 * lane) % m;
-    const int col_step = 64 % m;
-    for (int x = lane; 2 * x < E; x += 32) {
-        const int4 v = r[x];
-        const int4 ref = r[col >> 1];
-        if (v.x != ref.x || v.z != ref.z || (v.y | v.w) != 0 || (unsigned)v.x >= (unsigned)n ||
-            (unsigned)v.z >= (unsigned)n)
-            same = false;
-        col += col_step;
-        if (col >= m) col -= m;
+    int col = col0;
+#pragma unroll
+    for (int k = 0; k < kE / 64; ++k) {
+        if (2 * (lane + 32 * k) < E) {
+            const int4 v = r[32 * k];
+            const int4 ref = r0[col >> 1];
+            if (v.x != ref.x || v.z != ref.z || (v.y | v.w) != 0 || (unsigned)v.x >= (unsigned)n ||
+                (unsigned)v.z >= (unsigned)n)
+                same = false;
+            col += col_step;
+            if (col >= m) col -= m;
+        }
     }
     return __all_sync(kFull, same);
 }
@@ -317,12 +443,16 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
 
+    int* tok_s = reinterpret_cast<int*>(uniq);                        // identical rows: source row of X row r
+    const SumAddr sa = make_sum_addr(Wd, Xs, lane);                   // MODE 0
+    const DotAddr da = make_dot_addr(Ys, Xs, Sb, lane);               // MODE 1
+
     const int E = kT * m;
     const int m4 = m >> 2;
-    int swz[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) swz[k] = (ci ^ k) << 2;
-    const int sw_even = (ci ^ qi) << 2, sw_odd = sw_even ^ 16;   // swizzle of row qi + 4k, k even / odd
+    // word offset of 16-byte chunk ci inside staged row r = qi + 4k (k even / odd):
+    // tiled_sum stores chunk ^ ((r & 3) << 1), tiled_dot chunk ^ (r & 7), see the product routines
+    const int sw_even = MODE == 0 ? ((ci ^ (qi << 1)) << 2) : ((ci ^ qi) << 2);
+    const int sw_odd = MODE == 0 ? sw_even : (sw_even ^ 16);
     // piece z = lane + 32k of a [8][m] tile -> (row, 4-element piece); edge x = lane + 32k -> its row
     int wq[3], wc[3];
 #pragma unroll
@@ -332,24 +462,27 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         wq[k] = z / d;
         wc[k] = z - wq[k] * d;
     }
+    const int col0 = (2 * lane) % m, col_step = 64 % m;
     unsigned long long qpack = 0ull;                    // 3 bits per edge: its row
 #pragma unroll
     for (int k = 0; k < kEPL; ++k) qpack |= (unsigned long long)(((lane + 32 * k) / m) & 7) << (3 * k);
 
-    const long long total = (long long)batch * tiles;
-    const long long nwarps = (long long)gridDim.x * kWarps;
-    for (long long task = (long long)blockIdx.x * kWarps + warp; task < total; task += nwarps) {
-        const int b = (int)(task / tiles);
-        const int tile = (int)(task - (long long)b * tiles);
+    const unsigned total = (unsigned)batch * (unsigned)tiles;       // < 2^31, checked by the launcher
+    const unsigned nwarps = gridDim.x * kWarps;
+    const unsigned task0 = blockIdx.x * kWarps + warp;
+    int b = (int)(task0 / (unsigned)tiles);
+    int tile = (int)(task0 - (unsigned)b * (unsigned)tiles);
+    const int step_b = (int)(nwarps / (unsigned)tiles), step_t = (int)(nwarps % (unsigned)tiles);
+    int nb = b + step_b, ntile = tile + step_t;                      // this warp's next (batch, tile)
+    if (ntile >= tiles) { ntile -= tiles; ++nb; }
+    for (unsigned task = task0; task < total; task += nwarps) {
         const int i0 = tile * kT;
         const bool complete = i0 + kT <= n;
         const int64_t* src = idx + ((long long)b * n + i0) * m;
         // ---- warm the L2 for this warp's next tile: its index rows and its weight / Y rows
         {
-            const long long nx = task + nwarps;
-            if (nx < total) {
-                const int nb = (int)(nx / tiles);
-                const int ni0 = (int)(nx - (long long)nb * tiles) * kT;
+            if (nb < batch) {
+                const int ni0 = ntile * kT;
                 if (lane * 16 < E) prefetch_l2(idx + ((long long)nb * n + ni0) * m + lane * 16);
                 const int arow = MODE == 0 ? m : kC;               // elements per row of A
                 const int abytes = kT * arow * (int)sizeof(T);
@@ -373,19 +506,12 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         cp_async_commit();
         cp_async_wait<0>();
         __syncwarp();
-        const bool identical = rows_identical(ring, E, m, n, complete, lane);
+        const bool identical = rows_identical(ring, E, m, n, complete, lane, col0, col_step);
         int U = m;
         bool rowdup = false;
-        constexpr int kRowsPerPass = kIsFloat ? 4 : 8;   // 8 (4) lanes fetch one fp32 (16-bit) row
-        const int prow = kIsFloat ? qi : (lane >> 2);
-        int tok_reg[kUC / kRowsPerPass];                 // identical rows: source row of X row prow + kRowsPerPass * k
         if (identical) {
             const int* ring32 = reinterpret_cast<const int*>(ring);
-#pragma unroll
-            for (int k = 0; k < kUC / kRowsPerPass; ++k) {
-                const int r = prow + kRowsPerPass * k;
-                tok_reg[k] = r < m ? ring32[2 * r] : 0;
-            }
+            for (int r = lane; r < m; r += 32) tok_s[r] = ring32[2 * r];
         } else {
             U = dedup_tile(ds, ring, lut, E, m, i0, n, MODE == 0, &rowdup, lane);
         }
@@ -394,8 +520,9 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         for (int g = 0; g < heads; ++g) {
             const long long bb = (long long)b * heads + g;
             const T* Xh = X + (bb * n) * kC;
-            float2 acc[2][2];
-            acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = make_float2(0.f, 0.f);
+            float acc[2][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
             float oreg[kEPL];
 #pragma unroll
             for (int k = 0; k < kEPL; ++k) oreg[k] = 0.f;
@@ -406,21 +533,28 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                 const int rows8 = (Uc + 7) & ~7;
                 __syncwarp();
                 // ---- neighbour rows: 8 lanes x 16 bytes per fp32 row (4 lanes per 16-bit row)
-                if (kIsFloat) {
+                if (kIsFloat && identical) {
+                    const T* Xl = Xh + ci * 4;
+                    float* dst = Xs + qi * kC;
+#pragma unroll
+                    for (int k = 0; k < kUC / 4; ++k)
+                        if (qi + 4 * k < m)
+                            cp_async16_cg(dst + 4 * k * kC + ((k & 1) ? sw_odd : sw_even), Xl + (long long)tok_s[qi + 4 * k] * kC);
+                } else if (kIsFloat) {
 #pragma unroll
                     for (int k = 0; k < kUC / 4; ++k) {
                         const int r = qi + 4 * k;
                         if (r < rows8) {
                             int t = -1;
                             if (r < Uc) {
-                                if (identical) t = tok_reg[k];
+                                if (identical) t = tok_s[r];
                                 else {
                                     const unsigned short tt = uniq[u0 + r];
                                     t = tt == kSkip ? -1 : (int)tt;
                                 }
                             }
                             float* dst = Xs + r * kC + ((k & 1) ? sw_odd : sw_even);
-                            if (t >= 0) cp_async16_ca(dst, Xh + (long long)t * kC + ci * 4);
+                            if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * kC + ci * 4);
                             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
@@ -432,34 +566,31 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         if (r < rows8) {
                             int t = -1;
                             if (r < Uc) {
-                                if (identical) t = tok_reg[k];
+                                if (identical) t = tok_s[r];
                                 else {
                                     const unsigned short tt = uniq[u0 + r];
                                     t = tt == kSkip ? -1 : (int)tt;
                                 }
                             }
                             T* dst = Xraw + r * kC + pc * kPer;
-                            if (t >= 0) cp_async16_ca(dst, Xh + (long long)t * kC + pc * kPer);
+                            if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * kC + pc * kPer);
                             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
                 }
-                cp_async_commit();
-
                 if (MODE == 0) {
-                    // ---- weight tile -> Wd, every weight twice, while the rows are on their way
+                    // ---- weight tile -> Wd while the rows are on their way
                     const T* Wt = A + (bb * n + i0) * m;
                     if (identical) {
 #pragma unroll
                         for (int k = 0; k < 3; ++k)
                             if (lane + 32 * k < kT * m4) {
-                                const float4 w = ld4(Wt + wq[k] * m + wc[k] * 4);
-                                float* dd = Wd + wq[k] * kWLD2 + wc[k] * 8;
-                                *reinterpret_cast<float4*>(dd) = make_float4(w.x, w.x, w.y, w.y);
-                                *reinterpret_cast<float4*>(dd + 4) = make_float4(w.z, w.z, w.w, w.w);
+                                float* dd = Wd + wq[k] * kWLD + wc[k] * 4;
+                                if (kIsFloat) cp_async16_ca(dd, Wt + wq[k] * m + wc[k] * 4);
+                                else *reinterpret_cast<float4*>(dd) = ld4(Wt + wq[k] * m + wc[k] * 4);
                             }
                     } else {
-                        for (int z = lane; z < kT * kWLD2 / 4; z += 32)
+                        for (int z = lane; z < kT * kWLD / 4; z += 32)
                             reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                         __syncwarp();
                         if (!rowdup) {
@@ -472,7 +603,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                     if (sl != kSkip && rel >= 0 && rel < Uc) {
                                         const float w = Elem<T>::up(Wt[x]);
                                         const int q = (int)((qpack >> (3 * k)) & 7ull);
-                                        *reinterpret_cast<float2*>(Wd + q * kWLD2 + 2 * rel) = make_float2(w, w);
+                                        Wd[q * kWLD + rel] = w;
                                     }
                                 }
                             }
@@ -482,9 +613,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                 const unsigned short sl = lut[lane * m + j];
                                 const int rel = (int)sl - u0;
                                 if (sl != kSkip && rel >= 0 && rel < Uc) {
-                                    float2* cell = reinterpret_cast<float2*>(Wd + lane * kWLD2 + 2 * rel);
-                                    const float w = cell->x + Elem<T>::up(Wt[lane * m + j]);
-                                    *cell = make_float2(w, w);
+                                    Wd[lane * kWLD + rel] += Elem<T>::up(Wt[lane * m + j]);
                                 }
                             }
                         }
@@ -500,6 +629,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         *reinterpret_cast<float4*>(Ys + (z >> 3) * kYLD + (z & 7) * 4) = v;
                     }
                 }
+                cp_async_commit();
                 cp_async_wait<0>();
                 __syncwarp();
                 if (!kIsFloat) {
@@ -513,9 +643,9 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                 }
 
                 if (MODE == 0) {
-                    sum_product(Wd, Xs, rows8, qi, swz, acc);
+                    sum_product_mma<kIsFloat>(sa, rows8, acc);
                 } else {
-                    dot_product(Ys, Xs, Sb, (Uc + 7) >> 3, qi, ci);
+                    dot_product_mma<kIsFloat>(da, (Uc + 15) >> 4);
                     __syncwarp();
                     T* Ot = out + (bb * n + i0) * m;
                     if (identical) {
@@ -546,14 +676,36 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                 }
             }
             if (MODE == 0) {
+                // D fragments -> output tile [8][kOLD] in shared memory -> 16-byte stores
+                float* Ot = Op;
+                const int g = lane >> 2, t = lane & 3;
+                __syncwarp();
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    float* o = Ot + (2 * t) * kOLD + 16 * mt + g;
+                    o[0] = acc[mt][0];
+                    o[kOLD] = acc[mt][1];
+                    o[8] = acc[mt][2];
+                    o[kOLD + 8] = acc[mt][3];
+                }
+                __syncwarp();
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
-                    const int i = i0 + 2 * qi + a;
-                    if (i < n)
-                        st4(out + (bb * n + i) * kC + ci * 4,
-                            make_float4(acc[a][0].x, acc[a][0].y, acc[a][1].x, acc[a][1].y));
+                    const int q = 2 * qi + a;
+                    if (i0 + q < n)
+                        st4(out + (bb * n + i0 + q) * kC + ci * 4,
+                            *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4));
                 }
             }
+        }
+        // advance to this warp's next (batch, tile)
+        b = nb;
+        tile = ntile;
+        nb += step_b;
+        ntile += step_t;
+        if (ntile >= tiles) {
+            ntile -= tiles;
+            ++nb;
         }
     }
 }
@@ -571,6 +723,7 @@ template <typename T, int MODE>
 int gather_tiles_t(const char* label, const void* A, const void* X, const int64_t* idx, void* out, int b, int h,
                    int n, int m, cudaStream_t s) {
     const int tiles = (n + kT - 1) / kT;
+    if ((long long)b * tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
     const size_t smem = size_t(kWarps) * WarpSmem<T, MODE>::kTotal;
     auto kernel = gather_tiles_kernel<T, MODE>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -578,7 +731,11 @@ int gather_tiles_t(const char* label, const void* A, const void* X, const int64_
         return CLUSTEN_ERR_CUDA;
     }
     // one resident wave of CTAs; every warp strides over the (batch, tile) pairs
-    const int per_sm = (int)((227 * 1024) / (smem + 1024));
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
     long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
     const long long need = ((long long)b * tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
