@@ -28,6 +28,7 @@ SIGNATURES = {
     "clusten_qk_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "clusten_av_backward_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_wf_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_wf_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
 }
