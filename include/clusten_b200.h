@@ -58,7 +58,8 @@ enum {
     CLUSTEN_ERR_ALIGN = -4,       /* a pointer is not aligned to its element size */
     CLUSTEN_ERR_WORKSPACE = -5,   /* inverse-index buffer too small or not built for these sizes */
     CLUSTEN_ERR_UNSUPPORTED = -6, /* size outside what the kernels handle (see the function) */
-    CLUSTEN_ERR_CUDA = -7         /* the CUDA runtime reported an error at launch */
+    CLUSTEN_ERR_CUDA = -7,        /* the CUDA runtime reported an error at launch */
+    CLUSTEN_ERR_NOALLOC_CAPACITY = -8 /* clusten_av_backward_noalloc: sizes exceed the built-in array */
 };
 
 /* Human-readable name of a status code; never NULL. */
@@ -141,6 +142,24 @@ CLUSTEN_API int clusten_av_backward(const void* d_feat, const void* attn, const 
                         const int64_t* nbhd_idx, const void* inverse,
                         void* d_attn, void* d_value,
                         int b, int h, int n, int m, int c, int dtype, void* stream);
+
+/* AV backward without a workspace argument, for callers that cannot allocate.
+ * Same results as clusten_av_backward.  The inverse neighbour index is built, on
+ * every call, into an array that is part of the library image on each GPU
+ * (CLUSTEN_NOALLOC_MAX_INTS * 4 bytes, held until the process exits); the call
+ * makes no cudaMalloc / cudaFree and no allocating library call.  It is meant for
+ * hosts that own all device memory themselves or run inside an engine's enqueue
+ * callback and so have no buffer to pass and may not ask for one.
+ * Limit: 64 + 2 * roundup64(b * (n + 1)) + roundup64(b * n * m) <= CLUSTEN_NOALLOC_MAX_INTS,
+ * e.g. b = 16, n = 3136, m = 48; larger calls return CLUSTEN_ERR_NOALLOC_CAPACITY.
+ * The first call on a device looks up the array's device address (a little set-up
+ * work: make that call before any stream capture).  All calls share the array, so
+ * calls that overlap on the GPU race; serialise them on one stream.
+ * Has no counterpart in the reference. */
+#define CLUSTEN_NOALLOC_MAX_INTS 3407936
+CLUSTEN_API int clusten_av_backward_noalloc(const void* d_feat, const void* attn, const void* value,
+                                            const int64_t* nbhd_idx, void* d_attn, void* d_value,
+                                            int b, int h, int n, int m, int c, int dtype, void* stream);
 
 /* ------------------------------------------------------------------------
  * WF: feat_new[b,i,ic,c] = sum_j weights[b,i,j,ic] * feat[b,nbhd_idx[b,i,j],c]

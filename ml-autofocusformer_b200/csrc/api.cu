@@ -115,6 +115,9 @@ const char* clusten_status_string(int status) {
         case CLUSTEN_ERR_WORKSPACE: return "CLUSTEN_ERR_WORKSPACE: inverse-index buffer too small";
         case CLUSTEN_ERR_UNSUPPORTED: return "CLUSTEN_ERR_UNSUPPORTED: size outside the supported range";
         case CLUSTEN_ERR_CUDA: return "CLUSTEN_ERR_CUDA: the CUDA runtime reported an error";
+        case CLUSTEN_ERR_NOALLOC_CAPACITY:
+            return "CLUSTEN_ERR_NOALLOC_CAPACITY: sizes exceed the built-in inverse-index array of "
+                   "clusten_av_backward_noalloc (CLUSTEN_NOALLOC_MAX_INTS)";
         default: return "CLUSTEN: unknown status";
     }
 }
