@@ -63,18 +63,29 @@ gather_sum_kernel(const T* __restrict__ W, const T* __restrict__ X, const int64_
                     for (int i = 0; i < ICT; ++i) wl[i] = Elem<T>::up(wrow[(long long)jl * ic_n + i]);
                 }
                 const int cnt = min(32, m - j0);
-                for (int jj = 0; jj < cnt; ++jj) {
-                    const int t = __shfl_sync(kFull, tok, jj);
-                    A wv[ICT];
+                for (int jj = 0; jj < cnt; jj += 4) {       // four independent row loads per step
+                    int t[4];
+                    A wv[4][ICT];
+                    Vec<T, V> x[4];
 #pragma unroll
-                    for (int i = 0; i < ICT; ++i) wv[i] = __shfl_sync(kFull, wl[i], jj);
-                    if (t >= 0 && act) {
-                        const Vec<T, V> x = ldg_vec<T, V>(xb + (long long)t * c + ch);
+                    for (int u = 0; u < 4; ++u) {
+                        const int src = (jj + u) & 31;
+                        t[u] = __shfl_sync(kFull, tok, src);
+                        if (jj + u >= cnt) t[u] = -1;
 #pragma unroll
-                        for (int i = 0; i < ICT; ++i)
-#pragma unroll
-                            for (int v = 0; v < V; ++v) acc[i][v] += wv[i] * Elem<T>::up(x.v[v]);
+                        for (int i = 0; i < ICT; ++i) wv[u][i] = __shfl_sync(kFull, wl[i], src);
                     }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (t[u] >= 0 && act) x[u] = ldg_vec<T, V>(xb + (long long)t[u] * c + ch);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (t[u] >= 0 && act) {
+#pragma unroll
+                            for (int i = 0; i < ICT; ++i)
+#pragma unroll
+                                for (int v = 0; v < V; ++v) acc[i][v] += wv[u][i] * Elem<T>::up(x[u].v[v]);
+                        }
                 }
             }
             if (act) {
@@ -90,6 +101,8 @@ gather_sum_kernel(const T* __restrict__ W, const T* __restrict__ X, const int64_
     }
 }
 
+// One lane per neighbour: the lane walks its own gathered row (contiguous, V elements per load) against the
+// row's Y vectors, which every lane reads from the same address (one broadcast transaction).
 template <typename T, int V, int ICT>
 __global__ void __launch_bounds__(kThreads)
 gather_dot_kernel(const T* __restrict__ X, const T* __restrict__ Y, const int64_t* __restrict__ idx,
@@ -110,43 +123,27 @@ gather_dot_kernel(const T* __restrict__ X, const T* __restrict__ Y, const int64_
         T* orow = out + (((long long)bb * n_rows + row) * m) * ic_n + ic0;
         for (int j0 = 0; j0 < m; j0 += 32) {
             const int jl = j0 + lane;
-            int tok = -1;
-            if (jl < m) {
-                const long long tk = irow[jl];
-                if (tk >= 0 && tk < n_src) tok = (int)tk;
-            }
-            A res[ICT];
+            long long tk = -1;
+            if (jl < m) tk = irow[jl];
+            const bool ok = tk >= 0 && tk < n_src;
+            const T* xrow = xb + (ok ? tk : 0) * c;
+            A acc[ICT];
 #pragma unroll
-            for (int i = 0; i < ICT; ++i) res[i] = A(0);
-            const int cnt = min(32, m - j0);
-            for (int jj = 0; jj < cnt; ++jj) {
-                const int t = __shfl_sync(kFull, tok, jj);
-                A p[ICT];
-#pragma unroll
-                for (int i = 0; i < ICT; ++i) p[i] = A(0);
-                if (t >= 0) {
-                    for (int cb = 0; cb < c; cb += 32 * V) {
-                        const int ch = cb + lane * V;
-                        if (ch < c) {
-                            const Vec<T, V> x = ldg_vec<T, V>(xb + (long long)t * c + ch);
-#pragma unroll
-                            for (int i = 0; i < ICT; ++i) {
-                                const Vec<T, V> y = ldg_vec<T, V>(yrow + (long long)i * c + ch);
-#pragma unroll
-                                for (int v = 0; v < V; ++v) p[i] += Elem<T>::up(x.v[v]) * Elem<T>::up(y.v[v]);
-                            }
-                        }
-                    }
-                }
+            for (int i = 0; i < ICT; ++i) acc[i] = A(0);
+#pragma unroll 4
+            for (int cb = 0; cb < c; cb += V) {
+                const Vec<T, V> x = ldg_vec<T, V>(xrow + cb);
 #pragma unroll
                 for (int i = 0; i < ICT; ++i) {
-                    const A s = warp_sum(p[i]);
-                    if (lane == jj) res[i] = s;
+                    const Vec<T, V> y = ldg_vec<T, V>(yrow + (long long)i * c + cb);
+#pragma unroll
+                    for (int v = 0; v < V; ++v) acc[i] += Elem<T>::up(x.v[v]) * Elem<T>::up(y.v[v]);
                 }
             }
             if (jl < m) {
 #pragma unroll
-                for (int i = 0; i < ICT; ++i) orow[(long long)jl * ic_n + i] = Elem<T>::down(res[i]);
+                for (int i = 0; i < ICT; ++i)
+                    orow[(long long)jl * ic_n + i] = Elem<T>::down(ok ? acc[i] : A(0));
             }
         }
     }
@@ -181,32 +178,62 @@ scatter_sum_kernel(const T* __restrict__ W, const T* __restrict__ X, const int64
             for (int p0 = 0; p0 < len; p0 += 32) {
                 const unsigned en = (p0 + lane < len) ? (unsigned)ent[p0 + lane] : 0u;
                 const int cnt = min(32, len - p0);
-                for (int jj = 0; jj < cnt; ++jj) {
-                    const unsigned e = __shfl_sync(kFull, en, jj);
-                    if (!(e & kDupFlag)) {
-                        const int row = (int)e / m;
-                        for (int i = 0; i < ic_n; ++i) {
-                            const A w = Elem<T>::up(wb[(long long)e * ic_n + i]);
-                            if (act) {
-                                const Vec<T, V> x = ldg_vec<T, V>(xb + ((long long)row * ic_n + i) * c + ch);
+                for (int jj = 0; jj < cnt; jj += 4) {       // four entries per step: independent loads
+                    unsigned e[4];
+                    bool plain = true;
 #pragma unroll
-                                for (int v = 0; v < V; ++v) acc[v] += w * Elem<T>::up(x.v[v]);
-                            }
+                    for (int u = 0; u < 4; ++u) {
+                        e[u] = __shfl_sync(kFull, en, (jj + u) & 31);
+                        if (jj + u < cnt && (e[u] & kDupFlag)) plain = false;
+                    }
+                    if (plain) {
+                        int row[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) row[u] = (int)e[u] / m;
+                        for (int i = 0; i < ic_n; ++i) {
+                            A w[4];
+                            Vec<T, V> x[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                if (jj + u < cnt) {
+                                    w[u] = Elem<T>::up(wb[(long long)e[u] * ic_n + i]);
+                                    if (act) x[u] = ldg_vec<T, V>(xb + ((long long)row[u] * ic_n + i) * c + ch);
+                                }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+                                if (jj + u < cnt && act) {
+#pragma unroll
+                                    for (int v = 0; v < V; ++v) acc[v] += w[u] * Elem<T>::up(x[u].v[v]);
+                                }
                         }
-                    } else {
-                        // the target occurs more than once in this row: take its slots in order
-                        const int row = (int)(e & ~kDupFlag) / m;
-                        const int64_t* irow = idx + ((long long)bi * n_rows + row) * m;
-                        for (int j = 0; j < m; ++j) {
-                            if (irow[j] != t) continue;
-                            const long long e2 = (long long)row * m + j;
+                        continue;
+                    }
+                    for (int u = 0; u < 4 && jj + u < cnt; ++u) {
+                        if (!(e[u] & kDupFlag)) {
+                            const int row = (int)e[u] / m;
                             for (int i = 0; i < ic_n; ++i) {
-                                const A w = Elem<T>::up(wb[e2 * ic_n + i]);
+                                const A w = Elem<T>::up(wb[(long long)e[u] * ic_n + i]);
                                 if (act) {
-                                    const Vec<T, V> x =
-                                        ldg_vec<T, V>(xb + ((long long)row * ic_n + i) * c + ch);
+                                    const Vec<T, V> x = ldg_vec<T, V>(xb + ((long long)row * ic_n + i) * c + ch);
 #pragma unroll
                                     for (int v = 0; v < V; ++v) acc[v] += w * Elem<T>::up(x.v[v]);
+                                }
+                            }
+                        } else {
+                            // the target occurs more than once in this row: take its slots in order
+                            const int row = (int)(e[u] & ~kDupFlag) / m;
+                            const int64_t* irow = idx + ((long long)bi * n_rows + row) * m;
+                            for (int j = 0; j < m; ++j) {
+                                if (irow[j] != t) continue;
+                                const long long e2 = (long long)row * m + j;
+                                for (int i = 0; i < ic_n; ++i) {
+                                    const A w = Elem<T>::up(wb[e2 * ic_n + i]);
+                                    if (act) {
+                                        const Vec<T, V> x =
+                                            ldg_vec<T, V>(xb + ((long long)row * ic_n + i) * c + ch);
+#pragma unroll
+                                        for (int v = 0; v < V; ++v) acc[v] += w * Elem<T>::up(x.v[v]);
+                                    }
                                 }
                             }
                         }
@@ -275,7 +302,10 @@ int gather_sum_t(const char* label, const void* W, const void* X, const int64_t*
 template <typename T>
 int gather_dot_t(const char* label, const void* X, const void* Y, const int64_t* idx, void* out, int nb, int heads, int n_rows,
                  int n_src, int m, int ic, int c, cudaStream_t s) {
-    const int v = pick_vec(c, sizeof(T), {X, Y});
+    int v = (c % 4 == 0) ? 4 : (c % 2 == 0 ? 2 : 1);
+    while (v > 1 && (reinterpret_cast<uintptr_t>(X) % (v * sizeof(T)) != 0 ||
+                     reinterpret_cast<uintptr_t>(Y) % (v * sizeof(T)) != 0))
+        v >>= 1;
     const int grid = grid_for((long long)nb * n_rows);
     const int step = (ic % 4 == 0) ? 4 : 1;
     for (int ic0 = 0; ic0 < ic; ic0 += step) {

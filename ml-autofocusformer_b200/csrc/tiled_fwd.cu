@@ -185,29 +185,43 @@ __device__ __forceinline__ void sum_load(const SumAddr& sa, float (&b)[2], float
     }
 }
 
+// All 48 staged rows: six steps, fully unrolled, operands of step k+1 fetched before step k multiplies.
 template <bool SPLIT, int KS>
-__device__ __forceinline__ void sum_steps(const SumAddr& sa, int rows8, float (&acc)[2][4], float (&b)[2],
-                                          float (&a)[2][4]) {
-    // operands of step KS are in (a, b); fetch those of step KS + 1 before multiplying
-    if constexpr (KS < kUC / 8) {
-        if (KS * 8 < rows8) {
-            float bn[2], an[2][4];
-            if constexpr (KS + 1 < kUC / 8) {
-                if ((KS + 1) * 8 < rows8) sum_load<KS + 1>(sa, bn, an);
-            }
-            mma_block<SPLIT, 0>(acc[0], a[0], b);
-            mma_block<SPLIT, 0>(acc[1], a[1], b);
-            if constexpr (KS + 1 < kUC / 8) sum_steps<SPLIT, KS + 1>(sa, rows8, acc, bn, an);
-        }
+__device__ __forceinline__ void sum_steps48(const SumAddr& sa, float (&acc)[2][4], float (&b)[2], float (&a)[2][4]) {
+    if constexpr (KS + 1 < kUC / 8) {
+        float bn[2], an[2][4];
+        sum_load<KS + 1>(sa, bn, an);
+        mma_block<SPLIT, 0>(acc[0], a[0], b);
+        mma_block<SPLIT, 0>(acc[1], a[1], b);
+        sum_steps48<SPLIT, KS + 1>(sa, acc, bn, an);
+    } else {
+        mma_block<SPLIT, 0>(acc[0], a[0], b);
+        mma_block<SPLIT, 0>(acc[1], a[1], b);
     }
 }
 
 template <bool SPLIT>
 __device__ __forceinline__ void sum_product_mma(const SumAddr& sa, int rows8, float (&acc)[2][4]) {
-    if (rows8 > 0) {
+    if (rows8 == kUC) {
         float b[2], a[2][4];
         sum_load<0>(sa, b, a);
-        sum_steps<SPLIT, 0>(sa, rows8, acc, b, a);
+        sum_steps48<SPLIT, 0>(sa, acc, b, a);
+    } else {
+        // partial chunk: one step at a time with running addresses
+        SumAddr p = sa;
+#pragma unroll 1
+        for (int u0 = 0; u0 < rows8; u0 += 8) {
+            float b[2], a[2][4];
+            sum_load<0>(p, b, a);
+            mma_block<SPLIT, 0>(acc[0], a[0], b);
+            mma_block<SPLIT, 0>(acc[1], a[1], b);
+            p.w += 8 * 4;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                p.x[mt][0] += 8 * kC * 4;
+                p.x[mt][1] += 8 * kC * 4;
+            }
+        }
     }
 }
 
@@ -320,6 +334,9 @@ struct DedupScratch {
     unsigned short* pre;     // [kBMW]
     unsigned* rowbm;         // [kE / 32]
 };
+__device__ int dedup_tokens(const DedupScratch ps_, unsigned short* lut, int E, int m, bool want_rowdup,
+                            bool* rowdup, int lane, int lo, int hi);
+
 __device__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigned short* lut, int E, int m, int i0,
                           int n, bool want_rowdup, bool* rowdup, int lane) {
     const DedupScratch* ps = &ps_;
@@ -335,6 +352,13 @@ __device__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigne
         }
         ps->tok[x] = t;
     }
+    return dedup_tokens(ps_, lut, E, m, want_rowdup, rowdup, lane, lo, hi);
+}
+
+// ps.tok[0..E) (kSkip = none) with its value range [lo, hi] over the lanes -> lut, ps.uniq; returns U.
+__device__ int dedup_tokens(const DedupScratch ps_, unsigned short* lut, int E, int m, bool want_rowdup,
+                            bool* rowdup, int lane, int lo, int hi) {
+    const DedupScratch* ps = &ps_;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         lo = min(lo, __shfl_xor_sync(kFull, lo, o));
@@ -710,6 +734,244 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
     }
 }
 
+// ----------------------------------------------------------------------------- scatter side (d_key, d_value)
+//   out[bb, t, :] = sum over inverse-index entries (i, j) of target t:  W[bb, i, j] * X[bb, i, :]
+// Same scheme with targets as tile rows: a warp takes 8 consecutive targets, concatenates their
+// inverse-index segments (384 entries at a time), de-duplicates the SOURCE rows, stages each once
+// per head and multiplies the dense [8 x U] weights on the tensor cores.  Segments are ordered by
+// source row and slots ascend with the source row, so the summation order is fixed.
+constexpr int kES = 512;            // inverse-index entries handled at a time (8 targets x ~48 on average)
+constexpr int kESPL = kES / 32;
+
+template <typename T> struct ScatterSmem {
+    static constexpr bool kIsFloat = std::is_same<T, float>::value;
+    static constexpr int kX = kUC * kC * 4;
+    static constexpr int kXraw = kIsFloat ? 0 : kUC * kC * (int)sizeof(T);
+    static constexpr int kOp = kT * kWLD * 4;
+    static constexpr int kLut = kES * 2;
+    static constexpr int kTotal = kX + kXraw + kOp + 2 * kLut;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarps, 4)
+scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int64_t* __restrict__ idx,
+                     InverseView inv, T* __restrict__ out, int batch, int heads, int n, int m, int tiles) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    using WS = ScatterSmem<T>;
+    constexpr bool kIsFloat = WS::kIsFloat;
+    constexpr int kPer = 16 / (int)sizeof(T);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int qi = lane >> 3, ci = lane & 7;
+    unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
+    float* Xs = reinterpret_cast<float*>(base);
+    T* Xraw = reinterpret_cast<T*>(base + WS::kX);
+    float* Wd = reinterpret_cast<float*>(base + WS::kX + WS::kXraw);
+    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kXraw + WS::kOp);
+    unsigned short* uniq = lut + kES;
+    DedupScratch ds;
+    ds.tok = reinterpret_cast<unsigned short*>(base);           // the row buffer is free while de-duplicating
+    ds.uniq = uniq;
+    ds.bm = reinterpret_cast<unsigned*>(Wd);
+    ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
+    ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
+    const SumAddr sa = make_sum_addr(Wd, Xs, lane);
+    const int sw = (ci ^ (qi << 1)) << 2;                       // chunk swizzle of staged row qi + 4k
+
+    const unsigned total = (unsigned)batch * (unsigned)tiles;
+    const unsigned nwarps = gridDim.x * kWarps;
+    // segment (length, start) of target t0 + lane of a task, lanes 0..7
+    auto load_segment = [&](unsigned task, int& len, int& start) {
+        len = 0;
+        start = 0;
+        if (task < total) {
+            const int b = (int)(task / (unsigned)tiles);
+            const int t = (int)(task - (unsigned)b * (unsigned)tiles) * kT + lane;
+            if (lane < kT && t < n) {
+                len = inv.seglen[(long long)b * n + t];
+                start = inv.rowptr[(long long)b * (n + 1) + t];
+            }
+        }
+    };
+    int next_len, next_start;
+    load_segment(blockIdx.x * kWarps + warp, next_len, next_start);
+    for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
+        const int b = (int)(task / (unsigned)tiles);
+        const int t0 = (int)(task - (unsigned)b * (unsigned)tiles) * kT;
+        const int64_t* idx_b = idx + (long long)b * n * m;
+        const int* entries = inv.entries + (long long)b * n * m;
+        const int len = next_len, start = next_start;
+        load_segment(task + nwarps, next_len, next_start);      // in flight while this tile is worked on
+        int incl = len;
+#pragma unroll
+        for (int o = 1; o < kT; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += y;
+        }
+        const int E_total = __shfl_sync(kFull, incl, kT - 1);
+
+        for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kES) {
+            const int E = max(0, min(kES, E_total - e0));
+            // ---- this chunk's entries (all loads first), then their source rows; tile row 3 bits per edge
+            int ereg[kESPL];
+            unsigned long long rpack = 0ull;
+            {
+            int off[kT], st[kT];                                // per tile row: offset in the edge list, segment start
+#pragma unroll
+            for (int r = 0; r < kT; ++r) {
+                off[r] = __shfl_sync(kFull, incl - len, r);
+                st[r] = __shfl_sync(kFull, start, r);
+            }
+#pragma unroll
+            for (int k = 0; k < kESPL; ++k) {
+                const int p = e0 + lane + 32 * k;
+                int r = 0;
+#pragma unroll
+                for (int j = 1; j < kT; ++j) r += (p >= off[j]) ? 1 : 0;
+                int s0 = st[0], o0 = off[0];
+#pragma unroll
+                for (int j = 1; j < kT; ++j)
+                    if (r == j) {
+                        s0 = st[j];
+                        o0 = off[j];
+                    }
+                ereg[k] = (lane + 32 * k < E) ? __ldg(entries + s0 + (p - o0)) : 0;
+                rpack |= (unsigned long long)r << (3 * k);
+            }
+            }
+            int lo = INT_MAX, hi = -1;
+            bool any_flag = false;
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < kESPL; ++k) {
+                const int x = lane + 32 * k;
+                if (x < E) {
+                    const unsigned e = (unsigned)ereg[k];
+                    const int src = (int)(e & ~kDupFlag) / m;
+                    ds.tok[x] = (unsigned short)src;
+                    lo = min(lo, src);
+                    hi = max(hi, src);
+                    if (e & kDupFlag) any_flag = true;
+                }
+            }
+            any_flag = __any_sync(kFull, any_flag);
+            bool unused = false;
+            const int U = E > 0 ? dedup_tokens(ds, lut, E, m, false, &unused, lane, lo, hi) : 0;
+            __syncwarp();
+
+            for (int g = 0; g < heads; ++g) {
+                const long long bb = (long long)b * heads + g;
+                const T* Wh = W + (bb * n) * m;
+                const T* Xh = X + (bb * n) * kC;
+                // weights of this lane's edges: plain entries first (independent loads) ...
+                float wreg[kESPL];
+#pragma unroll
+                for (int k = 0; k < kESPL; ++k) {
+                    const unsigned e = (unsigned)ereg[k];
+                    const bool plain = lane + 32 * k < E && !(e & kDupFlag);
+                    wreg[k] = plain ? Elem<T>::up(Wh[plain ? e : 0u]) : 0.f;
+                }
+                // ... then targets that occur several times in their source row: sum that row's slots in order
+                if (any_flag) {
+#pragma unroll
+                    for (int k = 0; k < kESPL; ++k) {
+                        const unsigned e = (unsigned)ereg[k];
+                        if (lane + 32 * k < E && (e & kDupFlag)) {
+                            const int row = (int)(e & ~kDupFlag) / m;
+                            const int t = t0 + (int)((rpack >> (3 * k)) & 7ull);
+                            const int64_t* irow = idx_b + (long long)row * m;
+                            float w = 0.f;
+                            for (int j = 0; j < m; ++j)
+                                if (irow[j] == t) w += Elem<T>::up(Wh[(long long)row * m + j]);
+                            wreg[k] = w;
+                        }
+                    }
+                }
+                float acc[2][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
+                for (int u0 = 0; u0 < U; u0 += kUC) {
+                    const int Uc = min(kUC, U - u0);
+                    const int rows8 = (Uc + 7) & ~7;
+                    __syncwarp();
+                    if (kIsFloat) {
+#pragma unroll
+                        for (int k = 0; k < kUC / 4; ++k) {
+                            const int r = qi + 4 * k;
+                            if (r < rows8) {
+                                float* dst = Xs + r * kC + sw;
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * kC + ci * 4);
+                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+                    } else {
+                        const int pr = lane >> 2, pc = lane & 3;
+#pragma unroll
+                        for (int k = 0; k < kUC / 8; ++k) {
+                            const int r = pr + 8 * k;
+                            if (r < rows8) {
+                                T* dst = Xraw + r * kC + pc * kPer;
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * kC + pc * kPer);
+                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+                    }
+                    cp_async_commit();
+                    for (int z = lane; z < kT * kWLD / 4; z += 32)
+                        reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < kESPL; ++k) {
+                        const int x = lane + 32 * k;
+                        if (x < E) {
+                            const int rel = (int)lut[x] - u0;
+                            if (rel >= 0 && rel < Uc) Wd[(int)((rpack >> (3 * k)) & 7ull) * kWLD + rel] = wreg[k];
+                        }
+                    }
+                    cp_async_wait<0>();
+                    __syncwarp();
+                    if (!kIsFloat) {
+#pragma unroll
+                        for (int k = 0; k < kUC / 4; ++k) {
+                            const int r = qi + 4 * k;
+                            if (r < rows8) st4(Xs + r * kC + sw, ld4(Xraw + r * kC + ci * 4));
+                        }
+                        __syncwarp();
+                    }
+                    sum_product_mma<kIsFloat>(sa, rows8, acc);
+                }
+                // D fragments -> output tile in shared memory -> 16-byte stores (added to what earlier
+                // chunks of a long edge list wrote)
+                float* Ot = Wd;
+                const int gg = lane >> 2, tt = lane & 3;
+                __syncwarp();
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    float* o = Ot + (2 * tt) * kOLD + 16 * mt + gg;
+                    o[0] = acc[mt][0];
+                    o[kOLD] = acc[mt][1];
+                    o[8] = acc[mt][2];
+                    o[kOLD + 8] = acc[mt][3];
+                }
+                __syncwarp();
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    const int q = 2 * qi + a;
+                    if (t0 + q < n) {
+                        T* dstp = out + (bb * n + t0 + q) * kC + ci * 4;
+                        float4 v = *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4);
+                        if (e0 > 0) {
+                            const float4 old = ld4(dstp);
+                            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                        }
+                        st4(dstp, v);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------- host side
 bool gather_supported(int dtype, std::initializer_list<const void*> ptrs, int n, int m, int c) {
     if (c != kC || m < 1 || m > kMmax || n < 1 || n > 65000) return false;
@@ -741,6 +1003,31 @@ int gather_tiles_t(const char* label, const void* A, const void* X, const int64_
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);
     kernel<<<(int)grid, 32 * kWarps, smem, s>>>((const T*)A, (const T*)X, idx, (T*)out, b, h, n, m, tiles);
+    note_launch();
+    return check_launch();
+}
+
+template <typename T>
+int scatter_tiles_t(const char* label, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
+                    void* out, int b, int h, int n, int m, cudaStream_t s) {
+    const int tiles = (n + kT - 1) / kT;
+    if ((long long)b * tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    const size_t smem = size_t(kWarps) * ScatterSmem<T>::kTotal;
+    auto kernel = scatter_tiles_kernel<T>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const long long need = ((long long)b * tiles + kWarps - 1) / kWarps;
+    if (grid > need) grid = need;
+    ScopedKernelTimer timer(label, s);
+    kernel<<<(int)grid, 32 * kWarps, smem, s>>>((const T*)W, (const T*)X, idx, inv, (T*)out, b, h, n, m, tiles);
     note_launch();
     return check_launch();
 }
@@ -786,6 +1073,23 @@ int launch_tiled_dot(const char* label, int dtype, const void* X, const void* Y,
         case CLUSTEN_F32: return gather_tiles_t<float, 1>(label, Y, X, idx, out, b, h, n, m, s);
         case CLUSTEN_F16: return gather_tiles_t<__half, 1>(label, Y, X, idx, out, b, h, n, m, s);
         case CLUSTEN_BF16: return gather_tiles_t<__nv_bfloat16, 1>(label, Y, X, idx, out, b, h, n, m, s);
+        default: return CLUSTEN_ERR_DTYPE;
+    }
+}
+
+}  // namespace clusten
+
+namespace clusten {
+
+bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c) {
+    return gather_supported(dtype, {X, out}, n, 1, c) && m >= 1 && reinterpret_cast<uintptr_t>(W) % 4 == 0;
+}
+int launch_tiled_scatter(const char* label, int dtype, const void* W, const void* X, const int64_t* idx,
+                         const InverseView& inv, void* out, int b, int h, int n, int m, cudaStream_t s) {
+    switch (dtype) {
+        case CLUSTEN_F32: return scatter_tiles_t<float>(label, W, X, idx, inv, out, b, h, n, m, s);
+        case CLUSTEN_F16: return scatter_tiles_t<__half>(label, W, X, idx, inv, out, b, h, n, m, s);
+        case CLUSTEN_BF16: return scatter_tiles_t<__nv_bfloat16>(label, W, X, idx, inv, out, b, h, n, m, s);
         default: return CLUSTEN_ERR_DTYPE;
     }
 }
