@@ -16,6 +16,8 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 
+// P > 0: number of 32-slot passes over a row (m <= 32 P), rows kept in registers; P == 0: any m.
+template <int P>
 __global__ void __launch_bounds__(kThreads)
 inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int* __restrict__ header,
                      int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries) {
@@ -100,6 +102,59 @@ inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt,
     // row r inside target t's segment is the number of lower rows of the group that
     // also hit t, read off a 32-bit row mask.
     const unsigned bit = 1u << warp;
+    if (P > 0) {
+        // m <= 32 P: a lane keeps its P slots of the row in registers; the next group's slots are
+        // loaded before the current group is processed
+        int cur[P > 0 ? P : 1], nxt[P > 0 ? P : 1];
+        auto load_row = [&](int row, int (&dst)[P > 0 ? P : 1]) {
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                const int j = lane + 32 * p;
+                long long tk = -1;
+                if (row < n_rows && j < m) tk = ib[(long long)row * m + j];
+                dst[p] = (tk >= 0 && tk < nt) ? (int)tk : -1;
+            }
+        };
+        load_row(warp, cur);
+        for (int g0 = 0; g0 < n_rows; g0 += kWarps) {
+            const int row = g0 + warp;
+            load_row(row + kWarps, nxt);
+            unsigned win = 0u, last = 0u;
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                if (cur[p] >= 0) {
+                    const unsigned old = atomicOr(&mask[cur[p]], bit);
+                    if (old & bit) atomicOr(&dupm[cur[p]], bit);
+                    else win |= 1u << p;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                if ((win >> p) & 1u) {
+                    const int tk = cur[p];
+                    const unsigned mk = mask[tk];
+                    const int pos = base[tk] + __popc(mk & (bit - 1u));
+                    const bool dup = (dupm[tk] & bit) != 0u;
+                    ent[pos] = dup ? (int)(kDupFlag | (unsigned)(row * m)) : (row * m + lane + 32 * p);
+                    if ((mk >> warp) == 1u) last |= 1u << p;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                if ((last >> p) & 1u) {
+                    const int tk = cur[p];
+                    base[tk] += __popc(mask[tk]);
+                    mask[tk] = 0u;
+                    dupm[tk] = 0u;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int p = 0; p < P; ++p) cur[p] = nxt[p];
+        }
+    } else {
     for (int g0 = 0; g0 < n_rows; g0 += kWarps) {
         const int row = g0 + warp;
         const bool live = row < n_rows;
@@ -139,6 +194,7 @@ inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt,
         }
         __syncthreads();
     }
+    }
 
     int* sl = seglen + (long long)b * nt;
     for (int t = tid; t < nt; t += kThreads) sl[t] = base[t] - rp[t];
@@ -154,16 +210,16 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
         return CLUSTEN_ERR_CUDA;
     }
     const size_t smem = size_t(3) * nt * sizeof(int);
+    auto kernel = m <= 32 ? inverse_build_kernel<1> : (m <= 64 ? inverse_build_kernel<2> : inverse_build_kernel<0>);
     if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(inverse_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-            cudaSuccess) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
             return CLUSTEN_ERR_CUDA;
         }
     }
     ScopedKernelTimer timer("inverse_build", s);
-    inverse_build_kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
-                                                   const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
+    kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
+                                     const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
     note_launch();
     return check_launch();
 }

@@ -243,8 +243,8 @@ __device__ __forceinline__ DotAddr make_dot_addr(const float* Ys, const float* X
     return a;
 }
 
-template <bool SPLIT>
-__device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
+template <bool SPLIT, bool FULL>
+__device__ __forceinline__ void dot_product_tiles(const DotAddr& da, int mtiles) {
     float acc[kUC / 16][4];
 #pragma unroll
     for (int mt = 0; mt < kUC / 16; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
@@ -258,7 +258,7 @@ __device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
         if (ks == 3) { CLUSTEN_LDS(bb[0], da.y, 96); CLUSTEN_LDS(bb[1], da.y, 112); }
 #pragma unroll
         for (int mt = 0; mt < kUC / 16; ++mt) {
-            if (mt < mtiles) {
+            if (FULL || mt < mtiles) {
                 float a[4];
                 // rows 16 mt + g and + 8: byte offsets 16 mt * 128 and + 8 * 128
                 if (mt == 0) {
@@ -278,7 +278,7 @@ __device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
     // D fragment -> Sb[q][u]: d0=(u=16mt+g, q=2t) d1=(u, 2t+1) d2=(u+8, 2t) d3=(u+8, 2t+1)
 #pragma unroll
     for (int mt = 0; mt < kUC / 16; ++mt) {
-        if (mt < mtiles) {
+        if (FULL || mt < mtiles) {
             if (mt == 0) {
                 asm volatile("st.shared.f32 [%0+0], %1;\n" ::"r"(da.s), "f"(acc[0][0]));
                 asm volatile("st.shared.f32 [%0+208], %1;\n" ::"r"(da.s), "f"(acc[0][1]));
@@ -299,6 +299,12 @@ __device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
     }
 }
 static_assert(kWLD * 4 == 208 && kC * 4 == 128 && kUC == 48, "byte offsets above are written out for these sizes");
+
+template <bool SPLIT>
+__device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
+    if (mtiles == kUC / 16) dot_product_tiles<SPLIT, true>(da, mtiles);
+    else dot_product_tiles<SPLIT, false>(da, mtiles);
+}
 
 // ----------------------------------------------------------------------------- producer: tile analysis
 // Are the 8 rows of the tile identical, in range, and the tile complete?  One warp.
