@@ -740,28 +740,45 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
     }
 }
 
-// ----------------------------------------------------------------------------- scatter side (d_key, d_value)
-//   out[bb, t, :] = sum over inverse-index entries (i, j) of target t:  W[bb, i, j] * X[bb, i, :]
+// ----------------------------------------------------------------------------- scatter side (d_key, d_value, d_feat)
+//   out[b, t, 32 s .. 32 s + 31] = sum over inverse-index entries (i, j) of target t and k < ic:
+//                                   W[b, s, (i * m + j) * ic + k] * X[b, s, i * ic + k, :]
 // Same scheme with targets as tile rows: a warp takes 8 consecutive targets, concatenates their
-// inverse-index segments (384 entries at a time), de-duplicates the SOURCE rows, stages each once
-// per head and multiplies the dense [8 x U] weights on the tensor cores.  Segments are ordered by
-// source row and slots ascend with the source row, so the summation order is fixed.
-constexpr int kES = 512;            // inverse-index entries handled at a time (8 targets x ~48 on average)
-constexpr int kESPL = kES / 32;
+// inverse-index segments (512 edges at a time), de-duplicates the SOURCE rows, stages each once per
+// 32-channel slab ("head") and multiplies the dense [8 x U] weights on the tensor cores.  Segments
+// are ordered by source row and slots ascend with the source row, so the summation order is fixed.
+// QK / AV: ic = 1, a slab is a head.  WF: a slab is 32 of the c channels, the weights are shared by
+// the slabs and every entry fans out into its ic (weight, row) pairs.
+struct ScatterParams {
+    const void* W;  long long w_batch, w_head;                 // element strides
+    const void* X;  long long x_batch, x_head;  int x_row;
+    void* out;      long long o_batch, o_head;  int o_row;
+    const int64_t* idx;  int idx_rows;  int m;                   // nbhd_idx [batch][idx_rows][m]
+    InverseView inv;  int n_tgt;
+    int ic, heads, batch, tiles;
+    unsigned m_magic, m_shift, ic_magic, ic_shift;              // x / d = (umulhi(magic, x) + x) >> shift
+};
+__device__ __forceinline__ unsigned fast_div(unsigned x, unsigned magic, unsigned shift) {
+    return (__umulhi(magic, x) + x) >> shift;
+}
+
+constexpr int kES = 512;            // edges handled at a time (8 targets x ~48 on average)
 
 template <typename T> struct ScatterSmem {
     static constexpr bool kIsFloat = std::is_same<T, float>::value;
-    static constexpr int kX = kUC * kC * 4;
+    static constexpr int kX = kUC * kC * 4;         // staged rows; de-duplication scratch before that
     static constexpr int kXraw = kIsFloat ? 0 : kUC * kC * (int)sizeof(T);
-    static constexpr int kOp = kT * kWLD * 4;
-    static constexpr int kLut = kES * 2;
-    static constexpr int kTotal = kX + kXraw + kOp + 2 * kLut;
+    static constexpr int kOp = kT * kWLD * 4;       // dense weights; bitmap scratch; output tile
+    static constexpr int kEdge = kES * 4;           // weight index of each edge (bit 31: target repeats in its row)
+    static constexpr int kWbuf = kES * 4;           // weight of each edge for the current slab
+    static constexpr int kLut = kES * 2;            // slot | tile row << 12;   slot -> source row
+    static constexpr int kTotal = kX + kXraw + kOp + kEdge + kWbuf + 2 * kLut;
 };
+static_assert(2 * kES * 2 <= kUC * kC * 4, "token and slot scratch must fit in the row buffer");
 
 template <typename T>
 __global__ void __launch_bounds__(32 * kWarps, 4)
-scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int64_t* __restrict__ idx,
-                     InverseView inv, T* __restrict__ out, int batch, int heads, int n, int m, int tiles) {
+scatter_tiles_kernel(const ScatterParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using WS = ScatterSmem<T>;
     constexpr bool kIsFloat = WS::kIsFloat;
@@ -772,40 +789,47 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
     float* Xs = reinterpret_cast<float*>(base);
     T* Xraw = reinterpret_cast<T*>(base + WS::kX);
     float* Wd = reinterpret_cast<float*>(base + WS::kX + WS::kXraw);
-    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kXraw + WS::kOp);
+    unsigned* edge = reinterpret_cast<unsigned*>(base + WS::kX + WS::kXraw + WS::kOp);
+    float* wbuf = reinterpret_cast<float*>(base + WS::kX + WS::kXraw + WS::kOp + WS::kEdge);
+    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kXraw + WS::kOp + WS::kEdge + WS::kWbuf);
     unsigned short* uniq = lut + kES;
     DedupScratch ds;
     ds.tok = reinterpret_cast<unsigned short*>(base);           // the row buffer is free while de-duplicating
+    unsigned short* slots = ds.tok + kES;
     ds.uniq = uniq;
     ds.bm = reinterpret_cast<unsigned*>(Wd);
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
     const SumAddr sa = make_sum_addr(Wd, Xs, lane);
     const int sw = (ci ^ (qi << 1)) << 2;                       // chunk swizzle of staged row qi + 4k
+    const int m = p.m, ic = p.ic, n_tgt = p.n_tgt;
+    const T* Wg = static_cast<const T*>(p.W);
+    const T* Xg = static_cast<const T*>(p.X);
+    T* Og = static_cast<T*>(p.out);
 
-    const unsigned total = (unsigned)batch * (unsigned)tiles;
+    const unsigned total = (unsigned)p.batch * (unsigned)p.tiles;
     const unsigned nwarps = gridDim.x * kWarps;
     // segment (length, start) of target t0 + lane of a task, lanes 0..7
     auto load_segment = [&](unsigned task, int& len, int& start) {
         len = 0;
         start = 0;
         if (task < total) {
-            const int b = (int)(task / (unsigned)tiles);
-            const int t = (int)(task - (unsigned)b * (unsigned)tiles) * kT + lane;
-            if (lane < kT && t < n) {
-                len = inv.seglen[(long long)b * n + t];
-                start = inv.rowptr[(long long)b * (n + 1) + t];
+            const int b = (int)(task / (unsigned)p.tiles);
+            const int t = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT + lane;
+            if (lane < kT && t < n_tgt) {
+                len = p.inv.seglen[(long long)b * n_tgt + t];
+                start = p.inv.rowptr[(long long)b * (n_tgt + 1) + t];
             }
         }
     };
     int next_len, next_start;
     load_segment(blockIdx.x * kWarps + warp, next_len, next_start);
     for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
-        const int b = (int)(task / (unsigned)tiles);
-        const int t0 = (int)(task - (unsigned)b * (unsigned)tiles) * kT;
-        const int64_t* idx_b = idx + (long long)b * n * m;
-        const int* entries = inv.entries + (long long)b * n * m;
-        const int len = next_len, start = next_start;
+        const int b = (int)(task / (unsigned)p.tiles);
+        const int t0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
+        const int64_t* idx_b = p.idx + (long long)b * p.idx_rows * m;
+        const int* entries = p.inv.entries + (long long)b * p.idx_rows * m;
+        const int len = next_len * ic, start = next_start;      // every entry fans out into ic edges
         load_segment(task + nwarps, next_len, next_start);      // in flight while this tile is worked on
         int incl = len;
 #pragma unroll
@@ -814,25 +838,26 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
             if (lane >= o) incl += y;
         }
         const int E_total = __shfl_sync(kFull, incl, kT - 1);
+        int off[kT], st[kT];                                    // per tile row: offset in the edge list, segment start
+#pragma unroll
+        for (int r = 0; r < kT; ++r) {
+            off[r] = __shfl_sync(kFull, incl - len, r);
+            st[r] = __shfl_sync(kFull, start, r);
+        }
 
         for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kES) {
             const int E = max(0, min(kES, E_total - e0));
-            // ---- this chunk's entries (all loads first), then their source rows; tile row 3 bits per edge
-            int ereg[kESPL];
-            unsigned long long rpack = 0ull;
-            {
-            int off[kT], st[kT];                                // per tile row: offset in the edge list, segment start
-#pragma unroll
-            for (int r = 0; r < kT; ++r) {
-                off[r] = __shfl_sync(kFull, incl - len, r);
-                st[r] = __shfl_sync(kFull, start, r);
-            }
-#pragma unroll
-            for (int k = 0; k < kESPL; ++k) {
-                const int p = e0 + lane + 32 * k;
+            // ---- this chunk's edges: weight index (flagged when the target repeats in its row), source
+            //      row, tile row
+            int lo = INT_MAX, hi = -1;
+            bool any_flag = false;
+            __syncwarp();
+#pragma unroll 4
+            for (int x = lane; x < E; x += 32) {
+                const int pe = e0 + x;
                 int r = 0;
 #pragma unroll
-                for (int j = 1; j < kT; ++j) r += (p >= off[j]) ? 1 : 0;
+                for (int j = 1; j < kT; ++j) r += (pe >= off[j]) ? 1 : 0;
                 int s0 = st[0], o0 = off[0];
 #pragma unroll
                 for (int j = 1; j < kT; ++j)
@@ -840,55 +865,55 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
                         s0 = st[j];
                         o0 = off[j];
                     }
-                ereg[k] = (lane + 32 * k < E) ? __ldg(entries + s0 + (p - o0)) : 0;
-                rpack |= (unsigned long long)r << (3 * k);
-            }
-            }
-            int lo = INT_MAX, hi = -1;
-            bool any_flag = false;
-            __syncwarp();
-#pragma unroll
-            for (int k = 0; k < kESPL; ++k) {
-                const int x = lane + 32 * k;
-                if (x < E) {
-                    const unsigned e = (unsigned)ereg[k];
-                    const int src = (int)(e & ~kDupFlag) / m;
-                    ds.tok[x] = (unsigned short)src;
-                    lo = min(lo, src);
-                    hi = max(hi, src);
-                    if (e & kDupFlag) any_flag = true;
-                }
+                const unsigned q = (unsigned)(pe - o0);                     // position inside the fanned-out segment
+                const unsigned qe = fast_div(q, p.ic_magic, p.ic_shift);     // entry inside the segment
+                const unsigned k = q - qe * (unsigned)ic;
+                const unsigned e = (unsigned)__ldg(entries + s0 + (int)qe);
+                const unsigned plain = e & ~kDupFlag;                       // row * m + slot
+                const unsigned src = fast_div(plain, p.m_magic, p.m_shift);
+                edge[x] = (plain * (unsigned)ic + k) | (e & kDupFlag);
+                const int srow = (int)(src * (unsigned)ic + k);
+                ds.tok[x] = (unsigned short)srow;
+                lut[x] = (unsigned short)(r << 12);                         // the slot is merged in below
+                lo = min(lo, srow);
+                hi = max(hi, srow);
+                if (e & kDupFlag) any_flag = true;
             }
             any_flag = __any_sync(kFull, any_flag);
-            bool unused = false;
-            const int U = E > 0 ? dedup_tokens(ds, lut, E, m, false, &unused, lane, lo, hi) : 0;
+            int U = 0;
+            if (E > 0) {
+                bool unused = false;
+                U = dedup_tokens(ds, slots, E, m, false, &unused, lane, lo, hi);
+                for (int x = lane; x < E; x += 32) lut[x] = (unsigned short)(lut[x] | slots[x]);
+            }
             __syncwarp();
 
-            for (int g = 0; g < heads; ++g) {
-                const long long bb = (long long)b * heads + g;
-                const T* Wh = W + (bb * n) * m;
-                const T* Xh = X + (bb * n) * kC;
-                // weights of this lane's edges: plain entries first (independent loads) ...
-                float wreg[kESPL];
-#pragma unroll
-                for (int k = 0; k < kESPL; ++k) {
-                    const unsigned e = (unsigned)ereg[k];
-                    const bool plain = lane + 32 * k < E && !(e & kDupFlag);
-                    wreg[k] = plain ? Elem<T>::up(Wh[plain ? e : 0u]) : 0.f;
-                }
-                // ... then targets that occur several times in their source row: sum that row's slots in order
-                if (any_flag) {
-#pragma unroll
-                    for (int k = 0; k < kESPL; ++k) {
-                        const unsigned e = (unsigned)ereg[k];
-                        if (lane + 32 * k < E && (e & kDupFlag)) {
-                            const int row = (int)(e & ~kDupFlag) / m;
-                            const int t = t0 + (int)((rpack >> (3 * k)) & 7ull);
-                            const int64_t* irow = idx_b + (long long)row * m;
-                            float w = 0.f;
-                            for (int j = 0; j < m; ++j)
-                                if (irow[j] == t) w += Elem<T>::up(Wh[(long long)row * m + j]);
-                            wreg[k] = w;
+            for (int g = 0; g < p.heads; ++g) {
+                const T* Wh = Wg + (long long)b * p.w_batch + (long long)g * p.w_head;
+                const T* Xh = Xg + (long long)b * p.x_batch + (long long)g * p.x_head;
+                // ---- weights of the edges for this slab
+                if (g == 0 || p.w_head != 0) {
+#pragma unroll 4
+                    for (int x = lane; x < E; x += 32) {
+                        const unsigned e = edge[x];
+                        wbuf[x] = (e & kDupFlag) ? 0.f : Elem<T>::up(Wh[e]);
+                    }
+                    if (any_flag) {
+                        // targets that occur several times in their source row: sum that row's slots in order
+                        for (int x = lane; x < E; x += 32) {
+                            const unsigned e = edge[x];
+                            if (e & kDupFlag) {
+                                const unsigned we = e & ~kDupFlag;
+                                const unsigned pl = fast_div(we, p.ic_magic, p.ic_shift);
+                                const unsigned k = we - pl * (unsigned)ic;
+                                const unsigned row = fast_div(pl, p.m_magic, p.m_shift);
+                                const int t = t0 + (lut[x] >> 12);
+                                const int64_t* irow = idx_b + (long long)row * m;
+                                float w = 0.f;
+                                for (int j = 0; j < m; ++j)
+                                    if (irow[j] == t) w += Elem<T>::up(Wh[((long long)row * m + j) * ic + k]);
+                                wbuf[x] = w;
+                            }
                         }
                     }
                 }
@@ -905,7 +930,7 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
                             const int r = qi + 4 * k;
                             if (r < rows8) {
                                 float* dst = Xs + r * kC + sw;
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * kC + ci * 4);
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * p.x_row + ci * 4);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
@@ -916,7 +941,7 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
                             const int r = pr + 8 * k;
                             if (r < rows8) {
                                 T* dst = Xraw + r * kC + pc * kPer;
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * kC + pc * kPer);
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * p.x_row + pc * kPer);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
@@ -925,13 +950,11 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
                     for (int z = lane; z < kT * kWLD / 4; z += 32)
                         reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                     __syncwarp();
-#pragma unroll
-                    for (int k = 0; k < kESPL; ++k) {
-                        const int x = lane + 32 * k;
-                        if (x < E) {
-                            const int rel = (int)lut[x] - u0;
-                            if (rel >= 0 && rel < Uc) Wd[(int)((rpack >> (3 * k)) & 7ull) * kWLD + rel] = wreg[k];
-                        }
+#pragma unroll 4
+                    for (int x = lane; x < E; x += 32) {
+                        const unsigned lr = lut[x];
+                        const int rel = (int)(lr & 0xfffu) - u0;
+                        if (rel >= 0 && rel < Uc) Wd[(lr >> 12) * kWLD + rel] = wbuf[x];
                     }
                     cp_async_wait<0>();
                     __syncwarp();
@@ -959,11 +982,12 @@ scatter_tiles_kernel(const T* __restrict__ W, const T* __restrict__ X, const int
                     o[kOLD + 8] = acc[mt][3];
                 }
                 __syncwarp();
+                T* Oh = Og + (long long)b * p.o_batch + (long long)g * p.o_head;
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
                     const int q = 2 * qi + a;
-                    if (t0 + q < n) {
-                        T* dstp = out + (bb * n + t0 + q) * kC + ci * 4;
+                    if (t0 + q < n_tgt) {
+                        T* dstp = Oh + (long long)(t0 + q) * p.o_row + ci * 4;
                         float4 v = *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4);
                         if (e0 > 0) {
                             const float4 old = ld4(dstp);
@@ -1013,11 +1037,20 @@ int gather_tiles_t(const char* label, const void* A, const void* X, const int64_
     return check_launch();
 }
 
+// magic numbers for x / d with x < 2^31: q = (umulhi(magic, x) + x) >> shift
+void div_magic(unsigned d, unsigned* magic, unsigned* shift) {
+    unsigned l = 0;
+    while ((1ull << l) < d) ++l;
+    *magic = (unsigned)(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+    *shift = l;
+}
+
 template <typename T>
-int scatter_tiles_t(const char* label, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
-                    void* out, int b, int h, int n, int m, cudaStream_t s) {
-    const int tiles = (n + kT - 1) / kT;
-    if ((long long)b * tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+int scatter_tiles_t(const char* label, ScatterParams p, cudaStream_t s) {
+    p.tiles = (p.n_tgt + kT - 1) / kT;
+    if ((long long)p.batch * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    div_magic((unsigned)p.m, &p.m_magic, &p.m_shift);
+    div_magic((unsigned)p.ic, &p.ic_magic, &p.ic_shift);
     const size_t smem = size_t(kWarps) * ScatterSmem<T>::kTotal;
     auto kernel = scatter_tiles_kernel<T>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -1030,12 +1063,21 @@ int scatter_tiles_t(const char* label, const void* W, const void* X, const int64
         return CLUSTEN_ERR_CUDA;
     }
     long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
-    const long long need = ((long long)b * tiles + kWarps - 1) / kWarps;
+    const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);
-    kernel<<<(int)grid, 32 * kWarps, smem, s>>>((const T*)W, (const T*)X, idx, inv, (T*)out, b, h, n, m, tiles);
+    kernel<<<(int)grid, 32 * kWarps, smem, s>>>(p);
     note_launch();
     return check_launch();
+}
+
+int scatter_dispatch(const char* label, int dtype, const ScatterParams& p, cudaStream_t s) {
+    switch (dtype) {
+        case CLUSTEN_F32: return scatter_tiles_t<float>(label, p, s);
+        case CLUSTEN_F16: return scatter_tiles_t<__half>(label, p, s);
+        case CLUSTEN_BF16: return scatter_tiles_t<__nv_bfloat16>(label, p, s);
+        default: return CLUSTEN_ERR_DTYPE;
+    }
 }
 
 }  // namespace
@@ -1092,12 +1134,33 @@ bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void
 }
 int launch_tiled_scatter(const char* label, int dtype, const void* W, const void* X, const int64_t* idx,
                          const InverseView& inv, void* out, int b, int h, int n, int m, cudaStream_t s) {
-    switch (dtype) {
-        case CLUSTEN_F32: return scatter_tiles_t<float>(label, W, X, idx, inv, out, b, h, n, m, s);
-        case CLUSTEN_F16: return scatter_tiles_t<__half>(label, W, X, idx, inv, out, b, h, n, m, s);
-        case CLUSTEN_BF16: return scatter_tiles_t<__nv_bfloat16>(label, W, X, idx, inv, out, b, h, n, m, s);
-        default: return CLUSTEN_ERR_DTYPE;
-    }
+    ScatterParams p{};
+    p.W = W;  p.w_batch = (long long)h * n * m;  p.w_head = (long long)n * m;
+    p.X = X;  p.x_batch = (long long)h * n * kC; p.x_head = (long long)n * kC;  p.x_row = kC;
+    p.out = out;  p.o_batch = p.x_batch;  p.o_head = p.x_head;  p.o_row = kC;
+    p.idx = idx;  p.idx_rows = n;  p.m = m;  p.inv = inv;  p.n_tgt = n;
+    p.ic = 1;  p.heads = h;  p.batch = b;
+    return scatter_dispatch(label, dtype, p, s);
+}
+
+// WF: d_feat[b, t, :] over c channels in slabs of 32; rows of X are d_feat_new[b, i, k, :]
+bool tiled_wf_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n_out, int n, int m,
+                                int ic, int c) {
+    if (dtype != CLUSTEN_F32 && dtype != CLUSTEN_F16 && dtype != CLUSTEN_BF16) return false;
+    if (c % kC != 0 || ic < 1 || ic > 16 || m < 1 || n < 1 || (long long)n_out * ic > 65000) return false;
+    return reinterpret_cast<uintptr_t>(X) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+           reinterpret_cast<uintptr_t>(W) % 4 == 0;
+}
+int launch_tiled_wf_scatter(const char* label, int dtype, const void* W, const void* X, const int64_t* idx,
+                            const InverseView& inv, void* out, int b, int n_out, int n, int m, int ic, int c,
+                            cudaStream_t s) {
+    ScatterParams p{};
+    p.W = W;  p.w_batch = (long long)n_out * m * ic;  p.w_head = 0;
+    p.X = X;  p.x_batch = (long long)n_out * ic * c;  p.x_head = kC;  p.x_row = c;
+    p.out = out;  p.o_batch = (long long)n * c;  p.o_head = kC;  p.o_row = c;
+    p.idx = idx;  p.idx_rows = n_out;  p.m = m;  p.inv = inv;  p.n_tgt = n;
+    p.ic = ic;  p.heads = c / kC;  p.batch = b;
+    return scatter_dispatch(label, dtype, p, s);
 }
 
 }  // namespace clusten
