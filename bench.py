@@ -35,6 +35,15 @@ for _p in (ROOT, PKG):
     if _p not in sys.path:
         sys.path.insert(0, _p)
 
+if "reference" in sys.argv:
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it may run on
+    try:
+        _cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        _cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(_cores)
+    os.environ["MKL_NUM_THREADS"] = str(_cores)
+
 import torch  # noqa: E402
 
 import workloads  # noqa: E402
@@ -442,7 +451,7 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
         "kernels": per_kernel,
         "e2e": {"value": world * total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                 "ms_per_step": e2e_ms, "h2d_bytes_per_step": e2e.h2d, "d2h_bytes_per_step": e2e.d2h},
-        "gpu_launches": launches,
+        "gpu_launches": launches * world,          # every rank launches the same kernels
         "clocks": clocks,
     }
     if world == 1:
