@@ -181,36 +181,77 @@ def device_step(ops, wl):
 
 
 class EndToEnd:
-    """The same step through the autograd operators with HOST buffers: pinned inputs are copied
-    to the device, the operators run forward and backward, results are copied back."""
+    """The same step through the autograd operators with HOST buffers: every step copies its pinned
+    inputs to the device, runs the operators forward and backward and copies all six results back to
+    pinned host memory.  Copies run on their own streams (inputs of the merge operator travel while the
+    attention operator computes, results travel while the next step's inputs arrive; device buffers are
+    double-buffered), the timed region ends when the last result of the last step is on the host."""
 
     def __init__(self, wl):
         self.host = {k: v.cpu().pin_memory() for k, v in wl.items()}
-        self.dev = {k: torch.empty_like(v) for k, v in wl.items()}
+        self.dev = [{k: torch.empty_like(v) for k, v in wl.items()} for _ in range(2)]
         self.out_host = None
         self.h2d = sum(v.numel() * v.element_size() for v in self.host.values())
         self.d2h = 0
+        self.s_in = torch.cuda.Stream()
+        self.s_out = torch.cuda.Stream()
+        self.step_no = 0
+        self.done = [None, None]          # compute-done event per device buffer set
 
     def step(self):
         from clusten import CLUSTENAVFunction, CLUSTENWFFunction, clear_inverse_cache
-        d = self.dev
-        for k, v in self.host.items():
-            d[k].copy_(v, non_blocking=True)
+        main = torch.cuda.current_stream()
+        slot = self.step_no & 1
+        self.step_no += 1
+        d = self.dev[slot]
+        av_keys, wf_keys = ("idx", "v", "attn", "g_feat"), ("idx_w", "w", "feat", "g_new")
+        with torch.cuda.stream(self.s_in):
+            if self.done[slot] is not None:
+                self.s_in.wait_event(self.done[slot])      # the kernels that read this buffer set are finished
+            for k in av_keys:
+                d[k].copy_(self.host[k], non_blocking=True)
+            ev_av = torch.cuda.Event()
+            ev_av.record(self.s_in)
+            for k in wf_keys:
+                d[k].copy_(self.host[k], non_blocking=True)
+            ev_wf = torch.cuda.Event()
+            ev_wf.record(self.s_in)
         clear_inverse_cache()
+        main.wait_event(ev_av)
         attn = d["attn"].detach().requires_grad_(True)
         v = d["v"].detach().requires_grad_(True)
         feat = CLUSTENAVFunction.apply(attn, v, d["idx"])
         feat.backward(d["g_feat"])
+        res_av = [feat.detach(), attn.grad, v.grad]
+        ev_av_done = torch.cuda.Event()
+        ev_av_done.record(main)
+        main.wait_event(ev_wf)
         w = d["w"].detach().requires_grad_(True)
         f = d["feat"].detach().requires_grad_(True)
         out = CLUSTENWFFunction.apply(w, f, d["idx_w"])
         out.backward(d["g_new"])
-        results = [feat.detach(), attn.grad, v.grad, out.detach(), w.grad, f.grad]
+        res_wf = [out.detach(), w.grad, f.grad]
+        ev_done = torch.cuda.Event()
+        ev_done.record(main)
+        self.done[slot] = ev_done
+        results = res_av + res_wf
         if self.out_host is None:
             self.out_host = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in results]
             self.d2h = sum(r.numel() * r.element_size() for r in results)
-        for hbuf, r in zip(self.out_host, results):
-            hbuf.copy_(r, non_blocking=True)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(ev_av_done)
+            for hbuf, r in zip(self.out_host[:3], res_av):
+                hbuf.copy_(r, non_blocking=True)
+                r.record_stream(self.s_out)
+            self.s_out.wait_event(ev_done)
+            for hbuf, r in zip(self.out_host[3:], res_wf):
+                hbuf.copy_(r, non_blocking=True)
+                r.record_stream(self.s_out)
+
+    def finish(self):
+        """Make the current stream wait for all copies (call before the closing timing event)."""
+        torch.cuda.current_stream().wait_stream(self.s_out)
+        torch.cuda.current_stream().wait_stream(self.s_in)
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -408,11 +449,13 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
     e2e = EndToEnd(wl)
     for _ in range(min(args.warmup, 3)):
         e2e.step()
+    e2e.finish()
     barrier()
     e_steps = max(1, min(args.steps, 10))
     start.record()
     for _ in range(e_steps):
         e2e.step()
+    e2e.finish()
     stop.record()
     barrier()
     clocks = sampler.stop()
