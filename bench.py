@@ -93,6 +93,7 @@ def kernel_bytes(cfg, esize):
         "wf_d_weights": f + o + iw + w,
         "wf_d_feat": w + o + f,
         "inverse_build": idx + iw,                    # both neighbour tables, once each
+        "wf_order": b * n_out * (8 + 4),              # first neighbour of every row -> permutation
     }
 
 
@@ -174,9 +175,12 @@ def device_step(ops, wl):
     feat = ops.av_forward(wl["attn"], wl["v"], wl["idx"])
     inv = ops.build_inverse(wl["idx"], n)
     d_attn, d_v = ops.av_backward(wl["g_feat"], wl["attn"], wl["v"], wl["idx"], inv)
-    out = ops.wf_forward(wl["w"], wl["feat"], wl["idx_w"])
+    order = ops.build_row_order(wl["idx_w"])
+    if order is None:
+        order = False
+    out = ops.wf_forward(wl["w"], wl["feat"], wl["idx_w"], order)
     inv_w = ops.build_inverse(wl["idx_w"], n)
-    d_w, d_f = ops.wf_backward(wl["g_new"], wl["w"], wl["feat"], wl["idx_w"], inv_w)
+    d_w, d_f = ops.wf_backward(wl["g_new"], wl["w"], wl["feat"], wl["idx_w"], inv_w, order)
     return feat, d_attn, d_v, out, d_w, d_f
 
 

@@ -56,7 +56,7 @@ enum {
     CLUSTEN_ERR_SHAPE = -2,       /* a size is <= 0 or a product overflows int32 */
     CLUSTEN_ERR_NULL = -3,        /* a required pointer is NULL */
     CLUSTEN_ERR_ALIGN = -4,       /* a pointer is not aligned to its element size */
-    CLUSTEN_ERR_WORKSPACE = -5,   /* inverse-index buffer too small or not built for these sizes */
+    CLUSTEN_ERR_WORKSPACE = -5,   /* inverse-index or row-order buffer too small or not built for these sizes */
     CLUSTEN_ERR_UNSUPPORTED = -6, /* size outside what the kernels handle (see the function) */
     CLUSTEN_ERR_CUDA = -7,        /* the CUDA runtime reported an error at launch */
     CLUSTEN_ERR_NOALLOC_CAPACITY = -8 /* clusten_av_backward_noalloc: sizes exceed the built-in array */
@@ -166,15 +166,30 @@ CLUSTEN_API int clusten_av_backward_noalloc(const void* d_feat, const void* attn
  * replaces clusten_wf_forward (clusten/src/clustenwf_cuda.cpp:25-33, kernel
  * clustenwf_cuda_kernel.cu:18-53).  n_out = n_ (rows of weights / nbhd_idx).
  * ---------------------------------------------------------------------- */
-CLUSTEN_API int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx, void* feat_new,
-                       int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream);
+CLUSTEN_API int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx,
+                                   const void* row_order, void* feat_new,
+                                   int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream);
+
+/* Row order for the WF kernels: a permutation of the n_out rows of every batch
+ * element (int32 [b][n_out]) that puts rows with nearby neighbourhoods next to
+ * each other, so that one warp's 8 rows share most of the feature rows they
+ * gather.  The reference has no such step: its merge centres come out of an
+ * unsorted top-k (models/aff_transformer.py:320-336) and its kernel gathers
+ * every feature row once per (row, neighbour, ic) (clustenwf_cuda_kernel.cu:41-47).
+ * The order depends on nbhd_idx only; build it once per nbhd_idx and pass it as
+ * row_order to clusten_wf_forward / clusten_wf_backward.  row_order may be NULL:
+ * the rows are then taken in storage order (same results, more traffic).
+ * n_out above 4096 is not handled (CLUSTEN_ERR_UNSUPPORTED): pass NULL then. */
+CLUSTEN_API size_t clusten_wf_order_bytes(int b, int n_out);
+CLUSTEN_API int clusten_wf_order_build(const int64_t* nbhd_idx, int b, int n_out, int m,
+                                       void* row_order, size_t row_order_bytes, void* stream);
 
 /* d_weights[b,i,j,ic] = sum_c feat[b,idx,c] * d_feat_new[b,i,ic,c]
  * d_feat[b,t,c] = sum_{(i,j): idx[b,i,j]==t} sum_ic d_feat_new[b,i,ic,c] * weights[b,i,j,ic]
  * replaces clusten_wf_backward (clustenwf_cuda.cpp:35-45, kernels :96-169).
  * inverse: built by clusten_inverse_build(nbhd_idx, b, n_out, m, n, ...). */
 CLUSTEN_API int clusten_wf_backward(const void* d_feat_new, const void* weights, const void* feat,
-                        const int64_t* nbhd_idx, const void* inverse,
+                        const int64_t* nbhd_idx, const void* inverse, const void* row_order,
                         void* d_weights, void* d_feat,
                         int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream);
 

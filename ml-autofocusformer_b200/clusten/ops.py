@@ -78,9 +78,14 @@ class _InverseCache:
 _cache = _InverseCache(int(os.environ.get("CLUSTEN_INVERSE_CACHE", "4")))
 
 
+_order_cache = _InverseCache(int(os.environ.get("CLUSTEN_INVERSE_CACHE", "4")))
+_ORDER_MAX_ROWS = 4096     # clusten_wf_order_build sorts one batch element in shared memory
+
+
 def clear_inverse_cache():
-    """Drop every cached inverse index (and the index tensors they pin)."""
+    """Drop every cached inverse index and row order (and the index tensors they pin)."""
     _cache.clear()
+    _order_cache.clear()
 
 
 def build_inverse(nbhd_idx, n_targets):
@@ -108,6 +113,45 @@ def inverse_for(nbhd_idx, n_targets):
         inv = build_inverse(nbhd_idx, n_targets)
         _cache.put(nbhd_idx, n_targets, inv)
     return inv
+
+
+def build_row_order(nbhd_idx):
+    """Row order for the WF kernels: int32 [b, n_out] permutation that puts rows with nearby
+    neighbourhoods next to each other; None when n_out is more than the sort handles."""
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, rows, m = nbhd_idx.shape
+    if rows > _ORDER_MAX_ROWS:
+        return None
+    lib = _lib.load()
+    nbytes = lib.clusten_wf_order_bytes(b, rows)
+    order = torch.empty(nbytes // 4, dtype=torch.int32, device=nbhd_idx.device)
+    with torch.cuda.device_of(nbhd_idx):
+        _lib.check(lib.clusten_wf_order_build(nbhd_idx.data_ptr(), b, rows, m, order.data_ptr(), nbytes,
+                                              _stream(nbhd_idx)))
+    return order.view(b, rows)
+
+
+def row_order_for(nbhd_idx):
+    """Cached build_row_order."""
+    if _order_cache.capacity <= 0 or nbhd_idx.shape[1] > _ORDER_MAX_ROWS:
+        return build_row_order(nbhd_idx)
+    order = _order_cache.get(nbhd_idx, "order")
+    if order is None:
+        order = build_row_order(nbhd_idx)
+        _order_cache.put(nbhd_idx, "order", order)
+    return order
+
+
+def _order_ptr(row_order, nbhd_idx):
+    """row_order argument -> (tensor kept alive, pointer): None = cached order, False = storage order."""
+    if row_order is None:
+        row_order = row_order_for(nbhd_idx)
+    if row_order is None or row_order is False:
+        return None, None
+    if row_order.dtype != torch.int32 or row_order.numel() != nbhd_idx.shape[0] * nbhd_idx.shape[1] \
+            or not row_order.is_contiguous() or row_order.device != nbhd_idx.device:
+        raise RuntimeError("clusten: row_order must be a contiguous int32 [b, n_out] tensor on the inputs' device")
+    return row_order, row_order.data_ptr()
 
 
 # ----------------------------------------------------------------------------- QK
@@ -185,8 +229,10 @@ def av_backward(d_feat, attn, value, nbhd_idx, inverse=None):
 
 
 # ----------------------------------------------------------------------------- WF
-def wf_forward(weights, feat, nbhd_idx):
-    """feat_new[b,i,ic,:] = sum_j weights[b,i,j,ic] * feat[b,nbhd_idx[b,i,j],:]"""
+def wf_forward(weights, feat, nbhd_idx, row_order=None):
+    """feat_new[b,i,ic,:] = sum_j weights[b,i,j,ic] * feat[b,nbhd_idx[b,i,j],:]
+
+    row_order: None = the cached order of nbhd_idx, False = storage order, or a build_row_order tensor."""
     _chk("weights", weights, dim=4)
     _chk("feat", feat, weights.dtype, 3)
     _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
@@ -195,14 +241,15 @@ def wf_forward(weights, feat, nbhd_idx):
     if feat.shape[0] != b or nbhd_idx.shape != (b, n_out, m):
         raise RuntimeError("clusten: WF shape mismatch")
     feat_new = torch.empty((b, n_out, ic, c), dtype=weights.dtype, device=weights.device)
+    order, order_ptr = _order_ptr(row_order, nbhd_idx)
     with torch.cuda.device_of(weights):
         _lib.check(_lib.load().clusten_wf_forward(
-            weights.data_ptr(), feat.data_ptr(), nbhd_idx.data_ptr(), feat_new.data_ptr(),
+            weights.data_ptr(), feat.data_ptr(), nbhd_idx.data_ptr(), order_ptr, feat_new.data_ptr(),
             b, n_out, n, m, ic, c, _dt(weights), _stream(weights)))
     return feat_new
 
 
-def wf_backward(d_feat_new, weights, feat, nbhd_idx, inverse=None):
+def wf_backward(d_feat_new, weights, feat, nbhd_idx, inverse=None, row_order=None):
     _chk("d_feat_new", d_feat_new, weights.dtype, 4)
     _chk("weights", weights, dim=4)
     _chk("feat", feat, weights.dtype, 3)
@@ -215,9 +262,10 @@ def wf_backward(d_feat_new, weights, feat, nbhd_idx, inverse=None):
         inverse = inverse_for(nbhd_idx, n)
     d_weights = torch.empty_like(weights)
     d_feat = torch.empty_like(feat)
+    order, order_ptr = _order_ptr(row_order, nbhd_idx)
     with torch.cuda.device_of(weights):
         _lib.check(_lib.load().clusten_wf_backward(
             d_feat_new.data_ptr(), weights.data_ptr(), feat.data_ptr(), nbhd_idx.data_ptr(),
-            inverse.data_ptr(), d_weights.data_ptr(), d_feat.data_ptr(),
+            inverse.data_ptr(), order_ptr, d_weights.data_ptr(), d_feat.data_ptr(),
             b, n_out, n, m, ic, c, _dt(weights), _stream(weights)))
     return d_weights, d_feat

@@ -280,8 +280,22 @@ int clusten_av_backward(const void* d_feat, const void* attn, const void* value,
     return launch_scatter_sum("av_d_value", dtype, attn, d_feat, nbhd_idx, inv, d_value, b * h, h, n, n, m, 1, c, s);
 }
 
-int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx, void* feat_new, int b,
-                       int n_out, int n, int m, int ic, int c, int dtype, void* stream) {
+size_t clusten_wf_order_bytes(int b, int n_out) {
+    if (b < 1 || n_out < 1) return 0;
+    return wf_order_bytes(b, n_out);
+}
+
+int clusten_wf_order_build(const int64_t* nbhd_idx, int b, int n_out, int m, void* row_order, size_t row_order_bytes,
+                           void* stream) {
+    if (b < 1 || n_out < 1 || m < 1) return CLUSTEN_ERR_SHAPE;
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(row_order, 4);
+    if (row_order_bytes < wf_order_bytes(b, n_out)) return CLUSTEN_ERR_WORKSPACE;
+    return launch_wf_order(nbhd_idx, b, n_out, m, static_cast<int*>(row_order), (cudaStream_t)stream);
+}
+
+int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbhd_idx, const void* row_order,
+                       void* feat_new, int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream) {
     const int st = check_wf_args(b, n_out, n, m, ic, c, dtype);
     if (st != CLUSTEN_OK) return st;
     const size_t es = dtype_size(dtype);
@@ -289,13 +303,17 @@ int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbh
     CLUSTEN_REQUIRE_PTR(feat, es);
     CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
     CLUSTEN_REQUIRE_PTR(feat_new, es);
+    if (row_order && reinterpret_cast<uintptr_t>(row_order) % 4 != 0) return CLUSTEN_ERR_ALIGN;
+    if (tiled_wf_sum_supported(dtype, weights, feat, feat_new, n_out, n, m, ic, c))
+        return launch_tiled_wf_sum("wf_forward", dtype, weights, feat, nbhd_idx, static_cast<const int*>(row_order),
+                                   feat_new, b, n_out, n, m, ic, c, (cudaStream_t)stream);
     return launch_gather_sum("wf_forward", dtype, weights, feat, nbhd_idx, feat_new, b, 1, n_out, n, m, ic, c,
                              (cudaStream_t)stream);
 }
 
 int clusten_wf_backward(const void* d_feat_new, const void* weights, const void* feat, const int64_t* nbhd_idx,
-                        const void* inverse, void* d_weights, void* d_feat, int b, int n_out, int n, int m,
-                        int ic, int c, int dtype, void* stream) {
+                        const void* inverse, const void* row_order, void* d_weights, void* d_feat, int b, int n_out,
+                        int n, int m, int ic, int c, int dtype, void* stream) {
     int st = check_wf_args(b, n_out, n, m, ic, c, dtype);
     if (st != CLUSTEN_OK) return st;
     st = check_inverse_args(b, n_out, m, n);
