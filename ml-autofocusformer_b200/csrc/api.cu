@@ -304,7 +304,7 @@ int clusten_wf_forward(const void* weights, const void* feat, const int64_t* nbh
     CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
     CLUSTEN_REQUIRE_PTR(feat_new, es);
     if (row_order && reinterpret_cast<uintptr_t>(row_order) % 4 != 0) return CLUSTEN_ERR_ALIGN;
-    if (tiled_wf_sum_supported(dtype, weights, feat, feat_new, n_out, n, m, ic, c))
+    if (tiled_wf_gather_supported(dtype, weights, feat, feat_new, n_out, n, m, ic, c))
         return launch_tiled_wf_sum("wf_forward", dtype, weights, feat, nbhd_idx, static_cast<const int*>(row_order),
                                    feat_new, b, n_out, n, m, ic, c, (cudaStream_t)stream);
     return launch_gather_sum("wf_forward", dtype, weights, feat, nbhd_idx, feat_new, b, 1, n_out, n, m, ic, c,
@@ -328,7 +328,12 @@ int clusten_wf_backward(const void* d_feat_new, const void* weights, const void*
     CLUSTEN_REQUIRE_PTR(d_feat, es);
     cudaStream_t s = (cudaStream_t)stream;
     const InverseView inv = inverse_view(inverse, b, n_out, m, n);
-    st = launch_gather_dot("wf_d_weights", dtype, feat, d_feat_new, nbhd_idx, d_weights, b, 1, n_out, n, m, ic, c, s);
+    if (row_order && reinterpret_cast<uintptr_t>(row_order) % 4 != 0) return CLUSTEN_ERR_ALIGN;
+    if (tiled_wf_gather_supported(dtype, d_weights, feat, d_feat_new, n_out, n, m, ic, c))
+        st = launch_tiled_wf_dot("wf_d_weights", dtype, feat, d_feat_new, nbhd_idx, static_cast<const int*>(row_order),
+                                 d_weights, b, n_out, n, m, ic, c, s);
+    else
+        st = launch_gather_dot("wf_d_weights", dtype, feat, d_feat_new, nbhd_idx, d_weights, b, 1, n_out, n, m, ic, c, s);
     if (st != CLUSTEN_OK) return st;
     if (tiled_wf_scatter_supported(dtype, weights, d_feat_new, d_feat, n_out, n, m, ic, c))
         return launch_tiled_wf_scatter("wf_d_feat", dtype, weights, d_feat_new, nbhd_idx, inv, d_feat, b, n_out, n, m,

@@ -365,7 +365,7 @@ __device__ int dedup_tokens(const DedupScratch ps_, unsigned short* lut, int E, 
         for (int x = lane; x < E; x += 32) {
             const unsigned short t = ps->tok[x];
             lut[x] = t != kSkip ? (unsigned short)x : kSkip;
-            ps->uniq[x] = t;
+            ps->uniq[x] = t != kSkip ? t : (unsigned short)0;      // a slot nobody refers to: any valid row
         }
         __syncwarp();
         return E;

@@ -29,8 +29,11 @@ int launch_tiled_wf_scatter(const char* label, int dtype, const void* W, const v
 // WF gather side, tiles of 8 rows taken in row_order (nullptr = storage order)
 size_t wf_order_bytes(int b, int n_out);
 int launch_wf_order(const int64_t* idx, int b, int n_out, int m, int* order, cudaStream_t s);
-bool tiled_wf_sum_supported(int dtype, const void* W, const void* F, const void* out, int n_out, int n, int m, int ic,
-                            int c);
+bool tiled_wf_gather_supported(int dtype, const void* W, const void* F, const void* O, int n_out, int n, int m,
+                               int ic, int c);
+int launch_tiled_wf_dot(const char* label, int dtype, const void* F, const void* G, const int64_t* idx,
+                        const int* order, void* d_weights, int b, int n_out, int n, int m, int ic, int c,
+                        cudaStream_t s);
 int launch_tiled_wf_sum(const char* label, int dtype, const void* W, const void* F, const int64_t* idx,
                         const int* order, void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s);
 

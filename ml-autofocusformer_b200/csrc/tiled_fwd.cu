@@ -331,6 +331,9 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
 // inverse-index segments (512 edges at a time), de-duplicates the SOURCE rows, stages each once per
 // 32-channel slab ("head") and multiplies the dense [8 x U] weights on the tensor cores.  Segments
 // are ordered by source row and slots ascend with the source row, so the summation order is fixed.
+// Tiles whose 8 targets are listed by the same rows (neighbourhoods made of whole clusters) skip the
+// de-duplication: lane l works for target l % 8, so the 8 weights of one source row, which sit side
+// by side in memory, are read by neighbouring lanes.
 // QK / AV: ic = 1, a slab is a head.  WF: a slab is 32 of the c channels, the weights are shared by
 // the slabs and every entry fans out into its ic (weight, row) pairs.
 struct ScatterParams {
@@ -408,66 +411,54 @@ scatter_tiles_kernel(const ScatterParams p) {
     };
     int next_len, next_start;
     load_segment(blockIdx.x * kWarps + warp, next_len, next_start);
+    const int myq = lane & 7, psub = lane >> 3;
     for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
         const int b = (int)(task / (unsigned)p.tiles);
         const int t0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
         const int64_t* idx_b = p.idx + (long long)b * p.idx_rows * m;
         const int* entries = p.inv.entries + (long long)b * p.idx_rows * m;
-        const int len = next_len * ic, start = next_start;      // every entry fans out into ic edges
+        const int len = next_len, start = next_start;
         load_segment(task + nwarps, next_len, next_start);      // in flight while this tile is worked on
-        int incl = len;
+        const int qlen = __shfl_sync(kFull, len, myq);          // entries of this lane's target
+        const int* qent = entries + __shfl_sync(kFull, start, myq);
+        int maxlen = len;
 #pragma unroll
-        for (int o = 1; o < kT; o <<= 1) {
-            const int y = __shfl_up_sync(kFull, incl, o);
-            if (lane >= o) incl += y;
-        }
-        const int E_total = __shfl_sync(kFull, incl, kT - 1);
-        int off[kT], st[kT];                                    // per tile row: offset in the edge list, segment start
-#pragma unroll
-        for (int r = 0; r < kT; ++r) {
-            off[r] = __shfl_sync(kFull, incl - len, r);
-            st[r] = __shfl_sync(kFull, start, r);
-        }
+        for (int o = 4; o > 0; o >>= 1) maxlen = max(maxlen, __shfl_xor_sync(kFull, maxlen, o));
+        maxlen = __shfl_sync(kFull, maxlen, 0);
+        T* Ob = Og + (long long)b * p.o_batch;
 
         // ---- uniform tile: the 8 targets are listed by the same source rows, once each (the 8 tokens of
-        //      a cluster always are: every neighbour list that holds one of them holds the whole run).
-        //      The dense weights are then read straight through the entries; nothing to de-duplicate.
-        const int L = __shfl_sync(kFull, len, 0) / ic;                       // entries per target
-        bool uniform = t0 + kT <= n_tgt && L > 0 && ic <= kUC && __all_sync(kFull, lane >= kT || len == L * ic);
-        if (uniform) {
-            bool same = true;
-            for (int r = lane; r < L; r += 32) {
-                const unsigned e0v = (unsigned)__ldg(entries + st[0] + r);
-                const unsigned row0 = fast_div(e0v & ~kDupFlag, p.m_magic, p.m_shift);
-                unsigned flags = e0v;
-#pragma unroll
-                for (int q = 1; q < kT; ++q) {
-                    const unsigned e = (unsigned)__ldg(entries + st[q] + r);
-                    flags |= e;
-                    same = same && fast_div(e & ~kDupFlag, p.m_magic, p.m_shift) == row0;
-                }
-                same = same && !(flags & kDupFlag);
+        //      a cluster always are when neighbourhoods are made of whole clusters).  The dense weights
+        //      are then read straight through the entries; nothing to de-duplicate.
+        bool uniform = t0 + kT <= n_tgt && maxlen > 0 && ic <= kUC && qlen == maxlen;
+        if (__all_sync(kFull, uniform)) {
+            for (int r0 = 0; r0 < maxlen; r0 += 4) {                         // all lanes take every trip
+                const int r = min(r0 + psub, maxlen - 1);
+                const unsigned e = (unsigned)__ldg(qent + r);
+                const unsigned row = fast_div(e & ~kDupFlag, p.m_magic, p.m_shift);
+                const unsigned row0 = __shfl_sync(kFull, row, lane & 24);       // target 0's row, same position
+                uniform = uniform && !(e & kDupFlag) && row == row0;
             }
-            uniform = __all_sync(kFull, same);
+            uniform = __all_sync(kFull, uniform);
+        } else {
+            uniform = false;
         }
         if (uniform) {
-            const int per = kUC / ic;                                        // entries per pass (ic divides 48 or wastes a few rows)
-            for (int r0 = 0; r0 < L; r0 += per) {
-                const int Lc = min(per, L - r0);
+            const int per = kUC / ic;                                        // entries per pass
+            for (int r0 = 0; r0 < maxlen; r0 += per) {
+                const int Lc = min(per, maxlen - r0);
                 const int Uc = Lc * ic;                                      // source rows of this pass
                 const int rows8 = (Uc + 7) & ~7;
                 __syncwarp();
-                // weight index of every (target, entry) and the source rows
-#pragma unroll
-                for (int q = 0; q < kT; ++q)
-                    for (int r = lane; r < Lc; r += 32) {
-                        const unsigned plain = (unsigned)__ldg(entries + st[q] + r0 + r);
-                        edge[q * kUC + r] = plain * (unsigned)ic;
-                        if (q == 0) {
-                            const unsigned src = fast_div(plain, p.m_magic, p.m_shift) * (unsigned)ic;
-                            for (int k = 0; k < ic; ++k) uniq[r * ic + k] = (unsigned short)(src + k);
-                        }
+                // weight index of every (entry, target) and the source rows
+                for (int r = psub; r < Lc; r += 4) {
+                    const unsigned plain = (unsigned)__ldg(qent + r0 + r);
+                    edge[r * kT + myq] = plain * (unsigned)ic;
+                    if (myq == 0) {
+                        const unsigned src = fast_div(plain, p.m_magic, p.m_shift) * (unsigned)ic;
+                        for (int k = 0; k < ic; ++k) uniq[r * ic + k] = (unsigned short)(src + k);
                     }
+                }
                 __syncwarp();
                 for (int g = 0; g < p.heads; ++g) {
                     const T* Wh = Wg + (long long)b * p.w_batch + (long long)g * p.w_head;
@@ -496,16 +487,16 @@ scatter_tiles_kernel(const ScatterParams p) {
                     }
                     cp_async_commit();
                     if (g == 0 || p.w_head != 0) {
-#pragma unroll
-                        for (int q = 0; q < kT; ++q)
-                            for (int rr = lane; rr < rows8; rr += 32) {
-                                float w = 0.f;
-                                if (rr < Uc) {
-                                    const unsigned r = fast_div((unsigned)rr, p.ic_magic, p.ic_shift);
-                                    w = Elem<T>::up(Wh[edge[q * kUC + r] + ((unsigned)rr - r * (unsigned)ic)]);
-                                }
-                                Wd[q * kWLD + rr] = w;
+                        // dense weights [8][rows8]: lanes of one source row read neighbouring weights
+#pragma unroll 4
+                        for (int rr = psub; rr < rows8; rr += 4) {
+                            float w = 0.f;
+                            if (rr < Uc) {
+                                const unsigned r = fast_div((unsigned)rr, p.ic_magic, p.ic_shift);
+                                w = Elem<T>::up(Wh[edge[r * kT + myq] + ((unsigned)rr - r * (unsigned)ic)]);
                             }
+                            Wd[myq * kWLD + rr] = w;
+                        }
                     }
                     cp_async_wait<0>();
                     __syncwarp();
@@ -533,7 +524,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                         o[kOLD + 8] = acc[mt][3];
                     }
                     __syncwarp();
-                    T* Oh = Og + (long long)b * p.o_batch + (long long)g * p.o_head;
+                    T* Oh = Ob + (long long)g * p.o_head;
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
                         const int q = 2 * qi + a;
@@ -551,6 +542,21 @@ scatter_tiles_kernel(const ScatterParams p) {
             continue;
         }
 
+        // ---- general tile: the fanned-out segments of the 8 targets, concatenated, kES edges at a time
+        const int flen = len * ic;                              // lanes 0..7: edges of target `lane`
+        int incl = flen;
+#pragma unroll
+        for (int o = 1; o < kT; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += y;
+        }
+        const int E_total = __shfl_sync(kFull, incl, kT - 1);
+        int off[kT], st[kT];                                    // per tile row: offset in the edge list, segment start
+#pragma unroll
+        for (int r = 0; r < kT; ++r) {
+            off[r] = __shfl_sync(kFull, incl - flen, r);
+            st[r] = __shfl_sync(kFull, start, r);
+        }
         for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kES) {
             const int E = max(0, min(kES, E_total - e0));
             // ---- this chunk's edges: weight index (flagged when the target repeats in its row), source

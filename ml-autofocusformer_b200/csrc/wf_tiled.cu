@@ -7,15 +7,15 @@
 // picks them with an unsorted top-k), so consecutive rows of nbhd_idx share nothing.  A small pre-pass
 // orders the rows of each batch element by their first neighbour (wf_order_kernel, bitonic sort in
 // shared memory); a warp then takes 8 rows that are adjacent in that order -- spatial neighbours -- and,
-// as in the attention kernels, de-duplicates their 8 x m indices, stages every distinct feature row once
-// per 32-channel slab and multiplies on the tensor cores.  The reference gathers every feature row ic
-// times per output (clusten/src/clustenwf_cuda_kernel.cu:41-47).
+// as in the attention kernels, de-duplicates their 8 x m indices (about 100 distinct rows instead of
+// 384), stages every distinct feature row once, 32 rows x 64 channels at a time, and multiplies on the
+// tensor cores against the dense [8 ic x 32] weights (forward) or the [8 ic x 64] gradient tile
+// (d_weights).  The reference gathers every feature row ic times per output and neighbour
+// (clusten/src/clustenwf_cuda_kernel.cu:41-47, :118-126).
 #include "tile_core.cuh"
 
 namespace clusten {
 namespace {
-
-constexpr int kMaxIC = 4;
 
 // ----------------------------------------------------------------------------- row order
 constexpr int kOrderMax = 4096;     // rows per batch element that the shared-memory sort handles
@@ -53,54 +53,154 @@ wf_order_kernel(const int64_t* __restrict__ idx, int* __restrict__ order, int n_
     for (int i = tid; i < n_out; i += blockDim.x) order[(long long)b * n_out + i] = (int)(keys[i] & 0xffffu);
 }
 
-// ----------------------------------------------------------------------------- shared pieces
+// ----------------------------------------------------------------------------- tiles
+constexpr int kUW = 32;             // distinct feature rows per stage
+constexpr int kCG = 64;             // channels per stage
+constexpr int kDL = 36;             // row stride (floats) of the dense weight tile and of the score tile, [32][kDL]
+constexpr int kGL = 68;             // row stride (floats) of the gradient tile [32][kGL] and of the output tile [8][kGL]
+constexpr int kRowsM = 32;          // (ic, row) pairs of a tile: M of the d_weights product, N of the forward one
+
 struct WfParams {
-    const void* W;        // [b, n_out, m, ic]   (wf_dot: output d_weights)
-    const void* F;        // [b, n, c]
+    const void* W;        // wf_sum: weights [b, n_out, m, ic]
+    const void* F;        // feat [b, n, c]
     const void* G;        // wf_dot: d_feat_new [b, n_out, ic, c]
-    void* out;            // wf_sum: feat_new [b, n_out, ic, c];  wf_dot: d_weights
+    void* out;            // wf_sum: feat_new [b, n_out, ic, c];  wf_dot: d_weights [b, n_out, m, ic]
     const int64_t* idx;   // [b, n_out, m]
-    const int* order;     // [b, n_out] or nullptr (identity)
-    int batch, n_out, n, m, ic, c, tiles;
+    const int* order;     // [b, n_out] or nullptr (storage order)
+    int batch, n_out, n, m, c, tiles;
 };
 
-// per-warp shared memory:  X rows [48][32] fp32 (front: landed indices) | Xraw (16-bit inputs) |
-//                          Op: dense weights [8 ic][kWLD] (wf_sum) or Y [8 ic][kYLD] + scores [8 ic][kWLD] (wf_dot)
-//                          | lut | uniq
-template <typename T, int MODE> struct WfSmem {
-    static constexpr bool kIsFloat = std::is_same<T, float>::value;
-    static constexpr int kX = kUC * kC * 4;
-    static constexpr int kXraw = kIsFloat ? 0 : kUC * kC * (int)sizeof(T);
-    static constexpr int kOp = MODE == 0 ? kT * kMaxIC * kWLD * 4 : kT * kMaxIC * (kYLD + kWLD) * 4;
+// per-warp shared memory
+//   X    feature rows [32][64] fp32 (16-byte chunks XOR-swizzled with the row); before that the landing
+//        area of the tile's indices and the token scratch; afterwards the output tile (wf_sum) or the
+//        score tile (wf_dot)
+//   Op   wf_sum: dense weights [8 ic][kDL];  wf_dot: gradient tile [8 ic][kGL];  bitmap scratch before that
+//   lut  edge -> slot | tile row << 12,  uniq  slot -> feature row,  rows  the tile's 8 row numbers
+template <int MODE> struct WfSmem {
+    static constexpr int kX = kUW * kCG * 4;
+    static constexpr int kOp = MODE == 0 ? kRowsM * kDL * 4 : kRowsM * kGL * 4;
     static constexpr int kLut = kE * 2;
-    static constexpr int kTotal = kX + kXraw + kOp + 2 * kLut;
+    static constexpr int kRows = 32;
+    static constexpr int kTotal = kX + kOp + 2 * kLut + kRows;
 };
+static_assert(kE * 8 + kE * 2 <= kUW * kCG * 4, "indices and token scratch must fit in the row buffer");
+static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= kRowsM * kDL * 4, "bitmap scratch must fit in Op");
+static_assert(kRowsM * kDL * 4 <= kUW * kCG * 4 && kT * kGL * 4 <= kUW * kCG * 4, "score / output tile must fit in X");
 
-// three-pass product with operands that are already split
-__device__ __forceinline__ void mma3(float (&d)[4], const unsigned (&ah)[4], const unsigned (&al)[4],
-                                     const unsigned (&bh)[2], const unsigned (&bl)[2]) {
-    mma_tf32(d, al, bh);
-    mma_tf32(d, ah, bl);
+#define WF_LDS(dst, addr, off) asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(dst) : "r"((addr) + (unsigned)(off)))
+
+template <bool SPLIT> __device__ __forceinline__ void wf_split(float x, unsigned& hi, unsigned& lo) {
+    if (SPLIT) {
+        split_tf32(x, hi, lo);
+    } else {
+        hi = __float_as_uint(x);
+        lo = 0u;
+    }
+}
+template <bool SPLIT>
+__device__ __forceinline__ void wf_mma(float (&d)[4], const unsigned (&ah)[4], const unsigned (&al)[4],
+                                       const unsigned (&bh)[2], const unsigned (&bl)[2]) {
+    if (SPLIT) {
+        mma_tf32(d, al, bh);
+        mma_tf32(d, ah, bl);
+    }
     mma_tf32(d, ah, bh);
 }
 
-// ----------------------------------------------------------------------------- kernel
-// MODE 0: wf_sum, MODE 1: wf_dot.  ICT = ic (1, 2 or 4).
+// 8 elements of T -> two float4
+__device__ __forceinline__ void up8(const uint4 r, const __half*, float4& a, float4& b) {
+    const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+    const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+    const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&r.z));
+    const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&r.w));
+    a = make_float4(p0.x, p0.y, p1.x, p1.y);
+    b = make_float4(p2.x, p2.y, p3.x, p3.y);
+}
+__device__ __forceinline__ void up8(const uint4 r, const __nv_bfloat16*, float4& a, float4& b) {
+    a = make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                    __uint_as_float(r.y & 0xffff0000u));
+    b = make_float4(__uint_as_float(r.z << 16), __uint_as_float(r.z & 0xffff0000u), __uint_as_float(r.w << 16),
+                    __uint_as_float(r.w & 0xffff0000u));
+}
+
+// Stage rows8 rows of 64 channels into Xs (fp32, chunk c of row r at chunk ^ swz(r)); rows past n_rows
+// are zero.  src(r) gives the global address of row r's 64 channels.  SWZ 0: (r & 3) << 1, 1: r & 7.
+template <typename T, int SWZ, typename SrcFn>
+__device__ __forceinline__ void stage_rows64(float* Xs, int rows8, int n_rows, int lane, SrcFn src) {
+    if constexpr (std::is_same<T, float>::value) {
+        const int rsub = lane >> 4, ch = lane & 15;
+#pragma unroll 4
+        for (int i = 0; i < kUW / 2; ++i) {
+            const int r = 2 * i + rsub;
+            if (r < rows8) {
+                const int s = SWZ == 0 ? ((r & 3) << 1) : (r & 7);
+                float* dst = Xs + r * kCG + ((ch ^ s) << 2);
+                if (r < n_rows) cp_async16_cg(dst, src(r) + ch * 4);
+                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    } else {
+        const int rsub = lane >> 3, c8 = lane & 7;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            uint4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = 4 * (4 * half + i) + rsub;
+                v[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (r < n_rows) v[i] = *reinterpret_cast<const uint4*>(src(r) + c8 * 8);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = 4 * (4 * half + i) + rsub;
+                if (r < rows8) {
+                    const int s = SWZ == 0 ? ((r & 3) << 1) : (r & 7);
+                    float4 a, b;
+                    up8(v[i], static_cast<const T*>(nullptr), a, b);
+                    *reinterpret_cast<float4*>(Xs + r * kCG + (((2 * c8) ^ s) << 2)) = a;
+                    *reinterpret_cast<float4*>(Xs + r * kCG + (((2 * c8 + 1) ^ s) << 2)) = b;
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int ICT> __device__ __forceinline__ void load_w(const T* p, float (&w)[ICT]) {
+    if constexpr (ICT == 4) {
+        const float4 v = ld4(p);
+        w[0] = v.x;
+        w[1] = v.y;
+        w[2] = v.z;
+        w[3] = v.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < ICT; ++k) w[k] = Elem<T>::up(p[k]);
+    }
+}
+template <typename T, int ICT> __device__ __forceinline__ void store_w(T* p, const float (&w)[ICT]) {
+    if constexpr (ICT == 4) {
+        st4(p, make_float4(w[0], w[1], w[2], w[3]));
+    } else {
+#pragma unroll
+        for (int k = 0; k < ICT; ++k) p[k] = Elem<T>::down(w[k]);
+    }
+}
+
+// MODE 0: wf_sum, MODE 1: wf_dot.  ICT = ic (1, 2 or 4).  c must be a multiple of 64.
 template <typename T, int MODE, int ICT>
 __global__ void __launch_bounds__(32 * kWarps, 3)
 wf_tiles_kernel(const WfParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    using WS = WfSmem<T, MODE>;
-    constexpr bool kIsFloat = WS::kIsFloat;
-    constexpr int kPer = 16 / (int)sizeof(T);
+    using WS = WfSmem<MODE>;
+    constexpr bool kSplit = std::is_same<T, float>::value;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int qi = lane >> 3, ci = lane & 7, g = lane >> 2, t = lane & 3;
+    const int g = lane >> 2, t = lane & 3;
     unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
     float* Xs = reinterpret_cast<float*>(base);
-    T* Xraw = reinterpret_cast<T*>(base + WS::kX);
-    float* Op = reinterpret_cast<float*>(base + WS::kX + WS::kXraw);
-    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kXraw + WS::kOp);
+    float* Op = reinterpret_cast<float*>(base + WS::kX);
+    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kOp);
     unsigned short* uniq = lut + kE;
+    int* rowsS = reinterpret_cast<int*>(uniq + kE);
     long long* ring = reinterpret_cast<long long*>(Xs);
     DedupScratch ds;
     ds.tok = reinterpret_cast<unsigned short*>(base + kE * 8);
@@ -108,40 +208,58 @@ wf_tiles_kernel(const WfParams p) {
     ds.bm = reinterpret_cast<unsigned*>(Op);
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
-    float* Wd = Op;                                    // MODE 0: [ICT * 8][kWLD], row = k * 8 + q
-    float* Ys = Op;                                    // MODE 1: [ICT * 8][kYLD]
-    float* Sb = Op + kT * kMaxIC * kYLD;               // MODE 1: [ICT * 8][kWLD]
 
     const int m = p.m, c = p.c, n = p.n, n_out = p.n_out;
     const int E = kT * m;
-    const T* Wg = static_cast<const T*>(p.W);
     const T* Fg = static_cast<const T*>(p.F);
-    const T* Gg = static_cast<const T*>(p.G);
-    T* Og = static_cast<T*>(p.out);
-    const int sw_sum = (ci ^ (qi << 1)) << 2;          // MODE 0 swizzle of staged row qi + 4k
-    const int sw_dot_e = (ci ^ qi) << 2, sw_dot_o = sw_dot_e ^ 16;
-    const SumAddr sa = make_sum_addr(Wd, Xs, lane);
-    const DotAddr da = make_dot_addr(Ys, Xs, Sb, lane);
+
+    // fragment addresses (bytes in shared memory), fixed per lane
+    unsigned xa[4][2];          // MODE 0: A = X^T, &Xs[t][16 mt + 8 h + g]
+    unsigned wa = 0;            // MODE 0: B = Wd^T, &Wd[g][t]
+    unsigned ya[2];             // MODE 1: A = gradient tile, &Ys[16 mt + g][t]
+    unsigned xb[4][2];          // MODE 1: B = X^T, &Xs[g][8 ks + 4 h + t] for ks % 4 = 0..3
+    if (MODE == 0) {
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int col = 16 * mt + 8 * h + g;
+                xa[mt][h] = smem_u32(Xs + t * kCG + ((((col >> 2) ^ (t << 1)) << 2) + (col & 3)));
+            }
+        wa = smem_u32(Op + g * kDL + t);
+    } else {
+        ya[0] = smem_u32(Op + g * kGL + t);
+        ya[1] = smem_u32(Op + (16 + g) * kGL + t);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) xb[ks][h] = smem_u32(Xs + g * kCG + ((((2 * ks + h) ^ g) << 2) + t));
+    }
 
     const unsigned total = (unsigned)p.batch * (unsigned)p.tiles;
     const unsigned nwarps = gridDim.x * kWarps;
     for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
         const int b = (int)(task / (unsigned)p.tiles);
         const int i0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
-        // rows of this tile (lane q < 8 holds row q; -1 past the end)
-        int myrow = -1;
-        if (lane < kT && i0 + lane < n_out)
-            myrow = p.order ? p.order[(long long)b * n_out + i0 + lane] : i0 + lane;
-        int rows[kT];
-#pragma unroll
-        for (int q = 0; q < kT; ++q) rows[q] = __shfl_sync(kFull, myrow, q);
-        // ---- indices of the 8 rows -> ring [8][m]
+        const long long brow = (long long)b * n_out;
+        // ---- the tile's rows, their indices -> ring [8][m]
+        __syncwarp();
+        if (lane < kT) {
+            int r = -1;
+            if (i0 + lane < n_out) r = p.order ? p.order[brow + i0 + lane] : i0 + lane;
+            rowsS[lane] = r;
+        }
         __syncwarp();
 #pragma unroll
         for (int q = 0; q < kT; ++q) {
-            if (rows[q] >= 0) {
-                const int64_t* src = p.idx + ((long long)b * n_out + rows[q]) * m;
+            const int rq = rowsS[q];
+            if (rq >= 0) {
+                const int64_t* src = p.idx + (brow + rq) * m;
                 for (int j = lane; j < m; j += 32) cp_async8_ca(ring + q * m + j, src + j);
+                if (MODE == 0) {        // the row's weights will be wanted soon
+                    const char* wrow = reinterpret_cast<const char*>(static_cast<const T*>(p.W) + (brow + rq) * m * ICT);
+                    if (lane * 128 < m * ICT * (int)sizeof(T)) prefetch_l2(wrow + lane * 128);
+                }
             } else {
                 for (int j = lane; j < m; j += 32) ring[q * m + j] = -1;
             }
@@ -150,173 +268,273 @@ wf_tiles_kernel(const WfParams p) {
         cp_async_wait<0>();
         __syncwarp();
         bool rowdup = false;
-        // every row of the ring is "valid" for dedup_tile (i0 = 0, 8 rows); missing rows hold -1
         const int U = dedup_tile(ds, ring, lut, E, m, 0, kT, MODE == 0, &rowdup, lane, n);
+        // ---- per edge of this lane: offset of its weights; tile row into lut
+        int woff[kEPL];
+        {
+            int q = 0, j = lane;
+            while (j >= m) { j -= m; ++q; }
+#pragma unroll
+            for (int i = 0; i < kEPL; ++i) {
+                const int x = lane + 32 * i;
+                woff[i] = -1;
+                if (x < E) {
+                    const int rq = rowsS[q];
+                    if (rq >= 0) woff[i] = (rq * m + j) * ICT;
+                    const unsigned short s = lut[x];
+                    if (s != kSkip) lut[x] = (unsigned short)(s | (q << 12));
+                    j += 32;
+                    while (j >= m) { j -= m; ++q; }
+                }
+            }
+        }
         __syncwarp();
+        const int nchunks = (U + kUW - 1) / kUW;
 
-        float acc[ICT][2][4];                           // MODE 0
-        const int nslabs = c / kC;
-        for (int s = 0; s < (MODE == 0 ? nslabs : 1); ++s) {
+        if (MODE == 0) {
+            const T* Wb = static_cast<const T*>(p.W) + brow * m * ICT;
+            T* Ob = static_cast<T*>(p.out) + brow * ICT * c;
+            float* Wd = Op;
+            for (int c0 = 0; c0 < c; c0 += kCG) {
+                const T* Fb = Fg + (long long)b * n * c + c0;
+                float acc[ICT][4][4];
 #pragma unroll
-            for (int k = 0; k < ICT; ++k)
+                for (int k = 0; k < ICT; ++k)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) acc[k][0][i] = acc[k][1][i] = 0.f;
-            const int nchunks = U > 0 ? (U + kUC - 1) / kUC : 1;
-            for (int ch = 0; ch < nchunks; ++ch) {
-                const int u0 = ch * kUC;
-                const int Uc = max(0, min(kUC, U - u0));
-                const int rows8 = (Uc + 7) & ~7;
-                if (MODE == 0) {
-                    // ---------------- forward: stage slab s of the rows, spread the weights, multiply
-                    const T* Fb = Fg + (long long)b * n * c + s * kC;
+                    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[k][mt][i] = 0.f;
+                for (int ch = 0; ch < nchunks; ++ch) {
+                    const int u0 = ch * kUW;
+                    const int Uc = min(kUW, U - u0);
+                    const int rows8 = (Uc + 7) & ~7;
                     __syncwarp();
-                    if (kIsFloat) {
-#pragma unroll
-                        for (int k = 0; k < kUC / 4; ++k) {
-                            const int r = qi + 4 * k;
-                            if (r < rows8) {
-                                float* dst = Xs + r * kC + sw_sum;
-                                if (r < Uc) cp_async16_cg(dst, Fb + (long long)uniq[u0 + r] * c + ci * 4);
-                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                        }
-                    } else {
-                        const int pr = lane >> 2, pc = lane & 3;
-#pragma unroll
-                        for (int k = 0; k < kUC / 8; ++k) {
-                            const int r = pr + 8 * k;
-                            if (r < rows8) {
-                                T* dst = Xraw + r * kC + pc * kPer;
-                                if (r < Uc) cp_async16_cg(dst, Fb + (long long)uniq[u0 + r] * c + pc * kPer);
-                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                        }
-                    }
+                    stage_rows64<T, 0>(Xs, rows8, Uc, lane,
+                                       [&](int r) { return Fb + (long long)uniq[u0 + r] * c; });
                     cp_async_commit();
-                    for (int z = lane; z < ICT * kT * kWLD / 4; z += 32)
+                    for (int z = lane; z < ICT * kT * kDL / 4; z += 32)
                         reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                     __syncwarp();
                     if (!rowdup) {
-                        int q = 0, j = lane;                    // edge x = lane + 32 step  ->  (q, j)
-                        while (j >= m) { j -= m; ++q; }
-                        for (int x = lane; x < E; x += 32) {
-                            const unsigned short sl = lut[x];
-                            const int rel = (int)sl - u0;
-                            if (sl != kSkip && rel >= 0 && rel < Uc) {
-                                int rq = rows[0];
 #pragma unroll
-                                for (int qq = 1; qq < kT; ++qq)
-                                    if (q == qq) rq = rows[qq];
-                                const T* w = Wg + (((long long)b * n_out + rq) * m + j) * ICT;
+                        for (int i0e = 0; i0e < kEPL; i0e += 4) {
+                            float w[4][ICT];
+                            int dst[4];
 #pragma unroll
-                                for (int k = 0; k < ICT; ++k) Wd[(k * kT + q) * kWLD + rel] = Elem<T>::up(w[k]);
-                            }
-                            j += 32;
-                            while (j >= m) { j -= m; ++q; }
-                        }
-                    } else if (lane < kT) {
-                        // some row repeats a neighbour: one lane per row adds the weights in column order
-                        int rq = rows[0];
-#pragma unroll
-                        for (int qq = 1; qq < kT; ++qq)
-                            if (lane == qq) rq = rows[qq];
-                        if (rq >= 0) {
-                            const T* w = Wg + (((long long)b * n_out + rq) * m) * ICT;
-                            for (int j = 0; j < m; ++j) {
-                                const unsigned short sl = lut[lane * m + j];
-                                const int rel = (int)sl - u0;
-                                if (sl != kSkip && rel >= 0 && rel < Uc) {
-#pragma unroll
-                                    for (int k = 0; k < ICT; ++k)
-                                        Wd[(k * kT + lane) * kWLD + rel] += Elem<T>::up(w[j * ICT + k]);
+                            for (int i = 0; i < 4; ++i) {
+                                const int x = lane + 32 * (i0e + i);
+                                dst[i] = -1;
+                                if (x < E) {
+                                    const unsigned short lr = lut[x];
+                                    const int rel = (int)(lr & 0xfffu) - u0;
+                                    if (lr != kSkip && rel >= 0 && rel < Uc && woff[i0e + i] >= 0) {
+                                        dst[i] = (lr >> 12) * kDL + rel;
+                                        load_w<T, ICT>(Wb + woff[i0e + i], w[i]);
+                                    }
                                 }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                if (dst[i] >= 0) {
+#pragma unroll
+                                    for (int k = 0; k < ICT; ++k) Wd[k * kT * kDL + dst[i]] = w[i][k];
+                                }
+                        }
+                    } else if (lane < kT && rowsS[lane] >= 0) {
+                        // some row repeats a neighbour: one lane per row adds its weights in column order
+                        const T* wrow = Wb + (long long)rowsS[lane] * m * ICT;
+                        for (int j = 0; j < m; ++j) {
+                            const unsigned short lr = lut[lane * m + j];
+                            const int rel = (int)(lr & 0xfffu) - u0;
+                            if (lr != kSkip && rel >= 0 && rel < Uc) {
+#pragma unroll
+                                for (int k = 0; k < ICT; ++k)
+                                    Wd[(k * kT + lane) * kDL + rel] += Elem<T>::up(wrow[j * ICT + k]);
                             }
                         }
                     }
                     cp_async_wait<0>();
                     __syncwarp();
-                    if (!kIsFloat) {
-#pragma unroll
-                        for (int k = 0; k < kUC / 4; ++k) {
-                            const int r = qi + 4 * k;
-                            if (r < rows8) st4(Xs + r * kC + sw_sum, ld4(Xraw + r * kC + ci * 4));
-                        }
-                        __syncwarp();
-                    }
-                    // D_k[c][q] += sum_u X[u][c] * Wd[k*8+q][u]: A fragments loaded and split once per step
+                    // D_k[ch][q] += sum_u X[u][ch] * Wd[k 8 + q][u]
                     for (int us = 0; us < rows8; us += 8) {
-                        float a[2][4];
-                        unsigned ah[2][4], al[2][4];
+                        unsigned ah[4][4], al[4][4];
 #pragma unroll
-                        for (int mt = 0; mt < 2; ++mt) {
-                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(a[mt][0]) : "r"(sa.x[mt][0] + us * kC * 4));
-                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(a[mt][1]) : "r"(sa.x[mt][1] + us * kC * 4));
-                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(a[mt][2]) : "r"(sa.x[mt][0] + (us + 4) * kC * 4));
-                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(a[mt][3]) : "r"(sa.x[mt][1] + (us + 4) * kC * 4));
+                        for (int mt = 0; mt < 4; ++mt) {
+                            float a[4];
+                            const unsigned a0 = xa[mt][0] + us * (kCG * 4), a1 = xa[mt][1] + us * (kCG * 4);
+                            WF_LDS(a[0], a0, 0);
+                            WF_LDS(a[1], a1, 0);
+                            WF_LDS(a[2], a0, 4 * kCG * 4);
+                            WF_LDS(a[3], a1, 4 * kCG * 4);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                if (kIsFloat) split_tf32(a[mt][i], ah[mt][i], al[mt][i]);
-                                else { ah[mt][i] = __float_as_uint(a[mt][i]); al[mt][i] = 0u; }
-                            }
+                            for (int i = 0; i < 4; ++i) wf_split<kSplit>(a[i], ah[mt][i], al[mt][i]);
                         }
+                        const unsigned w0 = wa + us * 4;
 #pragma unroll
                         for (int k = 0; k < ICT; ++k) {
                             float bv[2];
-                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(bv[0]) : "r"(sa.w + (k * kT * kWLD + us) * 4));
-                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(bv[1]) : "r"(sa.w + (k * kT * kWLD + us + 4) * 4));
+                            WF_LDS(bv[0], w0, k * kT * kDL * 4);
+                            WF_LDS(bv[1], w0, k * kT * kDL * 4 + 16);
                             unsigned bh[2], bl[2];
+                            wf_split<kSplit>(bv[0], bh[0], bl[0]);
+                            wf_split<kSplit>(bv[1], bh[1], bl[1]);
 #pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                if (kIsFloat) split_tf32(bv[i], bh[i], bl[i]);
-                                else { bh[i] = __float_as_uint(bv[i]); bl[i] = 0u; }
-                            }
-#pragma unroll
-                            for (int mt = 0; mt < 2; ++mt) {
-                                if (kIsFloat) mma3(acc[k][mt], ah[mt], al[mt], bh, bl);
-                                else mma_tf32(acc[k][mt], ah[mt], bh);
-                            }
+                            for (int mt = 0; mt < 4; ++mt) wf_mma<kSplit>(acc[k][mt], ah[mt], al[mt], bh, bl);
                         }
                     }
                 }
-            }
-            if (MODE == 0) {
-                // D fragments -> output tile [8][kOLD] per k -> 16-byte stores
-                float* Ot = Op;
+                // D fragments -> output tile [8][kGL] in X -> 16-byte stores, one ic at a time
+                float* Ot = Xs;
 #pragma unroll
                 for (int k = 0; k < ICT; ++k) {
                     __syncwarp();
 #pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        float* o = Ot + (2 * t) * kOLD + 16 * mt + g;
+                    for (int mt = 0; mt < 4; ++mt) {
+                        float* o = Ot + (2 * t) * kGL + 16 * mt + g;
                         o[0] = acc[k][mt][0];
-                        o[kOLD] = acc[k][mt][1];
+                        o[kGL] = acc[k][mt][1];
                         o[8] = acc[k][mt][2];
-                        o[kOLD + 8] = acc[k][mt][3];
+                        o[kGL + 8] = acc[k][mt][3];
                     }
                     __syncwarp();
+                    const int rsub = lane >> 4, chn = lane & 15;
 #pragma unroll
-                    for (int a2 = 0; a2 < 2; ++a2) {
-                        const int q = 2 * qi + a2;
-                        int rq = rows[0];
-#pragma unroll
-                        for (int qq = 1; qq < kT; ++qq)
-                            if (q == qq) rq = rows[qq];
+                    for (int i = 0; i < 4; ++i) {
+                        const int q = 2 * i + rsub;
+                        const int rq = rowsS[q];
                         if (rq >= 0)
-                            st4(Og + (((long long)b * n_out + rq) * ICT + k) * c + s * kC + ci * 4,
-                                *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4));
+                            st4(Ob + ((long long)rq * ICT + k) * c + c0 + chn * 4,
+                                *reinterpret_cast<const float4*>(Ot + q * kGL + chn * 4));
                     }
                 }
+            }
+        } else {
+            T* Wout = static_cast<T*>(p.out) + brow * m * ICT;
+            const T* Gb = static_cast<const T*>(p.G) + brow * ICT * c;
+            float* Ys = Op;
+            float* Sb = Xs;
+            // edges without a neighbour get zero
+            {
+                float z[ICT];
+#pragma unroll
+                for (int k = 0; k < ICT; ++k) z[k] = 0.f;
+#pragma unroll
+                for (int i = 0; i < kEPL; ++i) {
+                    const int x = lane + 32 * i;
+                    if (x < E && woff[i] >= 0 && lut[x] == kSkip) store_w<T, ICT>(Wout + woff[i], z);
+                }
+            }
+            const bool multi = c > kCG;          // several channel groups: the gradient tile is staged per group
+            for (int ch = 0; ch < nchunks; ++ch) {
+                const int u0 = ch * kUW;
+                const int Uc = min(kUW, U - u0);
+                const int rows8 = (Uc + 7) & ~7;
+                constexpr int MT = (ICT * kT + 15) / 16;
+                float acc[MT][4][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+                for (int c0 = 0; c0 < c; c0 += kCG) {
+                    const T* Fb = Fg + (long long)b * n * c + c0;
+                    __syncwarp();
+                    stage_rows64<T, 1>(Xs, rows8, Uc, lane,
+                                       [&](int r) { return Fb + (long long)uniq[u0 + r] * c; });
+                    if (ch == 0 || multi) {
+                        // gradient tile: row k 8 + q <- d_feat_new[b, row q, k, c0 .. c0 + 63]
+                        if constexpr (std::is_same<T, float>::value) {
+                            const int rsub = lane >> 4, chn = lane & 15;
+#pragma unroll 4
+                            for (int i = 0; i < ICT * kT / 2; ++i) {
+                                const int r = 2 * i + rsub;              // k 8 + q
+                                const int rq = rowsS[r & 7];
+                                float* dst = Ys + r * kGL + chn * 4;
+                                if (rq >= 0) cp_async16_cg(dst, Gb + ((long long)rq * ICT + (r >> 3)) * c + c0 + chn * 4);
+                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        } else {
+                            const int rsub = lane >> 3, c8 = lane & 7;
+#pragma unroll 2
+                            for (int i = 0; i < ICT * kT / 4; ++i) {
+                                const int r = 4 * i + rsub;
+                                const int rq = rowsS[r & 7];
+                                float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vb = va;
+                                if (rq >= 0)
+                                    up8(*reinterpret_cast<const uint4*>(Gb + ((long long)rq * ICT + (r >> 3)) * c + c0 + c8 * 8),
+                                        static_cast<const T*>(nullptr), va, vb);
+                                *reinterpret_cast<float4*>(Ys + r * kGL + c8 * 8) = va;
+                                *reinterpret_cast<float4*>(Ys + r * kGL + c8 * 8 + 4) = vb;
+                            }
+                        }
+                    }
+                    cp_async_commit();
+                    cp_async_wait<0>();
+                    __syncwarp();
+                    // S[k 8 + q][u] += sum_ch Ys[k 8 + q][ch] * X[u][ch]
+#pragma unroll
+                    for (int ks = 0; ks < kCG / 8; ++ks) {
+                        unsigned ah[MT][4], al[MT][4];
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            float a[4];
+                            WF_LDS(a[0], ya[mt], ks * 32);
+                            WF_LDS(a[1], ya[mt], ks * 32 + 8 * kGL * 4);
+                            WF_LDS(a[2], ya[mt], ks * 32 + 16);
+                            WF_LDS(a[3], ya[mt], ks * 32 + 8 * kGL * 4 + 16);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) wf_split<kSplit>(a[i], ah[mt][i], al[mt][i]);
+                        }
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt) {
+                            if (nt * 8 < rows8) {
+                                float bv[2];
+                                WF_LDS(bv[0], xb[ks & 3][0], nt * 8 * kCG * 4 + (ks >> 2) * 128);
+                                WF_LDS(bv[1], xb[ks & 3][1], nt * 8 * kCG * 4 + (ks >> 2) * 128);
+                                unsigned bh[2], bl[2];
+                                wf_split<kSplit>(bv[0], bh[0], bl[0]);
+                                wf_split<kSplit>(bv[1], bh[1], bl[1]);
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) wf_mma<kSplit>(acc[mt][nt], ah[mt], al[mt], bh, bl);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();                               // every lane is done with X: the scores go there
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        float* sp = Sb + (16 * mt + g) * kDL + 8 * nt + 2 * t;
+                        *reinterpret_cast<float2*>(sp) = make_float2(acc[mt][nt][0], acc[mt][nt][1]);
+                        *reinterpret_cast<float2*>(sp + 8 * kDL) = make_float2(acc[mt][nt][2], acc[mt][nt][3]);
+                    }
                 __syncwarp();
+                // every edge whose neighbour is in this stage picks its ic scores
+#pragma unroll
+                for (int i = 0; i < kEPL; ++i) {
+                    const int x = lane + 32 * i;
+                    if (x < E && woff[i] >= 0) {
+                        const unsigned short lr = lut[x];
+                        const int rel = (int)(lr & 0xfffu) - u0;
+                        if (lr != kSkip && rel >= 0 && rel < Uc) {
+                            float w[ICT];
+#pragma unroll
+                            for (int k = 0; k < ICT; ++k) w[k] = Sb[(k * kT + (lr >> 12)) * kDL + rel];
+                            store_w<T, ICT>(Wout + woff[i], w);
+                        }
+                    }
+                }
             }
         }
-        (void)Gg; (void)da; (void)sw_dot_e; (void)sw_dot_o; (void)Ys; (void)Sb;
     }
 }
 
-template <typename T, int ICT>
-int wf_sum_t(const char* label, const WfParams& p, cudaStream_t s) {
-    const size_t smem = size_t(kWarps) * WfSmem<T, 0>::kTotal;
-    auto kernel = wf_tiles_kernel<T, 0, ICT>;
+template <typename T, int MODE, int ICT>
+int wf_tiles_t(const char* label, const WfParams& p, cudaStream_t s) {
+    const size_t smem = size_t(kWarps) * WfSmem<MODE>::kTotal;
+    auto kernel = wf_tiles_kernel<T, MODE, ICT>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
@@ -335,14 +553,30 @@ int wf_sum_t(const char* label, const WfParams& p, cudaStream_t s) {
     return check_launch();
 }
 
-template <typename T>
-int wf_sum_ic(const char* label, const WfParams& p, cudaStream_t s) {
-    switch (p.ic) {
-        case 1: return wf_sum_t<T, 1>(label, p, s);
-        case 2: return wf_sum_t<T, 2>(label, p, s);
-        case 4: return wf_sum_t<T, 4>(label, p, s);
+template <typename T, int MODE>
+int wf_tiles_ic(const char* label, int ic, const WfParams& p, cudaStream_t s) {
+    switch (ic) {
+        case 1: return wf_tiles_t<T, MODE, 1>(label, p, s);
+        case 2: return wf_tiles_t<T, MODE, 2>(label, p, s);
+        case 4: return wf_tiles_t<T, MODE, 4>(label, p, s);
         default: return CLUSTEN_ERR_UNSUPPORTED;
     }
+}
+
+template <int MODE>
+int wf_tiles_dispatch(const char* label, int dtype, int ic, const WfParams& p, cudaStream_t s) {
+    switch (dtype) {
+        case CLUSTEN_F32: return wf_tiles_ic<float, MODE>(label, ic, p, s);
+        case CLUSTEN_F16: return wf_tiles_ic<__half, MODE>(label, ic, p, s);
+        case CLUSTEN_BF16: return wf_tiles_ic<__nv_bfloat16, MODE>(label, ic, p, s);
+        default: return CLUSTEN_ERR_DTYPE;
+    }
+}
+
+bool aligned16(std::initializer_list<const void*> ptrs) {
+    for (const void* q : ptrs)
+        if (reinterpret_cast<uintptr_t>(q) % 16 != 0) return false;
+    return true;
 }
 
 }  // namespace
@@ -357,26 +591,31 @@ int launch_wf_order(const int64_t* idx, int b, int n_out, int m, int* order, cud
     return check_launch();
 }
 
-bool tiled_wf_sum_supported(int dtype, const void* W, const void* F, const void* out, int n_out, int n, int m, int ic,
-                            int c) {
+bool tiled_wf_gather_supported(int dtype, const void* W, const void* F, const void* O, int n_out, int n, int m,
+                               int ic, int c) {
     if (dtype != CLUSTEN_F32 && dtype != CLUSTEN_F16 && dtype != CLUSTEN_BF16) return false;
-    if (c % kC != 0 || (ic != 1 && ic != 2 && ic != 4) || m < 1 || m > kMmax || n > 65000 || n_out < 1) return false;
-    return reinterpret_cast<uintptr_t>(F) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
-           reinterpret_cast<uintptr_t>(W) % 16 == 0;
+    if (c % kCG != 0 || (ic != 1 && ic != 2 && ic != 4) || m < 1 || m > kMmax || n > 65000 || n_out < 1) return false;
+    if ((long long)n_out * m * ic > 0x7fffffffLL) return false;
+    return aligned16({W, F, O});
 }
 
 int launch_tiled_wf_sum(const char* label, int dtype, const void* W, const void* F, const int64_t* idx,
                         const int* order, void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s) {
     WfParams p{};
     p.W = W;  p.F = F;  p.G = nullptr;  p.out = out;  p.idx = idx;  p.order = order;
-    p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.ic = ic;  p.c = c;  p.tiles = (n_out + kT - 1) / kT;
+    p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;  p.tiles = (n_out + kT - 1) / kT;
     if ((long long)b * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
-    switch (dtype) {
-        case CLUSTEN_F32: return wf_sum_ic<float>(label, p, s);
-        case CLUSTEN_F16: return wf_sum_ic<__half>(label, p, s);
-        case CLUSTEN_BF16: return wf_sum_ic<__nv_bfloat16>(label, p, s);
-        default: return CLUSTEN_ERR_DTYPE;
-    }
+    return wf_tiles_dispatch<0>(label, dtype, ic, p, s);
+}
+
+int launch_tiled_wf_dot(const char* label, int dtype, const void* F, const void* G, const int64_t* idx,
+                        const int* order, void* d_weights, int b, int n_out, int n, int m, int ic, int c,
+                        cudaStream_t s) {
+    WfParams p{};
+    p.W = nullptr;  p.F = F;  p.G = G;  p.out = d_weights;  p.idx = idx;  p.order = order;
+    p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;  p.tiles = (n_out + kT - 1) / kT;
+    if ((long long)b * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    return wf_tiles_dispatch<1>(label, dtype, ic, p, s);
 }
 
 }  // namespace clusten

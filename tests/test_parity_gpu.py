@@ -82,6 +82,7 @@ WF_SHAPES = [
     (3, 64, 196, 48, 4, 32),
     (2, 36, 184, 48, 4, 128),
     (1, 14, 73, 48, 4, 256),
+    (2, 51, 392, 48, 2, 64),
     (1, 20, 100, 16, 3, 24),
     (1, 7, 30, 5, 2, 9),
 ]
@@ -156,6 +157,51 @@ def test_out_of_range_indices_are_ignored(ops):
     assert_close(da, ra * mask, torch.float32, "d_attn with bad indices")
     assert_close(dv, rv, torch.float32, "d_value with bad indices")
     assert ops.build_inverse(bad, n)[5].item() == int((mask == 0).sum())
+
+
+def test_wf_out_of_range_indices_are_ignored(ops):
+    b, n_out, n, m, ic, c = 2, 37, 120, 48, 4, 64
+    idx = workloads.select_rows(workloads.make_index("model", b, n, m, 9), n_out, 10).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, torch.float32, 11))
+    bad = idx.clone()
+    bad[0, ::3, 5] = n + 7
+    bad[1, 1::3, 2] = -1
+    bad[1, 4, :] = -5                                                # a row without any neighbour
+    mask = ((bad >= 0) & (bad < n)).float().unsqueeze(-1)            # [b,n_out,m,1]
+    safe = bad.clamp(0, n - 1)
+    assert_close(ops.wf_forward(w, feat, bad), formula.wf(w * mask, feat, safe), torch.float32, "wf with bad indices")
+    dw, df = ops.wf_backward(g, w, feat, bad)
+    _, rw, rf = formula.forward_backward("wf", w * mask, feat, safe, g)
+    assert_close(dw, rw * mask, torch.float32, "d_weights with bad indices")
+    assert_close(df, rf, torch.float32, "d_feat with bad indices")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def test_wf_row_order_variants(ops, dtype):
+    """The row order only groups the rows: storage order, the built order, any permutation and a stage
+    with more rows than the order kernel sorts give the same results."""
+    b, n_out, n, m, ic, c = 2, 203, 812, 48, 4, 64
+    idx = workloads.select_rows(workloads.make_index("shared", b, n, m, 9), n_out, 10).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, dtype, 11))
+    order = ops.build_row_order(idx)
+    assert order.dtype == torch.int32 and order.shape == (b, n_out)
+    assert torch.equal(order.long().sort(dim=1).values, torch.arange(n_out, device=DEV).expand(b, n_out))
+    first = idx[:, :, 0].gather(1, order.long())
+    assert bool((first[:, 1:] >= first[:, :-1]).all())
+    ref_out = exact("wf", "forward", w, feat, idx)
+    ref_dw, ref_df = exact("wf", "backward", g, w, feat, idx)
+    perm = torch.stack([torch.randperm(n_out, device=DEV) for _ in range(b)]).int().contiguous()
+    for ro in (None, False, order, perm):
+        assert_close(ops.wf_forward(w, feat, idx, ro), ref_out, dtype, "wf forward")
+        dw, df = ops.wf_backward(g, w, feat, idx, None, ro)
+        assert_close(dw, ref_dw, dtype, "d_weights")
+        assert_close(df, ref_df, dtype, "d_feat")
+    with pytest.raises(RuntimeError):
+        ops.wf_forward(w, feat, idx, order[:, :-1].contiguous())
+    big = torch.randint(0, 64, (1, 4100, 8), device=DEV)
+    assert ops.build_row_order(big) is None
+    w2, feat2, g2 = (x.to(DEV) for x in workloads.merge_operands(1, 4100, 64, 8, 1, 64, dtype, 12))
+    assert_close(ops.wf_forward(w2, feat2, big), exact("wf", "forward", w2, feat2, big), dtype, "wf forward, no order")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
