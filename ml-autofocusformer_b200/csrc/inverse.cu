@@ -200,6 +200,163 @@ inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt,
     for (int t = tid; t < nt; t += kThreads) sl[t] = base[t] - rp[t];
 }
 
+
+// ----------------------------------------------------------------------------- 128 rows at a time
+// Same scheme as pass 2 above with four rows per warp and 128-bit row masks: a quarter of the
+// block-wide barriers.  Needs 9 words of shared memory per target.  m <= 32 P.
+constexpr int kR = 4;                    // rows per warp and group
+constexpr int kGroupRows = kWarps * kR;  // 128
+template <int P>
+__global__ void __launch_bounds__(kThreads)
+inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int* __restrict__ header,
+                        int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries) {
+    extern __shared__ __align__(16) int sm128[];
+    unsigned* mask = reinterpret_cast<unsigned*>(sm128);             // [nt][4] rows of the current group that hit t
+    unsigned* dupm = reinterpret_cast<unsigned*>(sm128 + 4 * nt);    // [nt][4] rows that hit t more than once
+    int* base = sm128 + 8 * nt;                                      // [nt] running write position of target t
+    __shared__ int warp_tot[kWarps];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long E = (long long)n_rows * m;
+    const int64_t* ib = idx + (long long)b * E;
+    int* rp = rowptr + (long long)b * (nt + 1);
+    int* ent = entries + (long long)b * E;
+    if (b == 0 && tid == 0) {
+        header[0] = (int)kInvMagic;
+        header[1] = gridDim.x;
+        header[2] = n_rows;
+        header[3] = m;
+        header[4] = nt;
+    }
+    for (int t = tid; t < nt; t += kThreads) base[t] = 0;
+    for (int t = tid; t < 4 * nt; t += kThreads) {
+        mask[t] = 0u;
+        dupm[t] = 0u;
+    }
+    __syncthreads();
+    int oob = 0;
+    for (long long e = tid; e < E; e += kThreads) {
+        const long long tk = ib[e];
+        if (tk >= 0 && tk < nt) atomicAdd(&base[(int)tk], 1);
+        else ++oob;
+    }
+    if (oob) atomicAdd(&header[5], oob);
+    __syncthreads();
+    {
+        const int per = (nt + kThreads - 1) / kThreads;
+        const int lo = min(tid * per, nt);
+        const int hi = min(lo + per, nt);
+        int local = 0;
+        for (int t = lo; t < hi; ++t) local += base[t];
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += y;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const int w = warp_tot[lane];
+            int wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int y = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += y;
+            }
+            warp_tot[lane] = wi - w;
+        }
+        __syncthreads();
+        int run = warp_tot[warp] + incl - local;
+        for (int t = lo; t < hi; ++t) {
+            const int cnt = base[t];
+            base[t] = run;
+            rp[t] = run;
+            run += cnt;
+        }
+        if (hi == nt && lo < nt) rp[nt] = run;
+        if (nt == 0 && tid == 0) rp[0] = 0;
+    }
+    __syncthreads();
+
+    // row g0 + 4 warp + r of a group is bit (4 warp + r) % 32 of mask word warp / 8
+    const int word = warp >> 3;
+    const int bit0 = (warp & 7) * kR;
+    int cur[kR][P], nxt[kR][P];
+    auto load_rows = [&](int row0, int (&dst)[kR][P]) {
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                const int j = lane + 32 * p;
+                long long tk = -1;
+                if (row0 + r < n_rows && j < m) tk = ib[(long long)(row0 + r) * m + j];
+                dst[r][p] = (tk >= 0 && tk < nt) ? (int)tk : -1;
+            }
+    };
+    load_rows(warp * kR, cur);
+    for (int g0 = 0; g0 < n_rows; g0 += kGroupRows) {
+        const int row0 = g0 + warp * kR;
+        load_rows(row0 + kGroupRows, nxt);
+        unsigned win = 0u, last = 0u;                     // bit r * P + p
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                if (cur[r][p] >= 0) {
+                    const unsigned bit = 1u << (bit0 + r);
+                    const unsigned old = atomicOr(&mask[cur[r][p] * 4 + word], bit);
+                    if (old & bit) atomicOr(&dupm[cur[r][p] * 4 + word], bit);
+                    else win |= 1u << (r * P + p);
+                }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                if ((win >> (r * P + p)) & 1u) {
+                    const int tk = cur[r][p];
+                    const uint4 mk = *reinterpret_cast<const uint4*>(&mask[tk * 4]);
+                    const unsigned mw[4] = {mk.x, mk.y, mk.z, mk.w};
+                    const unsigned bit = 1u << (bit0 + r);
+                    int pos = base[tk];
+                    bool later = false;                   // does a later row of the group hit tk too?
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        if (w < word) pos += __popc(mw[w]);
+                        else if (w == word) {
+                            pos += __popc(mw[w] & (bit - 1u));
+                            later = later || (mw[w] >> (bit0 + r)) != 1u;
+                        } else {
+                            later = later || mw[w] != 0u;
+                        }
+                    }
+                    const bool dup = (dupm[tk * 4 + word] & bit) != 0u;
+                    const int row = row0 + r;
+                    ent[pos] = dup ? (int)(kDupFlag | (unsigned)(row * m)) : (row * m + lane + 32 * p);
+                    if (!later) last |= 1u << (r * P + p);
+                }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                if ((last >> (r * P + p)) & 1u) {
+                    const int tk = cur[r][p];
+                    const uint4 mk = *reinterpret_cast<const uint4*>(&mask[tk * 4]);
+                    base[tk] += __popc(mk.x) + __popc(mk.y) + __popc(mk.z) + __popc(mk.w);
+                    *reinterpret_cast<uint4*>(&mask[tk * 4]) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(&dupm[tk * 4]) = make_uint4(0u, 0u, 0u, 0u);
+                }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kR; ++r)
+#pragma unroll
+            for (int p = 0; p < P; ++p) cur[r][p] = nxt[r][p];
+    }
+    int* sl = seglen + (long long)b * nt;
+    for (int t = tid; t < nt; t += kThreads) sl[t] = base[t] - rp[t];
+}
+
 }  // namespace
 
 int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s) {
@@ -208,6 +365,19 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
     if (cudaMemsetAsync(p, 0, kInvHeaderInts * sizeof(int), s) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
+    }
+    if (m <= 64 && size_t(9) * nt * sizeof(int) <= 200 * 1024) {
+        const size_t smem128 = size_t(9) * nt * sizeof(int);
+        auto kernel128 = m <= 32 ? inverse_build128_kernel<1> : inverse_build128_kernel<2>;
+        if (cudaFuncSetAttribute(kernel128, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128) != cudaSuccess) {
+            cudaGetLastError();
+            return CLUSTEN_ERR_CUDA;
+        }
+        ScopedKernelTimer timer("inverse_build", s);
+        kernel128<<<b, kThreads, smem128, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
+                                               const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
+        note_launch();
+        return check_launch();
     }
     const size_t smem = size_t(3) * nt * sizeof(int);
     auto kernel = m <= 32 ? inverse_build_kernel<1> : (m <= 64 ? inverse_build_kernel<2> : inverse_build_kernel<0>);
