@@ -52,6 +52,9 @@ __device__ __forceinline__ void cp_async16_ca(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async16_cg(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(dst)), "l"(src));
 }
+__device__ __forceinline__ void cp_async4_ca(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(dst)), "l"(src));
+}
 __device__ __forceinline__ void cp_async8_ca(void* dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(smem_u32(dst)), "l"(src));
 }

@@ -605,10 +605,21 @@ scatter_tiles_kernel(const ScatterParams p) {
                 const T* Xh = Xg + (long long)b * p.x_batch + (long long)g * p.x_head;
                 // ---- weights of the edges for this slab
                 if (g == 0 || p.w_head != 0) {
+                    if (kIsFloat) {
+                        // asynchronous 4-byte copies: all of a lane's weights are in flight together with the
+                        // rows staged below; both are waited for before the dense weights are filled in
 #pragma unroll 4
-                    for (int x = lane; x < E; x += 32) {
-                        const unsigned e = edge[x];
-                        wbuf[x] = (e & kDupFlag) ? 0.f : Elem<T>::up(Wh[e]);
+                        for (int x = lane; x < E; x += 32) {
+                            const unsigned e = edge[x];
+                            if (e & kDupFlag) wbuf[x] = 0.f;
+                            else cp_async4_ca(wbuf + x, Wh + e);
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int x = lane; x < E; x += 32) {
+                            const unsigned e = edge[x];
+                            wbuf[x] = (e & kDupFlag) ? 0.f : Elem<T>::up(Wh[e]);
+                        }
                     }
                     if (any_flag) {
                         // targets that occur several times in their source row: sum that row's slots in order
@@ -661,6 +672,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                     cp_async_commit();
                     for (int z = lane; z < kT * kWLD / 4; z += 32)
                         reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    cp_async_wait<0>();
                     __syncwarp();
 #pragma unroll 4
                     for (int x = lane; x < E; x += 32) {
@@ -668,7 +680,6 @@ scatter_tiles_kernel(const ScatterParams p) {
                         const int rel = (int)(lr & 0xfffu) - u0;
                         if (rel >= 0 && rel < Uc) Wd[(lr >> 12) * kWLD + rel] = wbuf[x];
                     }
-                    cp_async_wait<0>();
                     __syncwarp();
                     if (!kIsFloat) {
 #pragma unroll
