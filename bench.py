@@ -53,8 +53,10 @@ CFG = dict(b=128, h=2, n=3136, m=48, c=32, n_out=784, cw=64, ic=4)
 CPU_SAMPLE_BATCH = 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture at b=32, scaled x4 to the
 # benchmark's b=128 (traffic grows with the batch); see profiles/
-NCU_DRAM_BYTES_PER_LAUNCH = {("av_d_value", "fp32"): 4 * (84347648 + 12541952),
-                             ("av_forward", "fp32"): 4 * (103102976 + 11558912)}
+NCU_DRAM_BYTES_PER_LAUNCH = {("av_d_value", "fp32"): 4 * (84363776 + 9671936),
+                             ("av_forward", "fp32"): 4 * (103102976 + 11558912),
+                             ("wf_forward", "fp32"): 4 * (54766336 + 2462720),
+                             ("wf_d_weights", "fp32"): 4 * (61190656 + 1755648)}
 
 
 def _peaks():
