@@ -335,6 +335,9 @@ int clusten_wf_backward(const void* d_feat_new, const void* weights, const void*
     else
         st = launch_gather_dot("wf_d_weights", dtype, feat, d_feat_new, nbhd_idx, d_weights, b, 1, n_out, n, m, ic, c, s);
     if (st != CLUSTEN_OK) return st;
+    if (tiled_wf_dfeat_supported(dtype, weights, d_feat_new, d_feat, n_out, n, m, ic, c))
+        return launch_tiled_wf_dfeat("wf_d_feat", dtype, weights, d_feat_new, nbhd_idx, inv, d_feat, b, n_out, n, m, ic,
+                                     c, s);
     if (tiled_wf_scatter_supported(dtype, weights, d_feat_new, d_feat, n_out, n, m, ic, c))
         return launch_tiled_wf_scatter("wf_d_feat", dtype, weights, d_feat_new, nbhd_idx, inv, d_feat, b, n_out, n, m,
                                        ic, c, s);

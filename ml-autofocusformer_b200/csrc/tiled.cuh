@@ -37,4 +37,11 @@ int launch_tiled_wf_dot(const char* label, int dtype, const void* F, const void*
 int launch_tiled_wf_sum(const char* label, int dtype, const void* W, const void* F, const int64_t* idx,
                         const int* order, void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s);
 
+// WF d_feat on 8-target tiles with the ic gradient rows of a merge row staged side by side
+bool tiled_wf_dfeat_supported(int dtype, const void* W, const void* G, const void* out, int n_out, int n, int m,
+                              int ic, int c);
+int launch_tiled_wf_dfeat(const char* label, int dtype, const void* W, const void* G, const int64_t* idx,
+                          const InverseView& inv, void* d_feat, int b, int n_out, int n, int m, int ic, int c,
+                          cudaStream_t s);
+
 }  // namespace clusten

@@ -89,6 +89,10 @@ static_assert(kRowsM * kDL * 4 <= kUW * kCG * 4 && kT * kGL * 4 <= kUW * kCG * 4
 
 #define WF_LDS(dst, addr, off) asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(dst) : "r"((addr) + (unsigned)(off)))
 
+__device__ __forceinline__ unsigned fast_div_u(unsigned x, unsigned magic, unsigned shift) {
+    return (__umulhi(magic, x) + x) >> shift;
+}
+
 template <bool SPLIT> __device__ __forceinline__ void wf_split(float x, unsigned& hi, unsigned& lo) {
     if (SPLIT) {
         split_tf32(x, hi, lo);
@@ -531,6 +535,287 @@ wf_tiles_kernel(const WfParams p) {
     }
 }
 
+// ----------------------------------------------------------------------------- d_feat
+//   d_feat[b, t, :] = sum over inverse-index entries (i, j) of target t and k < ic:
+//                     w[b, i, j, k] * d_feat_new[b, i, k, :]
+// A warp takes 8 consecutive targets, concatenates their segments (256 entries at a time) and
+// de-duplicates the merge ROWS i.  The ic gradient rows of a merge row are contiguous in memory and so
+// are the ic weights of an entry: the rows are staged as [32 / ic merge rows x ic][64 channels], the
+// weights go into the dense [8 targets x 32] tile with one 16-byte copy per entry (ic = 4), and the
+// product needs a single 8-wide N tile, so the accumulators are 16 registers.  The reference adds
+// every (entry, ic, channel) term with atomicAdd (clusten/src/clustenwf_cuda_kernel.cu:121-131).
+struct WfScatterParams {
+    const void* W;        // weights [b, n_out, m, ic]
+    const void* G;        // d_feat_new [b, n_out, ic, c]
+    void* out;            // d_feat [b, n, c]
+    const int64_t* idx;   // [b, n_out, m]
+    InverseView inv;
+    int batch, n_out, n, m, c, tiles;
+    unsigned m_magic, m_shift;            // x / m = (umulhi(magic, x) + x) >> shift
+};
+constexpr int kEE = 256;                  // entries handled at a time
+struct WfScatterSmem {
+    static constexpr int kX = kUW * kCG * 4;
+    static constexpr int kOp = kT * kWLD * 4;     // dense weights [8][kDL]; bitmap scratch before that
+    static constexpr int kEnt = kEE * 4;          // row * m + slot of each entry (bit 31: the row repeats the target)
+    static constexpr int kLut = kEE * 2;          // entry -> slot | tile row << 12;  slot -> merge row
+    static constexpr int kTotal = kX + kOp + kEnt + 2 * kLut;
+};
+static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= kT * kWLD * 4 && kT * kDL <= kT * kWLD, "scratch must fit in Op");
+static_assert(kEE * 2 <= kUW * kCG * 4, "token scratch must fit in the row buffer");
+
+template <typename T, int ICT>
+__global__ void __launch_bounds__(32 * kWarps, 4)
+wf_dfeat_kernel(const WfScatterParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    using WS = WfScatterSmem;
+    constexpr bool kSplit = std::is_same<T, float>::value;
+    constexpr int kRowsPer = kUW / ICT;          // merge rows per stage
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
+    float* Xs = reinterpret_cast<float*>(base);
+    float* Wd = reinterpret_cast<float*>(base + WS::kX);
+    unsigned* ent = reinterpret_cast<unsigned*>(base + WS::kX + WS::kOp);
+    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kOp + WS::kEnt);
+    unsigned short* uniq = lut + kEE;
+    DedupScratch ds;
+    ds.tok = reinterpret_cast<unsigned short*>(base);
+    ds.uniq = uniq;
+    ds.bm = reinterpret_cast<unsigned*>(Wd);
+    ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
+    ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
+    const int m = p.m, c = p.c, n_out = p.n_out, n_tgt = p.n;
+    const T* Wg = static_cast<const T*>(p.W);
+    const T* Gg = static_cast<const T*>(p.G);
+    T* Og = static_cast<T*>(p.out);
+
+    unsigned xa[4][2];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int col = 16 * mt + 8 * h + g;
+            xa[mt][h] = smem_u32(Xs + t * kCG + ((((col >> 2) ^ (t << 1)) << 2) + (col & 3)));
+        }
+    const unsigned wa = smem_u32(Wd + g * kDL + t);
+
+    const unsigned total = (unsigned)p.batch * (unsigned)p.tiles;
+    const unsigned nwarps = gridDim.x * kWarps;
+    auto load_segment = [&](unsigned task, int& len, int& start) {
+        len = 0;
+        start = 0;
+        if (task < total) {
+            const int b = (int)(task / (unsigned)p.tiles);
+            const int tt = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT + lane;
+            if (lane < kT && tt < n_tgt) {
+                len = p.inv.seglen[(long long)b * n_tgt + tt];
+                start = p.inv.rowptr[(long long)b * (n_tgt + 1) + tt];
+            }
+        }
+    };
+    int next_len, next_start;
+    load_segment(blockIdx.x * kWarps + warp, next_len, next_start);
+    for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
+        const int b = (int)(task / (unsigned)p.tiles);
+        const int t0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
+        const long long brow = (long long)b * n_out;
+        const int64_t* idx_b = p.idx + brow * m;
+        const int* entries = p.inv.entries + brow * m;
+        const T* Wb = Wg + brow * m * ICT;
+        const T* Gb = Gg + brow * ICT * c;
+        T* Ob = Og + (long long)b * n_tgt * c;
+        const int len = next_len, start = next_start;
+        load_segment(task + nwarps, next_len, next_start);
+        int incl = len;
+#pragma unroll
+        for (int o = 1; o < kT; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += y;
+        }
+        const int E_total = __shfl_sync(kFull, incl, kT - 1);
+        int off[kT], st[kT];
+#pragma unroll
+        for (int r = 0; r < kT; ++r) {
+            off[r] = __shfl_sync(kFull, incl - len, r);
+            st[r] = __shfl_sync(kFull, start, r);
+        }
+        for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kEE) {
+            const int E = max(0, min(kEE, E_total - e0));
+            int lo = INT_MAX, hi = -1;
+            __syncwarp();
+#pragma unroll 4
+            for (int x = lane; x < E; x += 32) {
+                const int pe = e0 + x;
+                int r = 0;
+#pragma unroll
+                for (int j = 1; j < kT; ++j) r += (pe >= off[j]) ? 1 : 0;
+                int s0 = st[0], o0 = off[0];
+#pragma unroll
+                for (int j = 1; j < kT; ++j)
+                    if (r == j) {
+                        s0 = st[j];
+                        o0 = off[j];
+                    }
+                const unsigned e = (unsigned)__ldg(entries + s0 + (pe - o0));
+                const int row = (int)fast_div_u(e & ~kDupFlag, p.m_magic, p.m_shift);
+                ent[x] = e;
+                ds.tok[x] = (unsigned short)row;
+                lut[x] = (unsigned short)(r << 12);
+                lo = min(lo, row);
+                hi = max(hi, row);
+            }
+            int U = 0;
+            if (E > 0) {
+                bool unused = false;
+                unsigned short* slots = ds.tok + kEE;
+                U = dedup_tokens(ds, slots, E, m, false, &unused, lane, lo, hi);
+                for (int x = lane; x < E; x += 32) lut[x] = (unsigned short)(lut[x] | slots[x]);
+            }
+            __syncwarp();
+            for (int c0 = 0; c0 < c; c0 += kCG) {
+                float acc[4][4];
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+                for (int u0 = 0; u0 < U; u0 += kRowsPer) {
+                    const int Uc = min(kRowsPer, U - u0);           // merge rows of this stage
+                    const int nrows = Uc * ICT;
+                    const int rows8 = (nrows + 7) & ~7;
+                    __syncwarp();
+                    for (int z = lane; z < kT * kDL / 4; z += 32)
+                        reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    __syncwarp();
+                    // the ic weights of every entry whose merge row is in this stage
+#pragma unroll 4
+                    for (int x = lane; x < E; x += 32) {
+                        const unsigned lr = lut[x];
+                        const int rel = (int)(lr & 0xfffu) - u0;
+                        if (rel >= 0 && rel < Uc) {
+                            const unsigned e = ent[x];
+                            float* dst = Wd + (lr >> 12) * kDL + rel * ICT;
+                            if (!(e & kDupFlag)) {
+                                if (kSplit && ICT == 4) {
+                                    cp_async16_ca(dst, Wb + (size_t)e * ICT);
+                                } else {
+                                    float w[ICT];
+                                    load_w<T, ICT>(Wb + (size_t)e * ICT, w);
+#pragma unroll
+                                    for (int k = 0; k < ICT; ++k) dst[k] = w[k];
+                                }
+                            } else {
+                                // the merge row names the target several times: add its slots in order
+                                const unsigned row = fast_div_u(e & ~kDupFlag, p.m_magic, p.m_shift);
+                                const int64_t* irow = idx_b + (long long)row * m;
+                                float w[ICT];
+#pragma unroll
+                                for (int k = 0; k < ICT; ++k) w[k] = 0.f;
+                                for (int j = 0; j < m; ++j)
+                                    if (irow[j] == t0 + (int)(lr >> 12)) {
+#pragma unroll
+                                        for (int k = 0; k < ICT; ++k)
+                                            w[k] += Elem<T>::up(Wb[((size_t)row * m + j) * ICT + k]);
+                                    }
+#pragma unroll
+                                for (int k = 0; k < ICT; ++k) dst[k] = w[k];
+                            }
+                        }
+                    }
+                    stage_rows64<T, 0>(Xs, rows8, nrows, lane, [&](int r) {
+                        return Gb + ((long long)uniq[u0 + r / ICT] * ICT + (r % ICT)) * c + c0;
+                    });
+                    cp_async_commit();
+                    cp_async_wait<0>();
+                    __syncwarp();
+                    for (int us = 0; us < rows8; us += 8) {
+                        float bv[2];
+                        const unsigned w0 = wa + us * 4;
+                        WF_LDS(bv[0], w0, 0);
+                        WF_LDS(bv[1], w0, 16);
+                        unsigned bh[2], bl[2];
+                        wf_split<kSplit>(bv[0], bh[0], bl[0]);
+                        wf_split<kSplit>(bv[1], bh[1], bl[1]);
+#pragma unroll
+                        for (int mt = 0; mt < 4; ++mt) {
+                            float a[4];
+                            const unsigned a0 = xa[mt][0] + us * (kCG * 4), a1 = xa[mt][1] + us * (kCG * 4);
+                            WF_LDS(a[0], a0, 0);
+                            WF_LDS(a[1], a1, 0);
+                            WF_LDS(a[2], a0, 4 * kCG * 4);
+                            WF_LDS(a[3], a1, 4 * kCG * 4);
+                            unsigned ah[4], al[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) wf_split<kSplit>(a[i], ah[i], al[i]);
+                            wf_mma<kSplit>(acc[mt], ah, al, bh, bl);
+                        }
+                    }
+                }
+                // D fragments -> output tile [8][kGL] in X -> 16-byte stores (added to what earlier chunks
+                // of a long entry list wrote)
+                float* Ot = Xs;
+                __syncwarp();
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    float* o = Ot + (2 * t) * kGL + 16 * mt + g;
+                    o[0] = acc[mt][0];
+                    o[kGL] = acc[mt][1];
+                    o[8] = acc[mt][2];
+                    o[kGL + 8] = acc[mt][3];
+                }
+                __syncwarp();
+                const int rsub = lane >> 4, chn = lane & 15;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int q = 2 * i + rsub;
+                    if (t0 + q < n_tgt) {
+                        T* dstp = Ob + (long long)(t0 + q) * c + c0 + chn * 4;
+                        float4 v = *reinterpret_cast<const float4*>(Ot + q * kGL + chn * 4);
+                        if (e0 > 0) {
+                            const float4 old = ld4(dstp);
+                            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                        }
+                        st4(dstp, v);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+}
+
+template <typename T, int ICT>
+int wf_dfeat_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
+    const size_t smem = size_t(kWarps) * WfScatterSmem::kTotal;
+    auto kernel = wf_dfeat_kernel<T, ICT>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
+    if (grid > need) grid = need;
+    ScopedKernelTimer timer(label, s);
+    kernel<<<(int)grid, 32 * kWarps, smem, s>>>(p);
+    note_launch();
+    return check_launch();
+}
+
+template <typename T>
+int wf_dfeat_ic(const char* label, int ic, const WfScatterParams& p, cudaStream_t s) {
+    switch (ic) {
+        case 1: return wf_dfeat_t<T, 1>(label, p, s);
+        case 2: return wf_dfeat_t<T, 2>(label, p, s);
+        case 4: return wf_dfeat_t<T, 4>(label, p, s);
+        default: return CLUSTEN_ERR_UNSUPPORTED;
+    }
+}
+
 template <typename T, int MODE, int ICT>
 int wf_tiles_t(const char* label, const WfParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfSmem<MODE>::kTotal;
@@ -606,6 +891,35 @@ int launch_tiled_wf_sum(const char* label, int dtype, const void* W, const void*
     p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;  p.tiles = (n_out + kT - 1) / kT;
     if ((long long)b * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
     return wf_tiles_dispatch<0>(label, dtype, ic, p, s);
+}
+
+bool tiled_wf_dfeat_supported(int dtype, const void* W, const void* G, const void* out, int n_out, int n, int m,
+                              int ic, int c) {
+    if (dtype != CLUSTEN_F32 && dtype != CLUSTEN_F16 && dtype != CLUSTEN_BF16) return false;
+    if (c % kCG != 0 || (ic != 1 && ic != 2 && ic != 4) || m < 1 || n < 1 || n_out < 1 || n_out > 65000) return false;
+    if ((long long)n_out * m * ic > 0x7fffffffLL) return false;
+    return aligned16({W, G, out});
+}
+
+int launch_tiled_wf_dfeat(const char* label, int dtype, const void* W, const void* G, const int64_t* idx,
+                          const InverseView& inv, void* d_feat, int b, int n_out, int n, int m, int ic, int c,
+                          cudaStream_t s) {
+    WfScatterParams p{};
+    p.W = W;  p.G = G;  p.out = d_feat;  p.idx = idx;  p.inv = inv;
+    p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;  p.tiles = (n + kT - 1) / kT;
+    if ((long long)b * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    {   // x / m for x < 2^31:  (umulhi(magic, x) + x) >> shift
+        unsigned l = 0;
+        while ((1ull << l) < (unsigned)m) ++l;
+        p.m_magic = (unsigned)(((1ull << 32) * ((1ull << l) - (unsigned)m)) / (unsigned)m + 1);
+        p.m_shift = l;
+    }
+    switch (dtype) {
+        case CLUSTEN_F32: return wf_dfeat_ic<float>(label, ic, p, s);
+        case CLUSTEN_F16: return wf_dfeat_ic<__half>(label, ic, p, s);
+        case CLUSTEN_BF16: return wf_dfeat_ic<__nv_bfloat16>(label, ic, p, s);
+        default: return CLUSTEN_ERR_DTYPE;
+    }
 }
 
 int launch_tiled_wf_dot(const char* label, int dtype, const void* F, const void* G, const int64_t* idx,
