@@ -290,6 +290,90 @@ __device__ __forceinline__ void dot_product_mma(const DotAddr& da, int mtiles) {
     else dot_product_tiles<SPLIT, false>(da, mtiles);
 }
 
+// ----------------------------------------------------------------------------- 16-bit products
+// FP16 / BF16 inputs stay 16-bit in shared memory and are multiplied with mma.sync m16n8k16 (FP32
+// accumulation, exact products).  Staged rows are [row][32 elements] = 64 bytes; the 16-byte chunk c of
+// row r is stored at chunk c ^ ((r >> 1) & 3), which makes the 8-row ldmatrix accesses conflict free.
+// Fragment layout (PTX ISA, m16n8k16): A regs a0=(g, 2t..2t+1) a1=(g+8, ..) a2=(g, 2t+8..) a3=(g+8, 2t+8..);
+// B regs b0=(k=2t..2t+1, n=g) b1=(k=2t+8.., n=g);  D as for m16n8k8.
+constexpr int kWLD16 = 56;         // row stride (elements) of the 16-bit dense weight tile [8][kWLD16]
+__device__ __forceinline__ void mma16(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2], const __half*) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma16(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2],
+                                      const __nv_bfloat16*) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma16(float (&)[4], const unsigned (&)[4], const unsigned (&)[2], const float*) {}
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// element offset of 8-element chunk c of staged 16-bit row r
+__device__ __forceinline__ int swz16(int r, int c) { return r * kC + ((c ^ ((r >> 1) & 3)) << 3); }
+
+// tiled_sum: D[ch][q] += sum_u X[u][ch] * Wd16[q][u], u < 16 ksteps.  A = X^T through ldmatrix.trans.
+template <typename T>
+__device__ __forceinline__ void sum_product16(const T* Xraw, const T* Wd16, int ksteps, int lane, float (&acc)[2][4]) {
+    const int mi = lane >> 3, rr = lane & 7, g = lane >> 2, t = lane & 3;
+    unsigned xa[2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) xa[mt] = smem_u32(Xraw + swz16((mi >> 1) * 8 + rr, 2 * mt + (mi & 1)));
+    const unsigned wa = smem_u32(Wd16 + g * kWLD16 + 2 * t);
+#pragma unroll
+    for (int ks = 0; ks < kUC / 16; ++ks) {
+        if (ks < ksteps) {
+            unsigned b[2];
+            asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(b[0]) : "r"(wa + ks * 32));
+            asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(b[1]) : "r"(wa + ks * 32 + 16));
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                unsigned a[4];
+                ldsm_x4_trans(a, xa[mt] + ks * 16 * kC * 2);
+                mma16(acc[mt], a, b, static_cast<const T*>(nullptr));
+            }
+        }
+    }
+}
+
+// tiled_dot: Sb[q][u] = sum_ch Y[q][ch] * X[u][ch] for u < 16 mtiles; yb = B fragments of the Y tile
+// (yb[ks][h] = Y[g][16 ks + 8 h + 2t .. + 1], loaded by the caller), A = X through ldmatrix.
+template <typename T>
+__device__ __forceinline__ void dot_product16(const T* Xraw, const unsigned (&yb)[2][2], float* Sb, int mtiles, int lane) {
+    const int mi = lane >> 3, rr = lane & 7, g = lane >> 2, t = lane & 3;
+    unsigned xd[2];
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) xd[ks] = smem_u32(Xraw + swz16((mi & 1) * 8 + rr, 2 * ks + (mi >> 1)));
+#pragma unroll
+    for (int mt = 0; mt < kUC / 16; ++mt) {
+        if (mt < mtiles) {
+            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                unsigned a[4];
+                ldsm_x4(a, xd[ks] + mt * 16 * kC * 2);
+                mma16(d, a, yb[ks], static_cast<const T*>(nullptr));
+            }
+            // d0=(u=16mt+g, q=2t) d1=(u, 2t+1) d2=(u+8, 2t) d3=(u+8, 2t+1)
+            float* sp = Sb + (2 * t) * kWLD + 16 * mt + g;
+            sp[0] = d[0];
+            sp[kWLD] = d[1];
+            sp[8] = d[2];
+            sp[kWLD + 8] = d[3];
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------- producer: tile analysis
 // Are the 8 rows of the tile identical, in range, and the tile complete?  One warp.
 // col0 = (2 * lane) % m and col_step = 64 % m are the column of the lane's first entry pair and its

@@ -76,6 +76,16 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         wq[k] = z / d;
         wc[k] = z - wq[k] * d;
     }
+    // 16-bit weight tiles travel in 8-element pieces: piece z = lane + 32k of an [8][m] tile, m % 8 == 0
+    int wq16[2], wc16[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int z = lane + 32 * k;
+        const int d = (m >> 3) > 0 ? (m >> 3) : 1;
+        wq16[k] = z / d;
+        wc16[k] = z - wq16[k] * d;
+    }
+    T* Wd16 = reinterpret_cast<T*>(Op);                  // MODE 0, 16-bit inputs: dense weights [8][kWLD16]
     const int col0 = (2 * lane) % m, col_step = 64 % m;
     unsigned long long qpack = 0ull;                    // 3 bits per edge: its row
 #pragma unroll
@@ -130,6 +140,9 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
             U = dedup_tile(ds, ring, lut, E, m, i0, n, MODE == 0, &rowdup, lane);
         }
         __syncwarp();                                    // the landing area is free again
+        // 16-bit inputs stay 16-bit (m16n8k16 products) unless a row repeats a neighbour: then the weights
+        // of one slot are summed in fp32 and the fp32 path below is taken
+        const bool native16 = !kIsFloat && !rowdup;
 
         for (int g = 0; g < heads; ++g) {
             const long long bb = (long long)b * heads + g;
@@ -174,10 +187,11 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                     }
                 } else {
                     const int pr = lane >> 2, pc = lane & 3;
+                    const int rows16 = (Uc + 15) & ~15;
 #pragma unroll
                     for (int k = 0; k < kUC / 8; ++k) {
                         const int r = pr + 8 * k;
-                        if (r < rows8) {
+                        if (r < rows16) {
                             int t = -1;
                             if (r < Uc) {
                                 if (identical) t = tok_s[r];
@@ -186,7 +200,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                     t = tt == kSkip ? -1 : (int)tt;
                                 }
                             }
-                            T* dst = Xraw + r * kC + pc * kPer;
+                            T* dst = Xraw + swz16(r, pc);
                             if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * kC + pc * kPer);
                             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
@@ -195,7 +209,28 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                 if (MODE == 0) {
                     // ---- weight tile -> Wd while the rows are on their way
                     const T* Wt = A + (bb * n + i0) * m;
-                    if (identical) {
+                    if (native16 && identical) {
+#pragma unroll
+                        for (int k = 0; k < 2; ++k)
+                            if (lane + 32 * k < kT * (m >> 3))
+                                cp_async16_ca(Wd16 + wq16[k] * kWLD16 + wc16[k] * 8, Wt + wq16[k] * m + wc16[k] * 8);
+                    } else if (native16) {
+                        for (int z = lane; z < kT * kWLD16 * 2 / 16; z += 32)
+                            reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        __syncwarp();
+#pragma unroll
+                        for (int k = 0; k < kEPL; ++k) {
+                            const int x = lane + 32 * k;
+                            if (x < E) {
+                                const unsigned short sl = lut[x];
+                                const int rel = (int)sl - u0;
+                                if (sl != kSkip && rel >= 0 && rel < Uc) {
+                                    const int q = (int)((qpack >> (3 * k)) & 7ull);
+                                    Wd16[q * kWLD16 + rel] = Wt[x];
+                                }
+                            }
+                        }
+                    } else if (identical) {
 #pragma unroll
                         for (int k = 0; k < 3; ++k)
                             if (lane + 32 * k < kT * m4) {
@@ -232,6 +267,8 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                             }
                         }
                     }
+                } else if (native16) {
+                    // ---- Y tile: the B fragments come straight from global memory (below)
                 } else if (ch == 0) {
                     // ---- Y tile -> Ys (fp32, row stride kYLD)
                     const T* Yt = A + (bb * n + i0) * kC;
@@ -246,20 +283,36 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                 cp_async_commit();
                 cp_async_wait<0>();
                 __syncwarp();
-                if (!kIsFloat) {
+                if (!kIsFloat && !native16) {
                     // 16-bit rows -> fp32, swizzled
 #pragma unroll
                     for (int k = 0; k < kUC / 4; ++k) {
                         const int r = qi + 4 * k;
-                        if (r < rows8) st4(Xs + r * kC + ((k & 1) ? sw_odd : sw_even), ld4(Xraw + r * kC + ci * 4));
+                        if (r < rows8)
+                            st4(Xs + r * kC + ((k & 1) ? sw_odd : sw_even), ld4(Xraw + swz16(r, ci >> 1) + (ci & 1) * 4));
                     }
                     __syncwarp();
                 }
 
                 if (MODE == 0) {
-                    sum_product_mma<kIsFloat>(sa, rows8, acc);
+                    if (native16) sum_product16<T>(Xraw, Wd16, (Uc + 15) >> 4, lane, acc);
+                    else sum_product_mma<kIsFloat>(sa, rows8, acc);
                 } else {
-                    dot_product_mma<kIsFloat>(da, (Uc + 15) >> 4);
+                    if (native16) {
+                        const int yg = lane >> 2, yt = lane & 3;
+                        unsigned yb[2][2] = {{0u, 0u}, {0u, 0u}};
+                        if (i0 + yg < n) {
+                            const unsigned* yrow = reinterpret_cast<const unsigned*>(A + (bb * n + i0 + yg) * kC);
+#pragma unroll
+                            for (int ks = 0; ks < 2; ++ks) {
+                                yb[ks][0] = yrow[8 * ks + yt];
+                                yb[ks][1] = yrow[8 * ks + 4 + yt];
+                            }
+                        }
+                        dot_product16<T>(Xraw, yb, Sb, (Uc + 15) >> 4, lane);
+                    } else {
+                        dot_product_mma<kIsFloat>(da, (Uc + 15) >> 4);
+                    }
                     __syncwarp();
                     T* Ot = out + (bb * n + i0) * m;
                     if (identical) {
@@ -376,6 +429,7 @@ scatter_tiles_kernel(const ScatterParams p) {
     float* Xs = reinterpret_cast<float*>(base);
     T* Xraw = reinterpret_cast<T*>(base + WS::kX);
     float* Wd = reinterpret_cast<float*>(base + WS::kX + WS::kXraw);
+    T* Wd16 = reinterpret_cast<T*>(Wd);                          // 16-bit inputs: dense weights [8][kWLD16]
     unsigned* edge = reinterpret_cast<unsigned*>(base + WS::kX + WS::kXraw + WS::kOp);
     float* wbuf = reinterpret_cast<float*>(base + WS::kX + WS::kXraw + WS::kOp + WS::kEdge);
     unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kX + WS::kXraw + WS::kOp + WS::kEdge + WS::kWbuf);
@@ -449,6 +503,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                 const int Lc = min(per, maxlen - r0);
                 const int Uc = Lc * ic;                                      // source rows of this pass
                 const int rows8 = (Uc + 7) & ~7;
+                const int rows16 = (Uc + 15) & ~15;
                 __syncwarp();
                 // weight index of every (entry, target) and the source rows
                 for (int r = psub; r < Lc; r += 4) {
@@ -478,8 +533,8 @@ scatter_tiles_kernel(const ScatterParams p) {
 #pragma unroll
                         for (int k = 0; k < kUC / 8; ++k) {
                             const int r = pr + 8 * k;
-                            if (r < rows8) {
-                                T* dst = Xraw + r * kC + pc * kPer;
+                            if (r < rows16) {
+                                T* dst = Xraw + swz16(r, pc);
                                 if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * p.x_row + pc * kPer);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
@@ -489,29 +544,23 @@ scatter_tiles_kernel(const ScatterParams p) {
                     if (g == 0 || p.w_head != 0) {
                         // dense weights [8][rows8]: lanes of one source row read neighbouring weights
 #pragma unroll 4
-                        for (int rr = psub; rr < rows8; rr += 4) {
-                            float w = 0.f;
+                        for (int rr = psub; rr < (kIsFloat ? rows8 : rows16); rr += 4) {
+                            T w = Elem<T>::down(0.f);
                             if (rr < Uc) {
                                 const unsigned r = fast_div((unsigned)rr, p.ic_magic, p.ic_shift);
-                                w = Elem<T>::up(Wh[edge[r * kT + myq] + ((unsigned)rr - r * (unsigned)ic)]);
+                                w = Wh[edge[r * kT + myq] + ((unsigned)rr - r * (unsigned)ic)];
                             }
-                            Wd[myq * kWLD + rr] = w;
+                            if (kIsFloat) Wd[myq * kWLD + rr] = Elem<T>::up(w);
+                            else Wd16[myq * kWLD16 + rr] = w;
                         }
                     }
                     cp_async_wait<0>();
                     __syncwarp();
-                    if (!kIsFloat) {
-#pragma unroll
-                        for (int k = 0; k < kUC / 4; ++k) {
-                            const int r = qi + 4 * k;
-                            if (r < rows8) st4(Xs + r * kC + sw, ld4(Xraw + r * kC + ci * 4));
-                        }
-                        __syncwarp();
-                    }
                     float acc[2][4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
-                    sum_product_mma<kIsFloat>(sa, rows8, acc);
+                    if (kIsFloat) sum_product_mma<true>(sa, rows8, acc);
+                    else sum_product16<T>(Xraw, Wd16, rows16 >> 4, lane, acc);
                     float* Ot = Xs;                                          // the dense weights may serve the next slab
                     const int gg = lane >> 2, tt = lane & 3;
                     __syncwarp();
@@ -646,6 +695,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                 for (int u0 = 0; u0 < U; u0 += kUC) {
                     const int Uc = min(kUC, U - u0);
                     const int rows8 = (Uc + 7) & ~7;
+                    const int rows16 = (Uc + 15) & ~15;
                     __syncwarp();
                     if (kIsFloat) {
 #pragma unroll
@@ -662,14 +712,16 @@ scatter_tiles_kernel(const ScatterParams p) {
 #pragma unroll
                         for (int k = 0; k < kUC / 8; ++k) {
                             const int r = pr + 8 * k;
-                            if (r < rows8) {
-                                T* dst = Xraw + r * kC + pc * kPer;
+                            if (r < rows16) {
+                                T* dst = Xraw + swz16(r, pc);
                                 if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * p.x_row + pc * kPer);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
                     }
                     cp_async_commit();
+                    // 16-bit inputs stay 16-bit unless a weight of this chunk is a sum over repeated slots
+                    const bool native16 = !kIsFloat && !any_flag;
                     for (int z = lane; z < kT * kWLD / 4; z += 32)
                         reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                     cp_async_wait<0>();
@@ -678,18 +730,22 @@ scatter_tiles_kernel(const ScatterParams p) {
                     for (int x = lane; x < E; x += 32) {
                         const unsigned lr = lut[x];
                         const int rel = (int)(lr & 0xfffu) - u0;
-                        if (rel >= 0 && rel < Uc) Wd[(lr >> 12) * kWLD + rel] = wbuf[x];
+                        if (rel >= 0 && rel < Uc) {
+                            if (native16) Wd16[(lr >> 12) * kWLD16 + rel] = Elem<T>::down(wbuf[x]);
+                            else Wd[(lr >> 12) * kWLD + rel] = wbuf[x];
+                        }
                     }
                     __syncwarp();
-                    if (!kIsFloat) {
+                    if (!kIsFloat && !native16) {
 #pragma unroll
                         for (int k = 0; k < kUC / 4; ++k) {
                             const int r = qi + 4 * k;
-                            if (r < rows8) st4(Xs + r * kC + sw, ld4(Xraw + r * kC + ci * 4));
+                            if (r < rows8) st4(Xs + r * kC + sw, ld4(Xraw + swz16(r, ci >> 1) + (ci & 1) * 4));
                         }
                         __syncwarp();
                     }
-                    sum_product_mma<kIsFloat>(sa, rows8, acc);
+                    if (native16) sum_product16<T>(Xraw, Wd16, rows16 >> 4, lane, acc);
+                    else sum_product_mma<kIsFloat>(sa, rows8, acc);
                 }
                 // D fragments -> output tile in shared memory -> 16-byte stores (added to what earlier
                 // chunks of a long edge list wrote)
