@@ -396,6 +396,7 @@ struct ScatterParams {
     const int64_t* idx;  int idx_rows;  int m;                   // nbhd_idx [batch][idx_rows][m]
     InverseView inv;  int n_tgt;
     int ic, heads, batch, tiles;
+    int w_pairs;                                                // W may be read in aligned 32-bit words
     unsigned m_magic, m_shift, ic_magic, ic_shift;              // x / d = (umulhi(magic, x) + x) >> shift
 };
 __device__ __forceinline__ unsigned fast_div(unsigned x, unsigned magic, unsigned shift) {
@@ -663,6 +664,14 @@ scatter_tiles_kernel(const ScatterParams p) {
                             if (e & kDupFlag) wbuf[x] = 0.f;
                             else cp_async4_ca(wbuf + x, Wh + e);
                         }
+                    } else if (!any_flag && p.w_pairs) {
+                        // 16-bit weights: copy the aligned 32-bit word that holds the element; the half is
+                        // picked when the dense weights are filled in
+#pragma unroll 4
+                        for (int x = lane; x < E; x += 32) {
+                            const uintptr_t a = reinterpret_cast<uintptr_t>(Wh + edge[x]);
+                            cp_async4_ca(wbuf + x, reinterpret_cast<const void*>(a & ~uintptr_t(3)));
+                        }
                     } else {
 #pragma unroll 4
                         for (int x = lane; x < E; x += 32) {
@@ -731,8 +740,16 @@ scatter_tiles_kernel(const ScatterParams p) {
                         const unsigned lr = lut[x];
                         const int rel = (int)(lr & 0xfffu) - u0;
                         if (rel >= 0 && rel < Uc) {
-                            if (native16) Wd16[(lr >> 12) * kWLD16 + rel] = Elem<T>::down(wbuf[x]);
-                            else Wd[(lr >> 12) * kWLD + rel] = wbuf[x];
+                            if (native16 && p.w_pairs) {
+                                const unsigned raw = reinterpret_cast<const unsigned*>(wbuf)[x];
+                                const bool high = (reinterpret_cast<uintptr_t>(Wh + edge[x]) & 2) != 0;
+                                reinterpret_cast<unsigned short*>(Wd16)[(lr >> 12) * kWLD16 + rel] =
+                                    (unsigned short)(high ? raw >> 16 : raw & 0xffffu);
+                            } else if (native16) {
+                                Wd16[(lr >> 12) * kWLD16 + rel] = Elem<T>::down(wbuf[x]);
+                            } else {
+                                Wd[(lr >> 12) * kWLD + rel] = wbuf[x];
+                            }
                         }
                     }
                     __syncwarp();
@@ -830,6 +847,9 @@ int scatter_tiles_t(const char* label, ScatterParams p, cudaStream_t s) {
     if ((long long)p.batch * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
     div_magic((unsigned)p.m, &p.m_magic, &p.m_shift);
     div_magic((unsigned)p.ic, &p.ic_magic, &p.ic_shift);
+    // reading the 32-bit word around a 16-bit element stays inside W when W starts on a 4-byte boundary
+    // and holds an even number of elements
+    p.w_pairs = reinterpret_cast<uintptr_t>(p.W) % 4 == 0 && p.w_batch % 2 == 0;
     const size_t smem = size_t(kWarps) * ScatterSmem<T>::kTotal;
     auto kernel = scatter_tiles_kernel<T>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

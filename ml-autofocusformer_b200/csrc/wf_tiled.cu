@@ -169,6 +169,42 @@ __device__ __forceinline__ void stage_rows64(float* Xs, int rows8, int n_rows, i
     }
 }
 
+// 16-bit rows of 64 channels kept 16-bit: 128 bytes per row, 16-byte chunk c of row r at c ^ (r & 7)
+// (conflict-free for ldmatrix with and without .trans)
+constexpr int kDL16 = 40;           // row stride (elements) of the 16-bit dense weight tile
+__device__ __forceinline__ int swz64(int r, int c) { return r * kCG + ((c ^ (r & 7)) << 3); }
+template <typename T, typename SrcFn>
+__device__ __forceinline__ void stage_rows64_raw(T* X16, int rows16, int n_rows, int lane, SrcFn src) {
+    const int rsub = lane >> 3, c8 = lane & 7;
+#pragma unroll 4
+    for (int i = 0; i < kUW / 4; ++i) {
+        const int r = 4 * i + rsub;
+        if (r < rows16) {
+            T* dst = X16 + swz64(r, c8);
+            if (r < n_rows) cp_async16_cg(dst, src(r) + c8 * 8);
+            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+}
+// ICT consecutive 16-bit elements, unconverted
+template <typename T, int ICT> __device__ __forceinline__ void load_raw(const T* p, unsigned short (&w)[ICT]) {
+    if constexpr (ICT == 4) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        w[0] = (unsigned short)(v.x & 0xffffu);
+        w[1] = (unsigned short)(v.x >> 16);
+        w[2] = (unsigned short)(v.y & 0xffffu);
+        w[3] = (unsigned short)(v.y >> 16);
+    } else {
+#pragma unroll
+        for (int k = 0; k < ICT; ++k) w[k] = reinterpret_cast<const unsigned short*>(p)[k];
+    }
+}
+__device__ __forceinline__ unsigned lds32(unsigned addr) {
+    unsigned v;
+    asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+
 template <typename T, int ICT> __device__ __forceinline__ void load_w(const T* p, float (&w)[ICT]) {
     if constexpr (ICT == 4) {
         const float4 v = ld4(p);
@@ -313,6 +349,53 @@ wf_tiles_kernel(const WfParams p) {
                     const int Uc = min(kUW, U - u0);
                     const int rows8 = (Uc + 7) & ~7;
                     __syncwarp();
+                    if (!kSplit && !rowdup) {
+                        // 16-bit inputs stay 16-bit: m16n8k16 products, A = X^T through ldmatrix.trans
+                        const int rows16 = (Uc + 15) & ~15;
+                        T* X16 = reinterpret_cast<T*>(Xs);
+                        unsigned short* Wd16 = reinterpret_cast<unsigned short*>(Op);
+                        stage_rows64_raw<T>(X16, rows16, Uc, lane,
+                                            [&](int r) { return Fb + (long long)uniq[u0 + r] * c; });
+                        cp_async_commit();
+                        for (int z = lane; z < ICT * kT * kDL16 * 2 / 16; z += 32)
+                            reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < kEPL; ++i) {
+                            const int x = lane + 32 * i;
+                            if (x < E) {
+                                const unsigned short lr = lut[x];
+                                const int rel = (int)(lr & 0xfffu) - u0;
+                                if (lr != kSkip && rel >= 0 && rel < Uc && woff[i] >= 0) {
+                                    unsigned short w[ICT];
+                                    load_raw<T, ICT>(Wb + woff[i], w);
+#pragma unroll
+                                    for (int k = 0; k < ICT; ++k) Wd16[(k * kT + (lr >> 12)) * kDL16 + rel] = w[k];
+                                }
+                            }
+                        }
+                        cp_async_wait<0>();
+                        __syncwarp();
+                        const int mi = lane >> 3, rr = lane & 7;
+                        unsigned xa16[4];
+#pragma unroll
+                        for (int mt = 0; mt < 4; ++mt) xa16[mt] = smem_u32(X16 + swz64((mi >> 1) * 8 + rr, 2 * mt + (mi & 1)));
+                        const unsigned wa16 = smem_u32(Wd16 + g * kDL16 + 2 * t);
+                        for (int ks = 0; ks < (rows16 >> 4); ++ks) {
+                            unsigned a[4][4];
+#pragma unroll
+                            for (int mt = 0; mt < 4; ++mt) ldsm_x4_trans(a[mt], xa16[mt] + ks * 16 * kCG * 2);
+#pragma unroll
+                            for (int k = 0; k < ICT; ++k) {
+                                unsigned bq[2];
+                                bq[0] = lds32(wa16 + (k * kT * kDL16 + 16 * ks) * 2);
+                                bq[1] = lds32(wa16 + (k * kT * kDL16 + 16 * ks + 8) * 2);
+#pragma unroll
+                                for (int mt = 0; mt < 4; ++mt) mma16(acc[k][mt], a[mt], bq, static_cast<const T*>(nullptr));
+                            }
+                        }
+                        continue;
+                    }
                     stage_rows64<T, 0>(Xs, rows8, Uc, lane,
                                        [&](int r) { return Fb + (long long)uniq[u0 + r] * c; });
                     cp_async_commit();
@@ -444,6 +527,51 @@ wf_tiles_kernel(const WfParams p) {
                 for (int c0 = 0; c0 < c; c0 += kCG) {
                     const T* Fb = Fg + (long long)b * n * c + c0;
                     __syncwarp();
+                    if constexpr (!kSplit) {
+                        // 16-bit inputs stay 16-bit: A = gradient tile and B = X^T, both through ldmatrix
+                        const int rows16 = (Uc + 15) & ~15;
+                        T* X16 = reinterpret_cast<T*>(Xs);
+                        T* Y16 = reinterpret_cast<T*>(Op);
+                        stage_rows64_raw<T>(X16, rows16, Uc, lane,
+                                            [&](int r) { return Fb + (long long)uniq[u0 + r] * c; });
+                        if (ch == 0 || multi) {
+                            const int rsub = lane >> 3, c8 = lane & 7;
+#pragma unroll 2
+                            for (int i = 0; i < MT * 16 / 4; ++i) {
+                                const int r = 4 * i + rsub;                       // k 8 + q
+                                const int rq = r < ICT * kT ? rowsS[r & 7] : -1;
+                                T* dst = Y16 + swz64(r, c8);
+                                if (rq >= 0) cp_async16_cg(dst, Gb + ((long long)rq * ICT + (r >> 3)) * c + c0 + c8 * 8);
+                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                        }
+                        cp_async_commit();
+                        cp_async_wait<0>();
+                        __syncwarp();
+                        const int mi = lane >> 3, rr = lane & 7;
+                        unsigned afr[MT][4][4];
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks)
+                                ldsm_x4(afr[mt][ks], smem_u32(Y16 + swz64(16 * mt + (mi & 1) * 8 + rr, 2 * ks + (mi >> 1))));
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt) {
+                            if (nt * 8 < rows16) {
+                                unsigned bfr[2][4];
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) ldsm_x4(bfr[h], smem_u32(X16 + swz64(8 * nt + rr, 4 * h + mi)));
+#pragma unroll
+                                for (int ks = 0; ks < 4; ++ks) {
+                                    const unsigned bq[2] = {bfr[ks >> 1][(ks & 1) * 2], bfr[ks >> 1][(ks & 1) * 2 + 1]};
+#pragma unroll
+                                    for (int mt = 0; mt < MT; ++mt)
+                                        mma16(acc[mt][nt], afr[mt][ks], bq, static_cast<const T*>(nullptr));
+                                }
+                            }
+                        }
+                        continue;
+                    }
                     stage_rows64<T, 1>(Xs, rows8, Uc, lane,
                                        [&](int r) { return Fb + (long long)uniq[u0 + r] * c; });
                     if (ch == 0 || multi) {
@@ -643,6 +771,7 @@ wf_dfeat_kernel(const WfScatterParams p) {
         for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kEE) {
             const int E = max(0, min(kEE, E_total - e0));
             int lo = INT_MAX, hi = -1;
+            bool any_flag = false;
             __syncwarp();
 #pragma unroll 4
             for (int x = lane; x < E; x += 32) {
@@ -664,7 +793,9 @@ wf_dfeat_kernel(const WfScatterParams p) {
                 lut[x] = (unsigned short)(r << 12);
                 lo = min(lo, row);
                 hi = max(hi, row);
+                any_flag = any_flag || (e & kDupFlag) != 0u;
             }
+            any_flag = __any_sync(kFull, any_flag);
             int U = 0;
             if (E > 0) {
                 bool unused = false;
@@ -684,6 +815,46 @@ wf_dfeat_kernel(const WfScatterParams p) {
                     const int nrows = Uc * ICT;
                     const int rows8 = (nrows + 7) & ~7;
                     __syncwarp();
+                    if (!kSplit && !any_flag) {
+                        // 16-bit inputs stay 16-bit (no weight of this chunk is a sum over repeated slots)
+                        const int rows16 = (nrows + 15) & ~15;
+                        T* X16 = reinterpret_cast<T*>(Xs);
+                        unsigned short* Wd16 = reinterpret_cast<unsigned short*>(Wd);
+                        stage_rows64_raw<T>(X16, rows16, nrows, lane, [&](int r) {
+                            return Gb + ((long long)uniq[u0 + r / ICT] * ICT + (r % ICT)) * c + c0;
+                        });
+                        cp_async_commit();
+                        for (int z = lane; z < kT * kDL16 * 2 / 16; z += 32)
+                            reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        __syncwarp();
+#pragma unroll 4
+                        for (int x = lane; x < E; x += 32) {
+                            const unsigned lr = lut[x];
+                            const int rel = (int)(lr & 0xfffu) - u0;
+                            if (rel >= 0 && rel < Uc) {
+                                unsigned short w[ICT];
+                                load_raw<T, ICT>(Wb + (size_t)ent[x] * ICT, w);
+#pragma unroll
+                                for (int k = 0; k < ICT; ++k) Wd16[(lr >> 12) * kDL16 + rel * ICT + k] = w[k];
+                            }
+                        }
+                        cp_async_wait<0>();
+                        __syncwarp();
+                        const int mi = lane >> 3, rr = lane & 7;
+                        const unsigned wa16 = smem_u32(Wd16 + g * kDL16 + 2 * t);
+                        for (int ks = 0; ks < (rows16 >> 4); ++ks) {
+                            unsigned bq[2];
+                            bq[0] = lds32(wa16 + 16 * ks * 2);
+                            bq[1] = lds32(wa16 + (16 * ks + 8) * 2);
+#pragma unroll
+                            for (int mt = 0; mt < 4; ++mt) {
+                                unsigned a[4];
+                                ldsm_x4_trans(a, smem_u32(X16 + swz64((mi >> 1) * 8 + rr, 2 * mt + (mi & 1))) + ks * 16 * kCG * 2);
+                                mma16(acc[mt], a, bq, static_cast<const T*>(nullptr));
+                            }
+                        }
+                        continue;
+                    }
                     for (int z = lane; z < kT * kDL / 4; z += 32)
                         reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                     __syncwarp();
