@@ -129,6 +129,35 @@ __device__ __forceinline__ void mma_block(float (&d)[4], const float (&a)[4], co
     mma_tf32(d, ah, bh);
 }
 
+// Two accumulators fed by the same B fragment: the passes of the two products alternate, so that an MMA
+// never directly follows the one whose accumulator it reads.
+template <bool SPLIT>
+__device__ __forceinline__ void mma_pair(float (&d)[2][4], const float (&a)[2][4], const float (&b)[2]) {
+    unsigned ah[2][4], bh[2];
+    if (SPLIT) {
+        unsigned al[2][4], bl[2];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) split_tf32(a[mt][i], ah[mt][i], al[mt][i]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) split_tf32(b[i], bh[i], bl[i]);
+        mma_tf32(d[0], al[0], bh);
+        mma_tf32(d[1], al[1], bh);
+        mma_tf32(d[0], ah[0], bl);
+        mma_tf32(d[1], ah[1], bl);
+    } else {
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ah[mt][i] = __float_as_uint(a[mt][i]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) bh[i] = __float_as_uint(b[i]);
+    }
+    mma_tf32(d[0], ah[0], bh);
+    mma_tf32(d[1], ah[1], bh);
+}
+
 // Fragment loads use 32-bit shared-memory addresses that are fixed per warp (computed once per kernel)
 // plus compile-time offsets.
 // Per-warp addresses for tiled_sum:  D[c][q] += sum_u Xs[u][c] * Wd[q][u].
@@ -175,12 +204,10 @@ __device__ __forceinline__ void sum_steps48(const SumAddr& sa, float (&acc)[2][4
     if constexpr (KS + 1 < kUC / 8) {
         float bn[2], an[2][4];
         sum_load<KS + 1>(sa, bn, an);
-        mma_block<SPLIT, 0>(acc[0], a[0], b);
-        mma_block<SPLIT, 0>(acc[1], a[1], b);
+        mma_pair<SPLIT>(acc, a, b);
         sum_steps48<SPLIT, KS + 1>(sa, acc, bn, an);
     } else {
-        mma_block<SPLIT, 0>(acc[0], a[0], b);
-        mma_block<SPLIT, 0>(acc[1], a[1], b);
+        mma_pair<SPLIT>(acc, a, b);
     }
 }
 
@@ -197,8 +224,7 @@ __device__ __forceinline__ void sum_product_mma(const SumAddr& sa, int rows8, fl
         for (int u0 = 0; u0 < rows8; u0 += 8) {
             float b[2], a[2][4];
             sum_load<0>(p, b, a);
-            mma_block<SPLIT, 0>(acc[0], a[0], b);
-            mma_block<SPLIT, 0>(acc[1], a[1], b);
+            mma_pair<SPLIT>(acc, a, b);
             p.w += 8 * 4;
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) {
@@ -240,6 +266,13 @@ __device__ __forceinline__ void dot_product_tiles(const DotAddr& da, int mtiles)
         if (ks == 1) { CLUSTEN_LDS(bb[0], da.y, 32); CLUSTEN_LDS(bb[1], da.y, 48); }
         if (ks == 2) { CLUSTEN_LDS(bb[0], da.y, 64); CLUSTEN_LDS(bb[1], da.y, 80); }
         if (ks == 3) { CLUSTEN_LDS(bb[0], da.y, 96); CLUSTEN_LDS(bb[1], da.y, 112); }
+        unsigned bh[2], bl[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (SPLIT) split_tf32(bb[i], bh[i], bl[i]);
+            else { bh[i] = __float_as_uint(bb[i]); bl[i] = 0u; }
+        }
+        unsigned ah[kUC / 16][4];
 #pragma unroll
         for (int mt = 0; mt < kUC / 16; ++mt) {
             if (FULL || mt < mtiles) {
@@ -255,9 +288,25 @@ __device__ __forceinline__ void dot_product_tiles(const DotAddr& da, int mtiles)
                     CLUSTEN_LDS(a[0], da.x[2 * ks], 4096);     CLUSTEN_LDS(a[1], da.x[2 * ks], 5120);
                     CLUSTEN_LDS(a[2], da.x[2 * ks + 1], 4096); CLUSTEN_LDS(a[3], da.x[2 * ks + 1], 5120);
                 }
-                mma_block<SPLIT, 0>(acc[mt], a, bb);
+                // the low-part pass of a row tile goes out as soon as its operands are there; the other two
+                // passes follow tile by tile below, so consecutive MMAs never share an accumulator
+                unsigned al[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (SPLIT) split_tf32(a[i], ah[mt][i], al[i]);
+                    else ah[mt][i] = __float_as_uint(a[i]);
+                }
+                if (SPLIT) mma_tf32(acc[mt], al, bh);
             }
         }
+        if (SPLIT) {
+#pragma unroll
+            for (int mt = 0; mt < kUC / 16; ++mt)
+                if (FULL || mt < mtiles) mma_tf32(acc[mt], ah[mt], bl);
+        }
+#pragma unroll
+        for (int mt = 0; mt < kUC / 16; ++mt)
+            if (FULL || mt < mtiles) mma_tf32(acc[mt], ah[mt], bh);
     }
     // D fragment -> Sb[q][u]: d0=(u=16mt+g, q=2t) d1=(u, 2t+1) d2=(u+8, 2t) d3=(u+8, 2t+1)
 #pragma unroll

@@ -31,7 +31,7 @@ namespace {
 // ----------------------------------------------------------------------------- the kernel
 // MODE 0: tiled_sum (A = W [bb, n, m]),  MODE 1: tiled_dot (A = Y [bb, n, 32]); X = [bb, n, 32]
 template <typename T, int MODE>
-__global__ void __launch_bounds__(32 * kWarps, 5)
+__global__ void __launch_bounds__(32 * kWarps, MODE == 0 ? 5 : 4)
 gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int64_t* __restrict__ idx,
                     T* __restrict__ out, int batch, int heads, int n, int m, int tiles) {
     extern __shared__ __align__(128) unsigned char smem_raw[];

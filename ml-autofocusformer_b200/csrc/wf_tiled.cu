@@ -110,6 +110,19 @@ __device__ __forceinline__ void wf_mma(float (&d)[4], const unsigned (&ah)[4], c
     }
     mma_tf32(d, ah, bh);
 }
+// NM accumulators fed by the same B fragment, pass by pass: consecutive MMAs never share an accumulator
+template <bool SPLIT, int NM>
+__device__ __forceinline__ void wf_mma_row(float (&d)[NM][4], const unsigned (&ah)[NM][4], const unsigned (&al)[NM][4],
+                                           const unsigned (&bh)[2], const unsigned (&bl)[2]) {
+    if (SPLIT) {
+#pragma unroll
+        for (int mt = 0; mt < NM; ++mt) mma_tf32(d[mt], al[mt], bh);
+#pragma unroll
+        for (int mt = 0; mt < NM; ++mt) mma_tf32(d[mt], ah[mt], bl);
+    }
+#pragma unroll
+    for (int mt = 0; mt < NM; ++mt) mma_tf32(d[mt], ah[mt], bh);
+}
 
 // 8 elements of T -> two float4
 __device__ __forceinline__ void up8(const uint4 r, const __half*, float4& a, float4& b) {
@@ -465,8 +478,7 @@ wf_tiles_kernel(const WfParams p) {
                             unsigned bh[2], bl[2];
                             wf_split<kSplit>(bv[0], bh[0], bl[0]);
                             wf_split<kSplit>(bv[1], bh[1], bl[1]);
-#pragma unroll
-                            for (int mt = 0; mt < 4; ++mt) wf_mma<kSplit>(acc[k][mt], ah[mt], al[mt], bh, bl);
+                            wf_mma_row<kSplit, 4>(acc[k], ah, al, bh, bl);
                         }
                     }
                 }
@@ -627,8 +639,14 @@ wf_tiles_kernel(const WfParams p) {
                                 unsigned bh[2], bl[2];
                                 wf_split<kSplit>(bv[0], bh[0], bl[0]);
                                 wf_split<kSplit>(bv[1], bh[1], bl[1]);
+                                if (kSplit) {
 #pragma unroll
-                                for (int mt = 0; mt < MT; ++mt) wf_mma<kSplit>(acc[mt][nt], ah[mt], al[mt], bh, bl);
+                                    for (int mt = 0; mt < MT; ++mt) mma_tf32(acc[mt][nt], al[mt], bh);
+#pragma unroll
+                                    for (int mt = 0; mt < MT; ++mt) mma_tf32(acc[mt][nt], ah[mt], bl);
+                                }
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) mma_tf32(acc[mt][nt], ah[mt], bh);
                             }
                         }
                     }
@@ -907,6 +925,7 @@ wf_dfeat_kernel(const WfScatterParams p) {
                         unsigned bh[2], bl[2];
                         wf_split<kSplit>(bv[0], bh[0], bl[0]);
                         wf_split<kSplit>(bv[1], bh[1], bl[1]);
+                        unsigned ah[4][4], al[4][4];
 #pragma unroll
                         for (int mt = 0; mt < 4; ++mt) {
                             float a[4];
@@ -915,11 +934,10 @@ wf_dfeat_kernel(const WfScatterParams p) {
                             WF_LDS(a[1], a1, 0);
                             WF_LDS(a[2], a0, 4 * kCG * 4);
                             WF_LDS(a[3], a1, 4 * kCG * 4);
-                            unsigned ah[4], al[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) wf_split<kSplit>(a[i], ah[i], al[i]);
-                            wf_mma<kSplit>(acc[mt], ah, al, bh, bl);
+                            for (int i = 0; i < 4; ++i) wf_split<kSplit>(a[i], ah[mt][i], al[mt][i]);
                         }
+                        wf_mma_row<kSplit, 4>(acc, ah, al, bh, bl);
                     }
                 }
                 // D fragments -> output tile [8][kGL] in X -> 16-byte stores (added to what earlier chunks
