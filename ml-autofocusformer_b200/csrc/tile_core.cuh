@@ -1,6 +1,6 @@
 // Building blocks of the tiled CLUSTEN kernels: constants, cp.async / conversion helpers, the
 // tensor-core products on staged neighbour rows and the warp-level de-duplication of a tile's indices.
-// Included by tiled_fwd.cu (QK / AV gather side, scatter side) and wf_tiled.cu (WF gather side); every
+// Included by tiled_fwd.cu (QK / AV gather and scatter side) and wf_tiled.cu (the WF kernels); every
 // definition has internal linkage.
 #pragma once
 

@@ -1,4 +1,4 @@
-// Tiled CLUSTEN kernels for head_dim 32 (declarations; see tiled.cu).
+// Tiled CLUSTEN kernels (declarations; tiled_fwd.cu: QK / AV, wf_tiled.cu: WF).
 #pragma once
 #include "common.cuh"
 

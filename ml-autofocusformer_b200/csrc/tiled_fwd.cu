@@ -1,16 +1,17 @@
-// Tiled kernels for the gather side of QK / AV (head_dim 32, m <= 48):
+// Tiled kernels for QK / AV (head_dim 32, m <= 48):
 //
-//   tiled_sum   out[i,:] = sum_j W[i,j] * X[idx[i,j],:]     AV forward, d_query
-//   tiled_dot   out[i,j] = <X[idx[i,j],:], Y[i,:]>          QK forward, d_attn
+//   tiled_sum      out[i,:] = sum_j W[i,j] * X[idx[i,j],:]          AV forward, d_query
+//   tiled_dot      out[i,j] = <X[idx[i,j],:], Y[i,:]>               QK forward, d_attn
+//   tiled_scatter  out[t,:] = sum_{idx[i,j]=t} W[i,j] * X[i,:]      d_key, d_value (over the inverse index)
 //
 // Every WARP works on its own: it takes a tile of 8 consecutive rows (one AutoFocusFormer
 // cluster) of one batch element, reads the tile's int64 neighbour indices once (cp.async into
 // shared memory) and then serves all heads from them.  For a head it stages each distinct
 // neighbour row ONCE in shared memory (cp.async, 16-byte chunks XOR-swizzled by row) and
-// multiplies the 8 rows of the tile against the staged rows with a register-tiled product on
-// the FP32 pipes (two-wide FMAs).  There is no block-level synchronisation; latency is hidden by
-// running about twenty such warps per SM (11 KB of shared memory each) and by L2 prefetches of
-// the next tile's index and weight lines.
+// multiplies the 8 rows of the tile against the staged rows on the tensor cores (mma.sync:
+// TF32 with a three-pass split for FP32 inputs, m16n8k16 for FP16 / BF16 inputs).  There is no
+// block-level synchronisation; latency is hidden by running 16 to 20 such warps per SM (9 to 14 KB
+// of shared memory each) and by L2 prefetches of the next tile's index and weight lines.
 //
 // Tiles whose 8 rows are identical (the tokens of a cluster share their neighbourhood) need no
 // de-duplication: the slot of a neighbour is its column.  Otherwise the warp de-duplicates the

@@ -25,6 +25,9 @@ import sys
 import sysconfig
 from concurrent.futures import ThreadPoolExecutor
 
+# where the reference checkout keeps the extension sources (override with CLUSTEN_REFERENCE_SRC)
+DEFAULT_SRC = os.environ.get("CLUSTEN_REFERENCE_SRC", "/root/reference/clusten/src")
+
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 MODULES = ("clustenqk_cuda", "clustenav_cuda", "clustenwf_cuda")
@@ -37,7 +40,7 @@ def _run(cmd):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default="/root/reference/clusten/src")
+    ap.add_argument("--src", default=DEFAULT_SRC)
     ap.add_argument("-j", type=int, default=3)
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args()
