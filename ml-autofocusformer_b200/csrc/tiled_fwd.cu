@@ -31,10 +31,12 @@ namespace {
 
 // ----------------------------------------------------------------------------- the kernel
 // MODE 0: tiled_sum (A = W [bb, n, m]),  MODE 1: tiled_dot (A = Y [bb, n, 32]); X = [bb, n, 32]
-template <typename T, int MODE>
+// M48: m = 48 (every AutoFocusFormer stage but the last) is known at compile time
+template <typename T, int MODE, bool M48>
 __global__ void __launch_bounds__(32 * kWarps, MODE == 0 ? 5 : 4)
 gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int64_t* __restrict__ idx,
-                    T* __restrict__ out, int batch, int heads, int n, int m, int tiles) {
+                    T* __restrict__ out, int batch, int heads, int n, int m_arg, int tiles) {
+    const int m = M48 ? kMmax : m_arg;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using WS = WarpSmem<T, MODE>;
     constexpr bool kIsFloat = WS::kIsFloat;
@@ -259,6 +261,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                             }
                         } else if (lane < kT) {
                             // some row repeats a neighbour: one lane per row adds the weights in column order
+#pragma unroll 1
                             for (int j = 0; j < m; ++j) {
                                 const unsigned short sl = lut[lane * m + j];
                                 const int rel = (int)sl - u0;
@@ -418,7 +421,9 @@ template <typename T> struct ScatterSmem {
 };
 static_assert(2 * kES * 2 <= kUC * kC * 4, "token and slot scratch must fit in the row buffer");
 
-template <typename T>
+// ATT48: attention tables with m = 48 and ic = 1 (every AutoFocusFormer stage but the last): the divisions by
+// m and ic and the edge loops' trip arithmetic are resolved at compile time.
+template <typename T, bool ATT48>
 __global__ void __launch_bounds__(32 * kWarps, 4)
 scatter_tiles_kernel(const ScatterParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -445,7 +450,9 @@ scatter_tiles_kernel(const ScatterParams p) {
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
     const SumAddr sa = make_sum_addr(Wd, Xs, lane);
     const int sw = (ci ^ (qi << 1)) << 2;                       // chunk swizzle of staged row qi + 4k
-    const int m = p.m, ic = p.ic, n_tgt = p.n_tgt;
+    const int m = ATT48 ? 48 : p.m, ic = ATT48 ? 1 : p.ic, n_tgt = p.n_tgt;
+    auto div_m = [&](unsigned x) { return ATT48 ? x / 48u : fast_div(x, p.m_magic, p.m_shift); };
+    auto div_ic = [&](unsigned x) { return ATT48 ? x : fast_div(x, p.ic_magic, p.ic_shift); };
     const T* Wg = static_cast<const T*>(p.W);
     const T* Xg = static_cast<const T*>(p.X);
     T* Og = static_cast<T*>(p.out);
@@ -491,7 +498,7 @@ scatter_tiles_kernel(const ScatterParams p) {
             for (int r0 = 0; r0 < maxlen; r0 += 4) {                         // all lanes take every trip
                 const int r = min(r0 + psub, maxlen - 1);
                 const unsigned e = (unsigned)__ldg(qent + r);
-                const unsigned row = fast_div(e & ~kDupFlag, p.m_magic, p.m_shift);
+                const unsigned row = div_m(e & ~kDupFlag);
                 const unsigned row0 = __shfl_sync(kFull, row, lane & 24);       // target 0's row, same position
                 uniform = uniform && !(e & kDupFlag) && row == row0;
             }
@@ -512,7 +519,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                     const unsigned plain = (unsigned)__ldg(qent + r0 + r);
                     edge[r * kT + myq] = plain * (unsigned)ic;
                     if (myq == 0) {
-                        const unsigned src = fast_div(plain, p.m_magic, p.m_shift) * (unsigned)ic;
+                        const unsigned src = div_m(plain) * (unsigned)ic;
                         for (int k = 0; k < ic; ++k) uniq[r * ic + k] = (unsigned short)(src + k);
                     }
                 }
@@ -549,7 +556,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                         for (int rr = psub; rr < (kIsFloat ? rows8 : rows16); rr += 4) {
                             T w = Elem<T>::down(0.f);
                             if (rr < Uc) {
-                                const unsigned r = fast_div((unsigned)rr, p.ic_magic, p.ic_shift);
+                                const unsigned r = div_ic((unsigned)rr);
                                 w = Wh[edge[r * kT + myq] + ((unsigned)rr - r * (unsigned)ic)];
                             }
                             if (kIsFloat) Wd[myq * kWLD + rr] = Elem<T>::up(w);
@@ -629,11 +636,11 @@ scatter_tiles_kernel(const ScatterParams p) {
                         o0 = off[j];
                     }
                 const unsigned q = (unsigned)(pe - o0);                     // position inside the fanned-out segment
-                const unsigned qe = fast_div(q, p.ic_magic, p.ic_shift);     // entry inside the segment
+                const unsigned qe = div_ic(q);     // entry inside the segment
                 const unsigned k = q - qe * (unsigned)ic;
                 const unsigned e = (unsigned)__ldg(entries + s0 + (int)qe);
                 const unsigned plain = e & ~kDupFlag;                       // row * m + slot
-                const unsigned src = fast_div(plain, p.m_magic, p.m_shift);
+                const unsigned src = div_m(plain);
                 edge[x] = (plain * (unsigned)ic + k) | (e & kDupFlag);
                 const int srow = (int)(src * (unsigned)ic + k);
                 ds.tok[x] = (unsigned short)srow;
@@ -686,12 +693,13 @@ scatter_tiles_kernel(const ScatterParams p) {
                             const unsigned e = edge[x];
                             if (e & kDupFlag) {
                                 const unsigned we = e & ~kDupFlag;
-                                const unsigned pl = fast_div(we, p.ic_magic, p.ic_shift);
+                                const unsigned pl = div_ic(we);
                                 const unsigned k = we - pl * (unsigned)ic;
-                                const unsigned row = fast_div(pl, p.m_magic, p.m_shift);
+                                const unsigned row = div_m(pl);
                                 const int t = t0 + (lut[x] >> 12);
                                 const int64_t* irow = idx_b + (long long)row * m;
                                 float w = 0.f;
+#pragma unroll 1
                                 for (int j = 0; j < m; ++j)
                                     if (irow[j] == t) w += Elem<T>::up(Wh[((long long)row * m + j) * ic + k]);
                                 wbuf[x] = w;
@@ -814,7 +822,7 @@ int gather_tiles_t(const char* label, const void* A, const void* X, const int64_
     const int tiles = (n + kT - 1) / kT;
     if ((long long)b * tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
     const size_t smem = size_t(kWarps) * WarpSmem<T, MODE>::kTotal;
-    auto kernel = gather_tiles_kernel<T, MODE>;
+    auto kernel = m == kMmax ? gather_tiles_kernel<T, MODE, true> : gather_tiles_kernel<T, MODE, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
@@ -852,7 +860,7 @@ int scatter_tiles_t(const char* label, ScatterParams p, cudaStream_t s) {
     // and holds an even number of elements
     p.w_pairs = reinterpret_cast<uintptr_t>(p.W) % 4 == 0 && p.w_batch % 2 == 0;
     const size_t smem = size_t(kWarps) * ScatterSmem<T>::kTotal;
-    auto kernel = scatter_tiles_kernel<T>;
+    auto kernel = (p.m == 48 && p.ic == 1) ? scatter_tiles_kernel<T, true> : scatter_tiles_kernel<T, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
