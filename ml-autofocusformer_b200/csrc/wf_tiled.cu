@@ -240,7 +240,8 @@ template <typename T, int ICT> __device__ __forceinline__ void store_w(T* p, con
 }
 
 // MODE 0: wf_sum, MODE 1: wf_dot.  ICT = ic (1, 2 or 4).  c must be a multiple of 64.
-template <typename T, int MODE, int ICT>
+// M48: m = 48 is known at compile time (every AutoFocusFormer merge table)
+template <typename T, int MODE, int ICT, bool M48>
 __global__ void __launch_bounds__(32 * kWarps, 3)
 wf_tiles_kernel(const WfParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -262,7 +263,7 @@ wf_tiles_kernel(const WfParams p) {
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
 
-    const int m = p.m, c = p.c, n = p.n, n_out = p.n_out;
+    const int m = M48 ? kMmax : p.m, c = p.c, n = p.n, n_out = p.n_out;
     const int E = kT * m;
     const T* Fg = static_cast<const T*>(p.F);
 
@@ -443,6 +444,7 @@ wf_tiles_kernel(const WfParams p) {
                     } else if (lane < kT && rowsS[lane] >= 0) {
                         // some row repeats a neighbour: one lane per row adds its weights in column order
                         const T* wrow = Wb + (long long)rowsS[lane] * m * ICT;
+#pragma unroll 1
                         for (int j = 0; j < m; ++j) {
                             const unsigned short lr = lut[lane * m + j];
                             const int rel = (int)(lr & 0xfffu) - u0;
@@ -710,7 +712,7 @@ struct WfScatterSmem {
 static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= kT * kWLD * 4 && kT * kDL <= kT * kWLD, "scratch must fit in Op");
 static_assert(kEE * 2 <= kUW * kCG * 4, "token scratch must fit in the row buffer");
 
-template <typename T, int ICT>
+template <typename T, int ICT, bool M48>
 __global__ void __launch_bounds__(32 * kWarps, 4)
 wf_dfeat_kernel(const WfScatterParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -731,7 +733,8 @@ wf_dfeat_kernel(const WfScatterParams p) {
     ds.bm = reinterpret_cast<unsigned*>(Wd);
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
-    const int m = p.m, c = p.c, n_out = p.n_out, n_tgt = p.n;
+    const int m = M48 ? kMmax : p.m, c = p.c, n_out = p.n_out, n_tgt = p.n;
+    auto div_m = [&](unsigned x) { return M48 ? x / 48u : fast_div_u(x, p.m_magic, p.m_shift); };
     const T* Wg = static_cast<const T*>(p.W);
     const T* Gg = static_cast<const T*>(p.G);
     T* Og = static_cast<T*>(p.out);
@@ -805,7 +808,7 @@ wf_dfeat_kernel(const WfScatterParams p) {
                         o0 = off[j];
                     }
                 const unsigned e = (unsigned)__ldg(entries + s0 + (pe - o0));
-                const int row = (int)fast_div_u(e & ~kDupFlag, p.m_magic, p.m_shift);
+                const int row = (int)div_m(e & ~kDupFlag);
                 ent[x] = e;
                 ds.tok[x] = (unsigned short)row;
                 lut[x] = (unsigned short)(r << 12);
@@ -895,11 +898,12 @@ wf_dfeat_kernel(const WfScatterParams p) {
                                 }
                             } else {
                                 // the merge row names the target several times: add its slots in order
-                                const unsigned row = fast_div_u(e & ~kDupFlag, p.m_magic, p.m_shift);
+                                const unsigned row = div_m(e & ~kDupFlag);
                                 const int64_t* irow = idx_b + (long long)row * m;
                                 float w[ICT];
 #pragma unroll
                                 for (int k = 0; k < ICT; ++k) w[k] = 0.f;
+#pragma unroll 1
                                 for (int j = 0; j < m; ++j)
                                     if (irow[j] == t0 + (int)(lr >> 12)) {
 #pragma unroll
@@ -976,7 +980,7 @@ wf_dfeat_kernel(const WfScatterParams p) {
 template <typename T, int ICT>
 int wf_dfeat_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfScatterSmem::kTotal;
-    auto kernel = wf_dfeat_kernel<T, ICT>;
+    auto kernel = p.m == kMmax ? wf_dfeat_kernel<T, ICT, true> : wf_dfeat_kernel<T, ICT, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
@@ -1008,7 +1012,7 @@ int wf_dfeat_ic(const char* label, int ic, const WfScatterParams& p, cudaStream_
 template <typename T, int MODE, int ICT>
 int wf_tiles_t(const char* label, const WfParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfSmem<MODE>::kTotal;
-    auto kernel = wf_tiles_kernel<T, MODE, ICT>;
+    auto kernel = p.m == kMmax ? wf_tiles_kernel<T, MODE, ICT, true> : wf_tiles_kernel<T, MODE, ICT, false>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
