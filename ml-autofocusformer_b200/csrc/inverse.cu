@@ -206,10 +206,12 @@ inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt,
 // block-wide barriers.  Needs 9 words of shared memory per target.  m <= 32 P.
 constexpr int kR = 4;                    // rows per warp and group
 constexpr int kGroupRows = kWarps * kR;  // 128
-template <int P>
+// M48: m = 48 known at compile time (P = 2)
+template <int P, bool M48>
 __global__ void __launch_bounds__(kThreads)
-inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int* __restrict__ header,
+inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, int nt, int* __restrict__ header,
                         int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries) {
+    const int m = M48 ? 48 : m_arg;
     extern __shared__ __align__(16) int sm128[];
     unsigned* mask = reinterpret_cast<unsigned*>(sm128);             // [nt][4] rows of the current group that hit t
     unsigned* dupm = reinterpret_cast<unsigned*>(sm128 + 4 * nt);    // [nt][4] rows that hit t more than once
@@ -368,7 +370,8 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
     }
     if (m <= 64 && size_t(9) * nt * sizeof(int) <= 200 * 1024) {
         const size_t smem128 = size_t(9) * nt * sizeof(int);
-        auto kernel128 = m <= 32 ? inverse_build128_kernel<1> : inverse_build128_kernel<2>;
+        auto kernel128 = m == 48 ? inverse_build128_kernel<2, true>
+                                 : (m <= 32 ? inverse_build128_kernel<1, false> : inverse_build128_kernel<2, false>);
         if (cudaFuncSetAttribute(kernel128, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128) != cudaSuccess) {
             cudaGetLastError();
             return CLUSTEN_ERR_CUDA;

@@ -240,8 +240,8 @@ template <typename T, int ICT> __device__ __forceinline__ void store_w(T* p, con
 }
 
 // MODE 0: wf_sum, MODE 1: wf_dot.  ICT = ic (1, 2 or 4).  c must be a multiple of 64.
-// M48: m = 48 is known at compile time (every AutoFocusFormer merge table)
-template <typename T, int MODE, int ICT, bool M48>
+// M48: m = 48 is known at compile time (every AutoFocusFormer merge table); C64: c = 64 (the first merge)
+template <typename T, int MODE, int ICT, bool M48, bool C64>
 __global__ void __launch_bounds__(32 * kWarps, 3)
 wf_tiles_kernel(const WfParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -263,7 +263,7 @@ wf_tiles_kernel(const WfParams p) {
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
 
-    const int m = M48 ? kMmax : p.m, c = p.c, n = p.n, n_out = p.n_out;
+    const int m = M48 ? kMmax : p.m, c = C64 ? kCG : p.c, n = p.n, n_out = p.n_out;
     const int E = kT * m;
     const T* Fg = static_cast<const T*>(p.F);
 
@@ -712,7 +712,7 @@ struct WfScatterSmem {
 static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= kT * kWLD * 4 && kT * kDL <= kT * kWLD, "scratch must fit in Op");
 static_assert(kEE * 2 <= kUW * kCG * 4, "token scratch must fit in the row buffer");
 
-template <typename T, int ICT, bool M48>
+template <typename T, int ICT, bool M48, bool C64>
 __global__ void __launch_bounds__(32 * kWarps, 4)
 wf_dfeat_kernel(const WfScatterParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -733,7 +733,7 @@ wf_dfeat_kernel(const WfScatterParams p) {
     ds.bm = reinterpret_cast<unsigned*>(Wd);
     ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
     ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
-    const int m = M48 ? kMmax : p.m, c = p.c, n_out = p.n_out, n_tgt = p.n;
+    const int m = M48 ? kMmax : p.m, c = C64 ? kCG : p.c, n_out = p.n_out, n_tgt = p.n;
     auto div_m = [&](unsigned x) { return M48 ? x / 48u : fast_div_u(x, p.m_magic, p.m_shift); };
     const T* Wg = static_cast<const T*>(p.W);
     const T* Gg = static_cast<const T*>(p.G);
@@ -980,7 +980,8 @@ wf_dfeat_kernel(const WfScatterParams p) {
 template <typename T, int ICT>
 int wf_dfeat_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfScatterSmem::kTotal;
-    auto kernel = p.m == kMmax ? wf_dfeat_kernel<T, ICT, true> : wf_dfeat_kernel<T, ICT, false>;
+    auto kernel = p.m != kMmax ? wf_dfeat_kernel<T, ICT, false, false>
+                               : (p.c == kCG ? wf_dfeat_kernel<T, ICT, true, true> : wf_dfeat_kernel<T, ICT, true, false>);
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
@@ -1012,7 +1013,8 @@ int wf_dfeat_ic(const char* label, int ic, const WfScatterParams& p, cudaStream_
 template <typename T, int MODE, int ICT>
 int wf_tiles_t(const char* label, const WfParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfSmem<MODE>::kTotal;
-    auto kernel = p.m == kMmax ? wf_tiles_kernel<T, MODE, ICT, true> : wf_tiles_kernel<T, MODE, ICT, false>;
+    auto kernel = p.m != kMmax ? wf_tiles_kernel<T, MODE, ICT, false, false>
+                               : (p.c == kCG ? wf_tiles_kernel<T, MODE, ICT, true, true> : wf_tiles_kernel<T, MODE, ICT, true, false>);
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
