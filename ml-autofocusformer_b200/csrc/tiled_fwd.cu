@@ -451,6 +451,7 @@ scatter_tiles_kernel(const ScatterParams p) {
     const SumAddr sa = make_sum_addr(Wd, Xs, lane);
     const int sw = (ci ^ (qi << 1)) << 2;                       // chunk swizzle of staged row qi + 4k
     const int m = ATT48 ? 48 : p.m, ic = ATT48 ? 1 : p.ic, n_tgt = p.n_tgt;
+    const int x_row = ATT48 ? kC : p.x_row, o_row = ATT48 ? kC : p.o_row;      // attention rows are 32 channels
     auto div_m = [&](unsigned x) { return ATT48 ? x / 48u : fast_div(x, p.m_magic, p.m_shift); };
     auto div_ic = [&](unsigned x) { return ATT48 ? x : fast_div(x, p.ic_magic, p.ic_shift); };
     const T* Wg = static_cast<const T*>(p.W);
@@ -533,7 +534,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                             const int r = qi + 4 * k;
                             if (r < rows8) {
                                 float* dst = Xs + r * kC + sw;
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * p.x_row + ci * 4);
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * x_row + ci * 4);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
@@ -544,7 +545,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                             const int r = pr + 8 * k;
                             if (r < rows16) {
                                 T* dst = Xraw + swz16(r, pc);
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * p.x_row + pc * kPer);
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * x_row + pc * kPer);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
@@ -586,7 +587,7 @@ scatter_tiles_kernel(const ScatterParams p) {
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
                         const int q = 2 * qi + a;
-                        T* dstp = Oh + (long long)(t0 + q) * p.o_row + ci * 4;
+                        T* dstp = Oh + (long long)(t0 + q) * o_row + ci * 4;
                         float4 v = *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4);
                         if (r0 > 0) {
                             const float4 old = ld4(dstp);
@@ -721,7 +722,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                             const int r = qi + 4 * k;
                             if (r < rows8) {
                                 float* dst = Xs + r * kC + sw;
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * p.x_row + ci * 4);
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * x_row + ci * 4);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
@@ -732,7 +733,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                             const int r = pr + 8 * k;
                             if (r < rows16) {
                                 T* dst = Xraw + swz16(r, pc);
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * p.x_row + pc * kPer);
+                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[u0 + r] * x_row + pc * kPer);
                                 else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                             }
                         }
@@ -792,7 +793,7 @@ scatter_tiles_kernel(const ScatterParams p) {
                 for (int a = 0; a < 2; ++a) {
                     const int q = 2 * qi + a;
                     if (t0 + q < n_tgt) {
-                        T* dstp = Oh + (long long)(t0 + q) * p.o_row + ci * 4;
+                        T* dstp = Oh + (long long)(t0 + q) * o_row + ci * 4;
                         float4 v = *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4);
                         if (e0 > 0) {
                             const float4 old = ld4(dstp);
