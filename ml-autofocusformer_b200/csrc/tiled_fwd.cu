@@ -616,6 +616,9 @@ scatter_tiles_kernel(const ScatterParams p) {
             off[r] = __shfl_sync(kFull, incl - flen, r);
             st[r] = __shfl_sync(kFull, start, r);
         }
+        unsigned pk[kT];                                        // (segment start - offset) << 3 | tile row
+#pragma unroll
+        for (int r = 0; r < kT; ++r) pk[r] = ((unsigned)(st[r] - off[r]) << 3) | (unsigned)r;
         for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kES) {
             const int E = max(0, min(kES, E_total - e0));
             // ---- this chunk's edges: weight index (flagged when the target repeats in its row), source
@@ -626,19 +629,35 @@ scatter_tiles_kernel(const ScatterParams p) {
 #pragma unroll 4
             for (int x = lane; x < E; x += 32) {
                 const int pe = e0 + x;
-                int r = 0;
+                int r;
+                unsigned qe, k;
+                int s0;
+                if (ATT48) {
+                    // ic = 1: entry address = (segment start - offset in the edge list) + pe; that difference
+                    // and the tile row travel through one select chain (the offsets ascend)
+                    unsigned v = pk[0];
 #pragma unroll
-                for (int j = 1; j < kT; ++j) r += (pe >= off[j]) ? 1 : 0;
-                int s0 = st[0], o0 = off[0];
+                    for (int j = 1; j < kT; ++j) v = pe >= off[j] ? pk[j] : v;
+                    r = (int)(v & 7u);
+                    s0 = (int)(v >> 3);
+                    qe = (unsigned)pe;
+                    k = 0u;
+                } else {
+                    r = 0;
 #pragma unroll
-                for (int j = 1; j < kT; ++j)
-                    if (r == j) {
-                        s0 = st[j];
-                        o0 = off[j];
-                    }
-                const unsigned q = (unsigned)(pe - o0);                     // position inside the fanned-out segment
-                const unsigned qe = div_ic(q);     // entry inside the segment
-                const unsigned k = q - qe * (unsigned)ic;
+                    for (int j = 1; j < kT; ++j) r += (pe >= off[j]) ? 1 : 0;
+                    s0 = st[0];
+                    int o0 = off[0];
+#pragma unroll
+                    for (int j = 1; j < kT; ++j)
+                        if (r == j) {
+                            s0 = st[j];
+                            o0 = off[j];
+                        }
+                    const unsigned q = (unsigned)(pe - o0);                 // position inside the fanned-out segment
+                    qe = div_ic(q);                                         // entry inside the segment
+                    k = q - qe * (unsigned)ic;
+                }
                 const unsigned e = (unsigned)__ldg(entries + s0 + (int)qe);
                 const unsigned plain = e & ~kDupFlag;                       // row * m + slot
                 const unsigned src = div_m(plain);

@@ -789,6 +789,9 @@ wf_dfeat_kernel(const WfScatterParams p) {
             off[r] = __shfl_sync(kFull, incl - len, r);
             st[r] = __shfl_sync(kFull, start, r);
         }
+        unsigned pk[kT];                                        // (segment start - offset) << 3 | tile row
+#pragma unroll
+        for (int r = 0; r < kT; ++r) pk[r] = ((unsigned)(st[r] - off[r]) << 3) | (unsigned)r;
         for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kEE) {
             const int E = max(0, min(kEE, E_total - e0));
             int lo = INT_MAX, hi = -1;
@@ -797,17 +800,12 @@ wf_dfeat_kernel(const WfScatterParams p) {
 #pragma unroll 4
             for (int x = lane; x < E; x += 32) {
                 const int pe = e0 + x;
-                int r = 0;
+                // (segment start - offset in the edge list) and the tile row travel through one select chain
+                unsigned v = pk[0];
 #pragma unroll
-                for (int j = 1; j < kT; ++j) r += (pe >= off[j]) ? 1 : 0;
-                int s0 = st[0], o0 = off[0];
-#pragma unroll
-                for (int j = 1; j < kT; ++j)
-                    if (r == j) {
-                        s0 = st[j];
-                        o0 = off[j];
-                    }
-                const unsigned e = (unsigned)__ldg(entries + s0 + (pe - o0));
+                for (int j = 1; j < kT; ++j) v = pe >= off[j] ? pk[j] : v;
+                const int r = (int)(v & 7u);
+                const unsigned e = (unsigned)__ldg(entries + (int)(v >> 3) + pe);
                 const int row = (int)div_m(e & ~kDupFlag);
                 ent[x] = e;
                 ds.tok[x] = (unsigned short)row;
