@@ -53,11 +53,11 @@ CFG = dict(b=128, h=2, n=3136, m=48, c=32, n_out=784, cw=64, ic=4)
 CPU_SAMPLE_BATCH = 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture at b=32, scaled x4 to the
 # benchmark's b=128 (traffic grows with the batch); see profiles/
-NCU_DRAM_BYTES_PER_LAUNCH = {("av_d_value", "fp32"): 4 * (84363264 + 11164416),
-                             ("av_forward", "fp32"): 4 * (103102976 + 11558912),
-                             ("wf_forward", "fp32"): 4 * (54766592 + 2501632),
-                             ("wf_d_weights", "fp32"): 4 * (61192704 + 2499328),
-                             ("wf_d_feat", "fp32"): 4 * (50630656 + 3367936)}
+NCU_DRAM_BYTES_PER_LAUNCH = {("av_d_value", "fp32"): 4 * (84358656 + 10250240),
+                             ("av_forward", "fp32"): 4 * (103323904 + 10757888),
+                             ("wf_forward", "fp32"): 4 * (54756864 + 2429440),
+                             ("wf_d_weights", "fp32"): 4 * (61346816 + 2926080),
+                             ("wf_d_feat", "fp32"): 4 * (50620928 + 4114688)}
 
 
 def _peaks():
