@@ -217,6 +217,14 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         for (int k = 0; k < 2; ++k)
                             if (lane + 32 * k < kT * (m >> 3))
                                 cp_async16_ca(Wd16 + wq16[k] * kWLD16 + wc16[k] * 8, Wt + wq16[k] * m + wc16[k] * 8);
+                        if (m & 15) {
+                            // the product runs over a multiple of 16 columns: the 8 columns behind the tile are zero
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const int z = lane + 32 * k;
+                                Wd16[(z >> 3) * kWLD16 + m + (z & 7)] = Elem<T>::down(0.f);
+                            }
+                        }
                     } else if (native16) {
                         for (int z = lane; z < kT * kWLD16 * 2 / 16; z += 32)
                             reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -30,12 +30,16 @@ def _attention_case(regime, b, h, n, m, c, dtype, seed):
 
 
 # (b, h, n, m, c): cluster-structured stages, the reference tests' shape, a padded stage (n % 8 != 0),
-# m = n = 49 (every token is a neighbour), m = 144, head dims other than 32, n < m
+# m = n = 49 (every token is a neighbour), head_dim 32 with m below 48 (the kernels' runtime-sized variants),
+# m = 144, head dims other than 32, n < m
 ATT_SHAPES = [
     (2, 2, 392, 48, 32),
     (3, 4, 196, 48, 32),
     (2, 3, 73, 48, 32),
     (2, 2, 49, 49, 32),
+    (2, 2, 100, 24, 32),
+    (1, 3, 64, 40, 32),
+    (2, 2, 57, 13, 32),
     (1, 2, 160, 144, 32),
     (2, 2, 64, 16, 16),
     (1, 1, 40, 9, 24),
@@ -83,6 +87,8 @@ WF_SHAPES = [
     (2, 36, 184, 48, 4, 128),
     (1, 14, 73, 48, 4, 256),
     (2, 51, 392, 48, 2, 64),
+    (2, 40, 160, 24, 4, 64),
+    (1, 33, 90, 13, 2, 128),
     (1, 20, 100, 16, 3, 24),
     (1, 7, 30, 5, 2, 9),
 ]
