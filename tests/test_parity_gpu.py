@@ -158,9 +158,11 @@ def test_inverse_index_is_exact(ops, regime, shape):
             assert (idx[bi][rows[~flagged], slots] == t).all()
 
 
-def test_out_of_range_indices_are_ignored(ops):
-    b, h, n, m, c = 1, 2, 64, 16, 32
-    idx, q, k, v, attn, g_attn, g_feat = _attention_case("random", b, h, n, m, c, torch.float32, 31)
+@pytest.mark.parametrize("shape", [(1, 2, 64, 16, 32), (2, 2, 104, 48, 32)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("regime", ["random", "model"])
+def test_out_of_range_indices_are_ignored(ops, regime, shape):
+    b, h, n, m, c = shape
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case(regime, b, h, n, m, c, torch.float32, 31)
     bad = idx.clone()
     bad[0, ::3, 5] = n + 7
     bad[0, 1::3, 2] = -1
