@@ -465,6 +465,44 @@ __device__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigne
     if (n_src < 0) n_src = n;
     const DedupScratch* ps = &ps_;
     int lo = INT_MAX, hi = -1;
+    // Tiles whose rows are made of aligned runs of 8 consecutive tokens (neighbourhoods built from whole
+    // clusters, as the model does): the runs are de-duplicated instead of the tokens, one eighth of the work.
+    bool maybe_runs = (m & 7) == 0 && i0 + kT <= n;
+    if (maybe_runs) {                                   // cheap look at the first 32 indices before the full check
+        const long long v = ring[lane], v0 = ring[lane & ~7];
+        maybe_runs = __all_sync(kFull, (v0 & 7) == 0 && v == v0 + (lane & 7));
+    }
+    if (maybe_runs) {
+        bool runs = true;
+        for (int x = lane; x < E; x += 32) {            // (x & 7) == (lane & 7)
+            const long long v = ring[x], v0 = ring[x & ~7];
+            runs = runs && v0 >= 0 && (v0 & 7) == 0 && v == v0 + (x & 7) && v0 + 7 < n_src;
+        }
+        if (__all_sync(kFull, runs)) {
+            const int R = E >> 3;                       // run edges, m / 8 per row
+            unsigned short* slot_r = ps->tok + 64;      // R <= 48
+            for (int y = lane; y < R; y += 32) {
+                const int rid = (int)(ring[8 * y] >> 3);
+                ps->tok[y] = (unsigned short)rid;
+                lo = min(lo, rid);
+                hi = max(hi, rid);
+            }
+            const int UR = dedup_tokens(ps_, slot_r, R, m >> 3, want_rowdup, rowdup, lane, lo, hi);
+            int rid[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) rid[k] = lane + 32 * k < UR ? (int)ps->uniq[lane + 32 * k] : 0;
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                if (lane + 32 * k < UR) {
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) ps->uniq[(lane + 32 * k) * 8 + r] = (unsigned short)(rid[k] * 8 + r);
+                }
+            for (int x = lane; x < E; x += 32) lut[x] = (unsigned short)(slot_r[x >> 3] * 8 + (x & 7));
+            __syncwarp();
+            return UR * 8;
+        }
+    }
     for (int x = lane; x < E; x += 32) {
         const long long v = ring[x];
         const int q = x / m;
