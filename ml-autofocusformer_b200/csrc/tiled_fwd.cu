@@ -416,6 +416,7 @@ __device__ __forceinline__ unsigned fast_div(unsigned x, unsigned magic, unsigne
 }
 
 constexpr int kES = 512;            // edges handled at a time (8 targets x ~48 on average)
+constexpr unsigned kNoEdge = 0xffffffffu;
 
 template <typename T> struct ScatterSmem {
     static constexpr bool kIsFloat = std::is_same<T, float>::value;
@@ -499,6 +500,110 @@ scatter_tiles_kernel(const ScatterParams p) {
         maxlen = __shfl_sync(kFull, maxlen, 0);
         T* Ob = Og + (long long)b * p.o_batch;
 
+        // ---- dense tile back end: the source rows of a pass are in uniq[0 .. Uc), the weight element of
+        //      (source row rr, target q) in edge[rr * 8 + q] (kNoEdge: the row does not name the target).
+        //      Lane l fills the weights of target l % 8, so the 8 weights of a source row -- neighbours in
+        //      memory when the targets are neighbours in the row's list -- are read by neighbouring lanes.
+        auto dense_heads = [&](int Uc, bool first) {
+            const int rows8 = (Uc + 7) & ~7;
+            const int rows16 = (Uc + 15) & ~15;
+            for (int g = 0; g < p.heads; ++g) {
+                const T* Wh = Wg + (long long)b * p.w_batch + (long long)g * p.w_head;
+                const T* Xh = Xg + (long long)b * p.x_batch + (long long)g * p.x_head;
+                if (kIsFloat) {
+#pragma unroll
+                    for (int k = 0; k < kUC / 4; ++k) {
+                        const int r = qi + 4 * k;
+                        if (r < rows8) {
+                            float* dst = Xs + r * kC + sw;
+                            if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * x_row + ci * 4);
+                            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+                } else {
+                    const int pr = lane >> 2, pc = lane & 3;
+#pragma unroll
+                    for (int k = 0; k < kUC / 8; ++k) {
+                        const int r = pr + 8 * k;
+                        if (r < rows16) {
+                            T* dst = Xraw + swz16(r, pc);
+                            if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * x_row + pc * kPer);
+                            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+                }
+                cp_async_commit();
+                if (g == 0 || p.w_head != 0) {
+#pragma unroll 4
+                    for (int rr = psub; rr < (kIsFloat ? rows8 : rows16); rr += 4) {
+                        const unsigned e = rr < Uc ? edge[rr * kT + myq] : kNoEdge;
+                        if (kIsFloat) {
+                            // asynchronous 4-byte copies, in flight together with the rows staged above
+                            float* dst = Wd + myq * kWLD + rr;
+                            if (e != kNoEdge) cp_async4_ca(dst, Wh + e);
+                            else *dst = 0.f;
+                        } else if (p.w_pairs) {
+                            // 16-bit weights: the aligned 32-bit word around the element travels; the half is
+                            // picked after the wait below
+                            if (e != kNoEdge)
+                                cp_async4_ca(wbuf + rr * kT + myq,
+                                             reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(Wh + e) & ~uintptr_t(3)));
+                        } else {
+                            Wd16[myq * kWLD16 + rr] = e != kNoEdge ? Wh[e] : Elem<T>::down(0.f);
+                        }
+                    }
+                    cp_async_commit();
+                }
+                cp_async_wait<0>();
+                __syncwarp();
+                if (!kIsFloat && p.w_pairs && (g == 0 || p.w_head != 0)) {
+#pragma unroll 4
+                    for (int rr = psub; rr < rows16; rr += 4) {
+                        const unsigned e = rr < Uc ? edge[rr * kT + myq] : kNoEdge;
+                        unsigned short hbits = 0;
+                        if (e != kNoEdge) {
+                            const unsigned raw = reinterpret_cast<const unsigned*>(wbuf)[rr * kT + myq];
+                            hbits = (unsigned short)((reinterpret_cast<uintptr_t>(Wh + e) & 2) ? raw >> 16 : raw & 0xffffu);
+                        }
+                        reinterpret_cast<unsigned short*>(Wd16)[myq * kWLD16 + rr] = hbits;
+                    }
+                    __syncwarp();
+                }
+                float acc[2][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
+                if (kIsFloat) sum_product_mma<true>(sa, rows8, acc);
+                else sum_product16<T>(Xraw, Wd16, rows16 >> 4, lane, acc);
+                float* Ot = Xs;                                          // the dense weights may serve the next slab
+                const int gg = lane >> 2, tt = lane & 3;
+                __syncwarp();
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    float* o = Ot + (2 * tt) * kOLD + 16 * mt + gg;
+                    o[0] = acc[mt][0];
+                    o[kOLD] = acc[mt][1];
+                    o[8] = acc[mt][2];
+                    o[kOLD + 8] = acc[mt][3];
+                }
+                __syncwarp();
+                T* Oh = Ob + (long long)g * p.o_head;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    const int q = 2 * qi + a;
+                    if (t0 + q < n_tgt) {
+                        T* dstp = Oh + (long long)(t0 + q) * o_row + ci * 4;
+                        float4 v = *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4);
+                        if (!first) {
+                            const float4 old = ld4(dstp);
+                            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                        }
+                        st4(dstp, v);
+                    }
+                }
+                __syncwarp();
+            }
+        };
+
         // ---- uniform tile: the 8 targets are listed by the same source rows, once each (the 8 tokens of
         //      a cluster always are when neighbourhoods are made of whole clusters).  The dense weights
         //      are then read straight through the entries; nothing to de-duplicate.
@@ -519,97 +624,23 @@ scatter_tiles_kernel(const ScatterParams p) {
             const int per = kUC / ic;                                        // entries per pass
             for (int r0 = 0; r0 < maxlen; r0 += per) {
                 const int Lc = min(per, maxlen - r0);
-                const int Uc = Lc * ic;                                      // source rows of this pass
-                const int rows8 = (Uc + 7) & ~7;
-                const int rows16 = (Uc + 15) & ~15;
                 __syncwarp();
-                // weight index of every (entry, target) and the source rows
+                // weight element of every (source row, target) and the source rows
                 for (int r = psub; r < Lc; r += 4) {
                     const unsigned plain = (unsigned)__ldg(qent + r0 + r);
-                    edge[r * kT + myq] = plain * (unsigned)ic;
+                    for (int k = 0; k < ic; ++k) edge[(r * ic + k) * kT + myq] = plain * (unsigned)ic + (unsigned)k;
                     if (myq == 0) {
                         const unsigned src = div_m(plain) * (unsigned)ic;
                         for (int k = 0; k < ic; ++k) uniq[r * ic + k] = (unsigned short)(src + k);
                     }
                 }
                 __syncwarp();
-                for (int g = 0; g < p.heads; ++g) {
-                    const T* Wh = Wg + (long long)b * p.w_batch + (long long)g * p.w_head;
-                    const T* Xh = Xg + (long long)b * p.x_batch + (long long)g * p.x_head;
-                    if (kIsFloat) {
-#pragma unroll
-                        for (int k = 0; k < kUC / 4; ++k) {
-                            const int r = qi + 4 * k;
-                            if (r < rows8) {
-                                float* dst = Xs + r * kC + sw;
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * x_row + ci * 4);
-                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                        }
-                    } else {
-                        const int pr = lane >> 2, pc = lane & 3;
-#pragma unroll
-                        for (int k = 0; k < kUC / 8; ++k) {
-                            const int r = pr + 8 * k;
-                            if (r < rows16) {
-                                T* dst = Xraw + swz16(r, pc);
-                                if (r < Uc) cp_async16_cg(dst, Xh + (long long)uniq[r] * x_row + pc * kPer);
-                                else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                            }
-                        }
-                    }
-                    cp_async_commit();
-                    if (g == 0 || p.w_head != 0) {
-                        // dense weights [8][rows8]: lanes of one source row read neighbouring weights
-#pragma unroll 4
-                        for (int rr = psub; rr < (kIsFloat ? rows8 : rows16); rr += 4) {
-                            T w = Elem<T>::down(0.f);
-                            if (rr < Uc) {
-                                const unsigned r = div_ic((unsigned)rr);
-                                w = Wh[edge[r * kT + myq] + ((unsigned)rr - r * (unsigned)ic)];
-                            }
-                            if (kIsFloat) Wd[myq * kWLD + rr] = Elem<T>::up(w);
-                            else Wd16[myq * kWLD16 + rr] = w;
-                        }
-                    }
-                    cp_async_wait<0>();
-                    __syncwarp();
-                    float acc[2][4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
-                    if (kIsFloat) sum_product_mma<true>(sa, rows8, acc);
-                    else sum_product16<T>(Xraw, Wd16, rows16 >> 4, lane, acc);
-                    float* Ot = Xs;                                          // the dense weights may serve the next slab
-                    const int gg = lane >> 2, tt = lane & 3;
-                    __syncwarp();
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        float* o = Ot + (2 * tt) * kOLD + 16 * mt + gg;
-                        o[0] = acc[mt][0];
-                        o[kOLD] = acc[mt][1];
-                        o[8] = acc[mt][2];
-                        o[kOLD + 8] = acc[mt][3];
-                    }
-                    __syncwarp();
-                    T* Oh = Ob + (long long)g * p.o_head;
-#pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const int q = 2 * qi + a;
-                        T* dstp = Oh + (long long)(t0 + q) * o_row + ci * 4;
-                        float4 v = *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4);
-                        if (r0 > 0) {
-                            const float4 old = ld4(dstp);
-                            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-                        }
-                        st4(dstp, v);
-                    }
-                    __syncwarp();
-                }
+                dense_heads(Lc * ic, r0 == 0);
             }
             continue;
         }
 
-        // ---- general tile: the fanned-out segments of the 8 targets, concatenated, kES edges at a time
+        // ---- the fanned-out segments of the 8 targets, concatenated
         const int flen = len * ic;                              // lanes 0..7: edges of target `lane`
         int incl = flen;
 #pragma unroll
@@ -627,6 +658,8 @@ scatter_tiles_kernel(const ScatterParams p) {
         unsigned pk[kT];                                        // (segment start - offset) << 3 | tile row
 #pragma unroll
         for (int r = 0; r < kT; ++r) pk[r] = ((unsigned)(st[r] - off[r]) << 3) | (unsigned)r;
+
+        // ---- general tile, kES edges at a time
         for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kES) {
             const int E = max(0, min(kES, E_total - e0));
             // ---- this chunk's edges: weight index (flagged when the target repeats in its row), source
