@@ -300,17 +300,62 @@ inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, 
         const int row0 = g0 + warp * kR;
         load_rows(row0 + kGroupRows, nxt);
         unsigned win = 0u, last = 0u;                     // bit r * P + p
+        // The warp's four rows are often one and the same neighbour list (the tokens of a cluster share
+        // theirs): they are then marked with one atomic per slot and placed at four consecutive positions.
+        bool same4 = row0 + kR <= n_rows;
 #pragma unroll
-        for (int r = 0; r < kR; ++r)
+        for (int p = 0; p < P; ++p)
+            same4 = same4 && cur[0][p] == cur[1][p] && cur[0][p] == cur[2][p] && cur[0][p] == cur[3][p];
+        same4 = __all_sync(0xffffffffu, same4);
+        if (same4) {
+            const unsigned bits = 0xfu << bit0, first = 1u << bit0;
 #pragma unroll
             for (int p = 0; p < P; ++p)
-                if (cur[r][p] >= 0) {
-                    const unsigned bit = 1u << (bit0 + r);
-                    const unsigned old = atomicOr(&mask[cur[r][p] * 4 + word], bit);
-                    if (old & bit) atomicOr(&dupm[cur[r][p] * 4 + word], bit);
-                    else win |= 1u << (r * P + p);
+                if (cur[0][p] >= 0) {
+                    const unsigned old = atomicOr(&mask[cur[0][p] * 4 + word], bits);
+                    if (old & first) atomicOr(&dupm[cur[0][p] * 4 + word], bits);
+                    else win |= 1u << p;
                 }
+        } else {
+#pragma unroll
+            for (int r = 0; r < kR; ++r)
+#pragma unroll
+                for (int p = 0; p < P; ++p)
+                    if (cur[r][p] >= 0) {
+                        const unsigned bit = 1u << (bit0 + r);
+                        const unsigned old = atomicOr(&mask[cur[r][p] * 4 + word], bit);
+                        if (old & bit) atomicOr(&dupm[cur[r][p] * 4 + word], bit);
+                        else win |= 1u << (r * P + p);
+                    }
+        }
         __syncthreads();
+        if (same4) {
+#pragma unroll
+            for (int p = 0; p < P; ++p)
+                if ((win >> p) & 1u) {
+                    const int tk = cur[0][p];
+                    const uint4 mk = *reinterpret_cast<const uint4*>(&mask[tk * 4]);
+                    const unsigned mw[4] = {mk.x, mk.y, mk.z, mk.w};
+                    const unsigned first = 1u << bit0;
+                    int pos = base[tk];
+                    bool later = false;                   // does a later row of the group hit tk too?
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        if (w < word) pos += __popc(mw[w]);
+                        else if (w == word) {
+                            pos += __popc(mw[w] & (first - 1u));
+                            later = later || (bit0 + kR < 32 && (mw[w] >> (bit0 + kR)) != 0u);
+                        } else {
+                            later = later || mw[w] != 0u;
+                        }
+                    }
+                    const bool dup = (dupm[tk * 4 + word] & first) != 0u;
+#pragma unroll
+                    for (int r = 0; r < kR; ++r)
+                        ent[pos + r] = dup ? (int)(kDupFlag | (unsigned)((row0 + r) * m)) : ((row0 + r) * m + lane + 32 * p);
+                    if (!later) last |= 1u << p;
+                }
+        } else {
 #pragma unroll
         for (int r = 0; r < kR; ++r)
 #pragma unroll
@@ -337,6 +382,7 @@ inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, 
                     ent[pos] = dup ? (int)(kDupFlag | (unsigned)(row * m)) : (row * m + lane + 32 * p);
                     if (!later) last |= 1u << (r * P + p);
                 }
+        }
         __syncthreads();
 #pragma unroll
         for (int r = 0; r < kR; ++r)
