@@ -236,10 +236,25 @@ inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, 
     }
     __syncthreads();
     int oob = 0;
-    for (long long e = tid; e < E; e += kThreads) {
-        const long long tk = ib[e];
-        if (tk >= 0 && tk < nt) atomicAdd(&base[(int)tk], 1);
-        else ++oob;
+    {
+        // eight indices per thread in flight at a time
+        constexpr int kBatch = 8;
+        for (long long e0 = tid; e0 < E; e0 += (long long)kBatch * kThreads) {
+            long long tk[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const long long e = e0 + (long long)u * kThreads;
+                tk[u] = e < E ? ib[e] : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const long long e = e0 + (long long)u * kThreads;
+                if (e < E) {
+                    if (tk[u] >= 0 && tk[u] < nt) atomicAdd(&base[(int)tk[u]], 1);
+                    else ++oob;
+                }
+            }
+        }
     }
     if (oob) atomicAdd(&header[5], oob);
     __syncthreads();
