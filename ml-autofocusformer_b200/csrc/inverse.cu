@@ -306,7 +306,9 @@ inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, 
             for (int p = 0; p < P; ++p) {
                 const int j = lane + 32 * p;
                 long long tk = -1;
-                if (row0 + r < n_rows && j < m) tk = ib[(long long)(row0 + r) * m + j];
+                // volatile: the loads of the next group are issued here, ahead of this group's barriers
+                if (row0 + r < n_rows && j < m)
+                    asm volatile("ld.global.nc.s64 %0, [%1];\n" : "=l"(tk) : "l"(ib + (long long)(row0 + r) * m + j));
                 dst[r][p] = (tk >= 0 && tk < nt) ? (int)tk : -1;
             }
     };
