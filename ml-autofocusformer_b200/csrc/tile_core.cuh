@@ -460,7 +460,7 @@ struct DedupScratch {
 __device__ int dedup_tokens(const DedupScratch ps_, unsigned short* lut, int E, int m, bool want_rowdup,
                             bool* rowdup, int lane, int lo, int hi);
 
-__device__ __noinline__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigned short* lut, int E, int m, int i0,
+__device__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigned short* lut, int E, int m, int i0,
                           int n, bool want_rowdup, bool* rowdup, int lane, int n_src = -1) {
     if (n_src < 0) n_src = n;
     const DedupScratch* ps = &ps_;
