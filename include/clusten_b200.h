@@ -71,13 +71,6 @@ CLUSTEN_API int clusten_version(void);
 /* Number of kernels this library has launched in this process (all threads). */
 CLUSTEN_API unsigned long long clusten_launch_count(void);
 
-/* Device status word.  The pipelined kernels bound every wait on a shared-memory
- * barrier; a wait that runs out sets bit 0 and the kernel returns early (its
- * output is then incomplete).  This call synchronises with the device, stores
- * the word in *status (0 = healthy) and clears it when clear != 0.
- * No counterpart in the reference. */
-CLUSTEN_API int clusten_device_status(int* status, int clear);
-
 /* Per-kernel timing for benchmarks.  While enabled, every kernel launch of the
  * library is bracketed by two CUDA events recorded on the launch stream.
  * clusten_timing_collect synchronises those events, writes one line per kernel
@@ -101,8 +94,10 @@ CLUSTEN_API int clusten_timing_collect(char* buf, size_t buf_bytes);
  *
  *   n_rows    rows of nbhd_idx per batch element (n for QK/AV, n_ for WF)
  *   n_targets number of tokens the indices point into (n)
- * Limits: m <= 2048, n_targets <= 18000 (per-batch counters live in shared
- * memory), n_rows * m < 2^31; otherwise CLUSTEN_ERR_UNSUPPORTED.
+ * Limits: m <= 2048, n_targets <= 2^20, n_rows * m < 2^31; otherwise
+ * CLUSTEN_ERR_UNSUPPORTED.  Up to 18000 targets the build keeps its per-target
+ * counters in shared memory; beyond that they live in the buffer itself (which
+ * clusten_inverse_bytes sizes accordingly) and the build is slower.
  * ---------------------------------------------------------------------- */
 CLUSTEN_API size_t clusten_inverse_bytes(int b, int n_rows, int m, int n_targets);
 

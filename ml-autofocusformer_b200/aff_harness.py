@@ -1,0 +1,213 @@
+"""Model-level harness: the reference's AutoFocusFormer, unmodified, calling this package's operators.
+
+The CLUSTEN operators are called from three lines of models/aff_transformer.py of
+apple/ml-autofocusformer (:120 QK, :154 AV, :361 WF).  This module imports that file as it
+is (sourceless bytecode that oracle/build_ref.py compiles from the checkout into
+oracle/_ref/aff_model/; nothing of the model is re-implemented here) and supplies the three
+things the file needs that are not in this environment:
+
+  * `timm.models.layers.DropPath` / `trunc_normal_` (models/aff_transformer.py:9): written
+    here from their documented behaviour -- DropPath is the identity in eval mode and, in
+    training, zeroes whole samples with probability p and rescales the rest by 1 / (1 - p);
+    trunc_normal_ is torch.nn.init.trunc_normal_.
+  * `knn_keops` (models/point_utils.py:27-58; pykeops is not installed): the k nearest
+    database points of every query by exact Euclidean distance, ascending, computed with
+    torch.cdist + topk.  Tie-breaking of the original is not pinned by any reference test.
+  * the `clusten` package: this repository's operators ("b200"), the PyTorch gather
+    formulation of the reference's kernel tests ("formula", the parity checker), or the
+    reference's own wrappers on its own CUDA kernels ("reference", the speed bar).
+
+The same stand-ins serve every implementation, so a comparison between two of them is a
+comparison of the operators on identical neighbourhood tables.
+
+Configurations (BASELINE configs 3 and 4):
+  tiny224  embed 64/128/256/512, depths 2/2/6/2, heads 2/4/8/16, mlp_ratio 3 (configs/aff_tiny.yaml:7-8),
+           cluster 8, nbhd 48/48/48/49, ds_rate 1/4, 224 x 224 input, 1000 classes
+  base384  embed 128/256/512/1024, depths 3/4/18/2, heads 4/8/16/32, mlp_ratio 3, layer_scale 1e-5
+           (configs/aff_base_22kto1k_384.yaml:6-12), cluster 8, nbhd 48/48/48/49, ds_rate 1/5, 384 x 384
+"""
+import importlib
+import os
+import sys
+import types
+
+import torch
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_REF = os.path.join(_ROOT, "oracle", "_ref")
+MODEL_DIR = os.path.join(_REF, "aff_model")
+REF_CLUSTEN_DIR = os.path.join(_REF, "ref_clusten")
+
+CONFIGS = {
+    "tiny224": dict(embed_dim=[64, 128, 256, 512], depths=[2, 2, 6, 2], num_heads=[2, 4, 8, 16], mlp_ratio=3.,
+                    cluster_size=8, nbhd_size=[48, 48, 48, 49], ds_rate=0.25, layer_scale=0.0, img_size=224,
+                    num_classes=1000, drop_path_rate=0.0),
+    "base384": dict(embed_dim=[128, 256, 512, 1024], depths=[3, 4, 18, 2], num_heads=[4, 8, 16, 32], mlp_ratio=3.,
+                    cluster_size=8, nbhd_size=[48, 48, 48, 49], ds_rate=0.2, layer_scale=1e-5, img_size=384,
+                    num_classes=1000, drop_path_rate=0.0),
+}
+
+
+def available():
+    """Is the reference's model bytecode there (oracle/build_ref.py has run)?"""
+    return os.path.exists(os.path.join(MODEL_DIR, "models", "aff_transformer.pyc"))
+
+
+# ----------------------------------------------------------------------------- stand-ins
+class DropPath(torch.nn.Module):
+    """Stochastic depth per sample: identity in eval mode or with p = 0."""
+
+    def __init__(self, drop_prob=0.0):
+        super().__init__()
+        self.drop_prob = float(drop_prob)
+
+    def forward(self, x):
+        if self.drop_prob == 0.0 or not self.training:
+            return x
+        keep = 1.0 - self.drop_prob
+        mask = x.new_empty((x.shape[0],) + (1,) * (x.dim() - 1)).bernoulli_(keep)
+        return x * mask / keep
+
+
+def _install_timm_standin():
+    if "timm.models.layers" in sys.modules:
+        return
+    try:
+        importlib.import_module("timm.models.layers")
+        return
+    except ImportError:
+        pass
+    timm = types.ModuleType("timm")
+    models = types.ModuleType("timm.models")
+    layers = types.ModuleType("timm.models.layers")
+    layers.DropPath = DropPath
+    layers.trunc_normal_ = torch.nn.init.trunc_normal_
+    timm.models, models.layers = models, layers
+    sys.modules.update({"timm": timm, "timm.models": models, "timm.models.layers": layers})
+
+
+def knn(query, database, k, return_dist=False, chunk_elems=1 << 28):
+    """Interface of knn_keops (models/point_utils.py:27-58): query [b, n_, d], database [b, n, d]
+    -> indices [b, n_, k] of the k nearest database points by ascending distance (and the distances).
+    Exact fp32 distances (no matrix-multiply shortcut); batches are processed in chunks so that the
+    [chunk, n_, n] distance matrix stays below chunk_elems elements."""
+    with torch.no_grad():
+        q = query.detach().float()
+        d = database.detach().float()
+        b, nq, _ = q.shape
+        n = d.shape[1]
+        step = max(1, min(b, chunk_elems // max(1, nq * n)))
+        idxs, dists = [], []
+        for s in range(0, b, step):
+            dist = torch.cdist(q[s:s + step], d[s:s + step], compute_mode="donot_use_mm_for_euclid_dist")
+            nn_dist, nn_idx = dist.topk(k, dim=2, largest=False, sorted=True)
+            idxs.append(nn_idx)
+            dists.append(nn_dist)
+        nn_idx = torch.cat(idxs, 0)
+        if return_dist:
+            return nn_idx, torch.cat(dists, 0)
+        return nn_idx
+
+
+# ----------------------------------------------------------------------------- clusten implementations
+class _FormulaFunction:
+    """`.apply(a, b, nbhd_idx)` on the PyTorch gather formulation (oracle/formula.py), with the
+    operators' dtype rule: the second tensor is converted to the first one's dtype."""
+
+    def __init__(self, fn, chunk):
+        self.fn, self.chunk = fn, chunk
+
+    def apply(self, a, b, nbhd_idx):
+        b = b.to(a.dtype)
+        step = self.chunk
+        if step is None or step >= a.shape[0]:
+            return self.fn(a, b, nbhd_idx)
+        return torch.cat([self.fn(a[s:s + step], b[s:s + step], nbhd_idx[s:s + step])
+                          for s in range(0, a.shape[0], step)], 0)
+
+
+def _implementation(name, formula_chunk=8):
+    """-> (CLUSTENQKFunction, CLUSTENAVFunction, CLUSTENWFFunction) of the named implementation."""
+    if name == "b200":
+        import clusten
+        return clusten.CLUSTENQKFunction, clusten.CLUSTENAVFunction, clusten.CLUSTENWFFunction
+    if name == "formula":
+        if _ROOT not in sys.path:
+            sys.path.insert(0, _ROOT)
+        from oracle import formula
+        return (_FormulaFunction(formula.qk, formula_chunk), _FormulaFunction(formula.av, formula_chunk),
+                _FormulaFunction(formula.wf, formula_chunk))
+    if name == "reference":
+        # the reference's clusten/clusten.py (bytecode) on its own extension modules in oracle/_ref/
+        if _REF not in sys.path:
+            sys.path.insert(0, _REF)
+        spec = importlib.util.spec_from_file_location(
+            "ref_clusten_pkg", os.path.join(REF_CLUSTEN_DIR, "clusten", "clusten.pyc"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod.CLUSTENQKFunction, mod.CLUSTENAVFunction, mod.CLUSTENWFFunction
+    raise ValueError(name)
+
+
+def reference_kernels_available():
+    if not os.path.exists(os.path.join(REF_CLUSTEN_DIR, "clusten", "clusten.pyc")):
+        return False
+    try:
+        _implementation("reference")
+        return True
+    except Exception:
+        return False
+
+
+_aff = None
+
+
+def model_module():
+    """The reference's models.aff_transformer, imported once with the stand-ins in place."""
+    global _aff
+    if _aff is None:
+        if not available():
+            raise RuntimeError("the reference model's bytecode is missing: run oracle/build_ref.py where the "
+                               "checkout of apple/ml-autofocusformer is present")
+        _install_timm_standin()
+        import clusten  # noqa: F401  this package's operators: what `from clusten import ...` in the model resolves to
+        if MODEL_DIR not in sys.path:
+            sys.path.insert(0, MODEL_DIR)
+        point_utils = importlib.import_module("models.point_utils")
+        point_utils.knn_keops = knn
+        _aff = importlib.import_module("models.aff_transformer")
+        _aff.knn_keops = knn
+    return _aff
+
+
+def use_implementation(name, **kw):
+    """Make the model's three call sites use the named `clusten` implementation."""
+    aff = model_module()
+    aff.CLUSTENQKFunction, aff.CLUSTENAVFunction, aff.CLUSTENWFFunction = _implementation(name, **kw)
+    return aff
+
+
+def build_model(config, device, seed=0):
+    """AutoFocusFormer(**CONFIGS[config]).eval() with seeded random weights on `device`."""
+    aff = model_module()
+    torch.manual_seed(seed)
+    model = aff.AutoFocusFormer(**CONFIGS[config])
+    return model.to(device).eval()
+
+
+def synthetic_images(config, batch, device, seed=1):
+    """N(0,1) images of the configuration's ImageNet shape (the dataset itself is not available)."""
+    size = CONFIGS[config]["img_size"]
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return torch.randn(batch, 3, size, size, generator=g, device=device)
+
+
+def forward(model, images, dtype=torch.float32):
+    """One inference forward the way main.py:343-354 of the reference runs it: no_grad, with
+    autocast when a 16-bit dtype is asked for."""
+    with torch.no_grad():
+        if dtype == torch.float32:
+            return model(images)
+        with torch.autocast(device_type=images.device.type, dtype=dtype):
+            return model(images)

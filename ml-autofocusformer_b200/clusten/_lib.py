@@ -19,7 +19,6 @@ SIGNATURES = {
     "clusten_status_string": (ctypes.c_char_p, [_i]),
     "clusten_version": (_i, []),
     "clusten_launch_count": (ctypes.c_ulonglong, []),
-    "clusten_device_status": (_i, [ctypes.POINTER(ctypes.c_int), _i]),
     "clusten_timing_enable": (_i, [_i]),
     "clusten_timing_collect": (_i, [ctypes.c_char_p, _sz]),
     "clusten_inverse_bytes": (_sz, [_i, _i, _i, _i]),
@@ -63,13 +62,6 @@ def check(status):
     if status != 0:
         msg = load().clusten_status_string(status).decode()
         raise RuntimeError(f"clusten: {msg} (status {status})")
-
-
-def device_status(clear=True):
-    """Device status word of the library (0 = healthy); synchronises with the device."""
-    v = ctypes.c_int(0)
-    check(load().clusten_device_status(ctypes.byref(v), 1 if clear else 0))
-    return v.value
 
 
 def timing_enable(on):

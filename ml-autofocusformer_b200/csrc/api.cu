@@ -64,6 +64,42 @@ int sm_count() {
     return cached[dev];
 }
 
+int resident_ctas(const void* kernel, int threads, size_t smem) {
+    struct Key {
+        const void* k; int dev; size_t smem; int threads;
+        bool operator<(const Key& o) const {
+            if (k != o.k) return k < o.k;
+            if (dev != o.dev) return dev < o.dev;
+            if (smem != o.smem) return smem < o.smem;
+            return threads < o.threads;
+        }
+    };
+    static std::mutex mu;
+    static std::map<Key, int> cache;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    const Key key{kernel, dev, smem, threads};
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) {
+        cudaGetLastError();
+        return CLUSTEN_ERR_CUDA;
+    }
+    if (per_sm < 1) per_sm = 1;
+    cache[key] = per_sm;
+    return per_sm;
+}
+
 namespace {
 
 bool aligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; }
@@ -99,6 +135,25 @@ int check_inverse_args(int b, int n_rows, int m, int nt) {
     } while (0)
 
 }  // namespace
+
+int validate_av_backward(const void* d_feat, const void* attn, const void* value, const int64_t* nbhd_idx,
+                         const void* inverse, const void* d_attn, const void* d_value, int b, int h, int n, int m,
+                         int c, int dtype) {
+    int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    st = check_inverse_args(b, n, m, n);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(d_feat, es);
+    CLUSTEN_REQUIRE_PTR(attn, es);
+    CLUSTEN_REQUIRE_PTR(value, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(inverse, 16);
+    CLUSTEN_REQUIRE_PTR(d_attn, es);
+    CLUSTEN_REQUIRE_PTR(d_value, es);
+    return CLUSTEN_OK;
+}
+
 }  // namespace clusten
 
 using namespace clusten;
@@ -123,11 +178,6 @@ const char* clusten_status_string(int status) {
 }
 
 int clusten_version(void) { return 100; }
-
-int clusten_device_status(int* status, int clear) {
-    if (status == nullptr) return CLUSTEN_ERR_NULL;
-    return read_device_status(status, clear != 0);
-}
 
 int clusten_timing_enable(int on) {
     g_timing.store(on ? 1 : 0, std::memory_order_relaxed);
@@ -254,18 +304,8 @@ int clusten_av_forward(const void* attn, const void* value, const int64_t* nbhd_
 int clusten_av_backward(const void* d_feat, const void* attn, const void* value, const int64_t* nbhd_idx,
                         const void* inverse, void* d_attn, void* d_value, int b, int h, int n, int m, int c,
                         int dtype, void* stream) {
-    int st = check_attn_args(b, h, n, m, c, dtype);
+    int st = validate_av_backward(d_feat, attn, value, nbhd_idx, inverse, d_attn, d_value, b, h, n, m, c, dtype);
     if (st != CLUSTEN_OK) return st;
-    st = check_inverse_args(b, n, m, n);
-    if (st != CLUSTEN_OK) return st;
-    const size_t es = dtype_size(dtype);
-    CLUSTEN_REQUIRE_PTR(d_feat, es);
-    CLUSTEN_REQUIRE_PTR(attn, es);
-    CLUSTEN_REQUIRE_PTR(value, es);
-    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
-    CLUSTEN_REQUIRE_PTR(inverse, 16);
-    CLUSTEN_REQUIRE_PTR(d_attn, es);
-    CLUSTEN_REQUIRE_PTR(d_value, es);
     cudaStream_t s = (cudaStream_t)stream;
     const InverseView inv = inverse_view(inverse, b, n, m, n);
     // d_attn: dot of each gathered value row with the row's d_feat

@@ -58,7 +58,8 @@ __device__ __forceinline__ void st_vec(T* p, const Vec<T, V>& x) {
 constexpr int kInvHeaderInts = 64;
 constexpr uint32_t kInvMagic = 0x434c5354u;
 constexpr uint32_t kDupFlag = 0x80000000u;
-constexpr int kInvMaxTargets = 18000;
+constexpr int kInvSmemTargets = 18000;       // up to here the build keeps its per-target counters in shared memory
+constexpr int kInvMaxTargets = 1 << 20;      // beyond kInvSmemTargets they live behind the entries, in the buffer itself
 
 struct InverseView {
     const int* rowptr;    // [b][nt + 1]
@@ -68,9 +69,14 @@ struct InverseView {
 
 __host__ __device__ inline size_t inv_align(size_t x) { return (x + 63) & ~size_t(63); }
 
+// counters of the build when they do not fit in shared memory: [b][3 * nt] behind the entries
+inline size_t inverse_scratch_ints(int b, int nt) {
+    return nt > kInvSmemTargets ? inv_align(size_t(b) * 3 * nt) : 0;
+}
+
 inline size_t inverse_ints(int b, int n_rows, int m, int nt) {
     return kInvHeaderInts + inv_align(size_t(b) * (nt + 1)) + inv_align(size_t(b) * nt) +
-           inv_align(size_t(b) * n_rows * m);
+           inv_align(size_t(b) * n_rows * m) + inverse_scratch_ints(b, nt);
 }
 
 inline InverseView inverse_view(const void* buf, int b, int n_rows, int m, int nt) {
@@ -94,6 +100,11 @@ struct ScopedKernelTimer {
 };
 int check_launch();               // cudaGetLastError -> CLUSTEN_OK / CLUSTEN_ERR_CUDA
 int sm_count();                   // multiprocessors of the current device (cached per device)
+// One-time set-up of a kernel on the current device: raises its dynamic shared-memory limit to
+// smem bytes and returns how many CTAs of `threads` threads fit on one multiprocessor (>= 1), or a
+// negative status.  The answer is cached per (kernel, device, smem), so repeated launches cost a
+// map lookup instead of two runtime calls.
+int resident_ctas(const void* kernel, int threads, size_t smem);
 
 template <typename T> struct DtypeOf;
 template <> struct DtypeOf<float> { static constexpr int value = CLUSTEN_F32; };
@@ -111,11 +122,6 @@ inline int dtype_size(int dtype) {
     }
 }
 
-// ---------------------------------------------------------------- device status word
-// Bits a kernel ORs into the library's device status word when it has to give up.
-constexpr int kErrPipelineTimeout = 1;   // a bounded wait on a shared-memory barrier ran out
-int read_device_status(int* status, bool clear);   // tiled_fwd.cu; synchronises the device
-
 // ---------------------------------------------------------------- generic kernels (generic.cu)
 // out[bb, row, ic, :] = sum_j W[bb, row, j, ic] * X[bb, idx[bb / heads, row, j], :]
 int launch_gather_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out,
@@ -127,6 +133,11 @@ int launch_gather_dot(const char* label, int dtype, const void* X, const void* Y
 int launch_scatter_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
                        void* out, int nb, int heads, int n_rows, int n_tgt, int m, int ic, int c,
                        cudaStream_t s);
+
+// api.cu: every argument check of clusten_av_backward (sizes, dtype, pointers and their alignment)
+int validate_av_backward(const void* d_feat, const void* attn, const void* value, const int64_t* nbhd_idx,
+                         const void* inverse, const void* d_attn, const void* d_value, int b, int h, int n, int m,
+                         int c, int dtype);
 
 // inverse.cu
 int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s);

@@ -20,11 +20,15 @@ constexpr int kWarps = kThreads / 32;
 template <int P>
 __global__ void __launch_bounds__(kThreads)
 inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int* __restrict__ header,
-                     int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries) {
+                     int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries,
+                     int* __restrict__ scratch) {
     extern __shared__ int sm[];
-    int* base = sm;                                              // running write position of target t
-    unsigned* mask = reinterpret_cast<unsigned*>(sm + nt);       // rows of the current group that hit t
-    unsigned* dupm = reinterpret_cast<unsigned*>(sm + 2 * nt);   // rows that hit t more than once
+    // the three per-target arrays: in shared memory, or (more targets than fit there) in this batch
+    // element's part of the global scratch; the block barriers below order the accesses either way
+    int* counters = scratch ? scratch + (long long)blockIdx.x * 3 * nt : sm;
+    int* base = counters;                                              // running write position of target t
+    unsigned* mask = reinterpret_cast<unsigned*>(counters + nt);       // rows of the current group that hit t
+    unsigned* dupm = reinterpret_cast<unsigned*>(counters + 2 * nt);   // rows that hit t more than once
     __shared__ int warp_tot[kWarps];
 
     const int b = blockIdx.x;
@@ -435,27 +439,24 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
         const size_t smem128 = size_t(9) * nt * sizeof(int);
         auto kernel128 = m == 48 ? inverse_build128_kernel<2, true>
                                  : (m <= 32 ? inverse_build128_kernel<1, false> : inverse_build128_kernel<2, false>);
-        if (cudaFuncSetAttribute(kernel128, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem128) != cudaSuccess) {
-            cudaGetLastError();
-            return CLUSTEN_ERR_CUDA;
-        }
+        const int fit = resident_ctas(reinterpret_cast<const void*>(kernel128), kThreads, smem128);
+        if (fit < 0) return fit;
         ScopedKernelTimer timer("inverse_build", s);
         kernel128<<<b, kThreads, smem128, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
                                                const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
         note_launch();
         return check_launch();
     }
-    const size_t smem = size_t(3) * nt * sizeof(int);
+    int* scratch = nullptr;
+    if (nt > kInvSmemTargets)
+        scratch = const_cast<int*>(v.entries) + inv_align(size_t(b) * n_rows * m);
+    const size_t smem = scratch ? 0 : size_t(3) * nt * sizeof(int);
     auto kernel = m <= 32 ? inverse_build_kernel<1> : (m <= 64 ? inverse_build_kernel<2> : inverse_build_kernel<0>);
-    if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            cudaGetLastError();
-            return CLUSTEN_ERR_CUDA;
-        }
-    }
+    const int fit = resident_ctas(reinterpret_cast<const void*>(kernel), kThreads, smem);
+    if (fit < 0) return fit;
     ScopedKernelTimer timer("inverse_build", s);
     kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
-                                     const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
+                                     const_cast<int*>(v.seglen), const_cast<int*>(v.entries), scratch);
     note_launch();
     return check_launch();
 }

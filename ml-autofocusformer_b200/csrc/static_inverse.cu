@@ -14,7 +14,9 @@
 // device current, the first time the entry point runs there (that first call therefore does a little
 // set-up work and should come before any stream capture).  All calls share the one array: it keeps
 // the previous call's contents, the build re-initialises everything it later reads, and two calls
-// that overlap on the GPU (different streams or threads) race on it.
+// that overlap on the GPU (different streams or threads) race on it.  The looked-up address is kept
+// per device ordinal for the life of the process; it belongs to the device's primary context, so a
+// program that calls cudaDeviceReset must not use this entry point afterwards.
 #include <mutex>
 
 #include "common.cuh"
@@ -59,12 +61,16 @@ extern "C" int clusten_av_backward_noalloc(const void* d_feat, const void* attn,
                                            int n, int m, int c, int dtype, void* stream) {
     if (dtype_size(dtype) == 0) return CLUSTEN_ERR_DTYPE;
     if (b <= 0 || h <= 0 || n <= 0 || m <= 0 || c <= 0) return CLUSTEN_ERR_SHAPE;
-    if (m > 2048 || n > kInvMaxTargets || (long long)n * m >= 0x7fffffffLL) return CLUSTEN_ERR_UNSUPPORTED;
+    if (clusten_inverse_bytes(b, n, m, n) == 0) return CLUSTEN_ERR_UNSUPPORTED;
     // the fixed array must hold the whole inverse index of this call
     if (inverse_ints(b, n, m, n) > (size_t)CLUSTEN_NOALLOC_MAX_INTS) return CLUSTEN_ERR_NOALLOC_CAPACITY;
     int* inverse = static_inverse_address();
     if (inverse == nullptr) return CLUSTEN_ERR_CUDA;
-    int st = clusten_inverse_build(nbhd_idx, b, n, m, n, inverse, (size_t)CLUSTEN_NOALLOC_MAX_INTS * sizeof(int),
+    // every check of the regular entry point runs before anything is launched, so a rejected call
+    // neither touches the shared array nor spends a launch
+    int st = validate_av_backward(d_feat, attn, value, nbhd_idx, inverse, d_attn, d_value, b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    st = clusten_inverse_build(nbhd_idx, b, n, m, n, inverse, (size_t)CLUSTEN_NOALLOC_MAX_INTS * sizeof(int),
                                    stream);
     if (st != CLUSTEN_OK) return st;
     return clusten_av_backward(d_feat, attn, value, nbhd_idx, inverse, d_attn, d_value, b, h, n, m, c, dtype,

@@ -25,8 +25,6 @@
 
 namespace clusten {
 
-__device__ int g_device_status = 0;   // bits of kErr*, see read_device_status
-
 namespace {
 
 // ----------------------------------------------------------------------------- the kernel
@@ -884,17 +882,10 @@ int gather_tiles_t(const char* label, const void* A, const void* X, const int64_
     if ((long long)b * tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
     const size_t smem = size_t(kWarps) * WarpSmem<T, MODE>::kTotal;
     auto kernel = m == kMmax ? gather_tiles_kernel<T, MODE, true> : gather_tiles_kernel<T, MODE, false>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
     // one resident wave of CTAs; every warp strides over the (batch, tile) pairs
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kWarps, smem);
+    if (per_sm < 0) return per_sm;
+    long long grid = (long long)sm_count() * per_sm;
     const long long need = ((long long)b * tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);
@@ -922,16 +913,9 @@ int scatter_tiles_t(const char* label, ScatterParams p, cudaStream_t s) {
     p.w_pairs = reinterpret_cast<uintptr_t>(p.W) % 4 == 0 && p.w_batch % 2 == 0;
     const size_t smem = size_t(kWarps) * ScatterSmem<T>::kTotal;
     auto kernel = (p.m == 48 && p.ic == 1) ? scatter_tiles_kernel<T, true> : scatter_tiles_kernel<T, false>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kWarps, smem);
+    if (per_sm < 0) return per_sm;
+    long long grid = (long long)sm_count() * per_sm;
     const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);
@@ -950,23 +934,6 @@ int scatter_dispatch(const char* label, int dtype, const ScatterParams& p, cudaS
 }
 
 }  // namespace
-
-int read_device_status(int* status, bool clear) {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    if (clear && v != 0) {
-        const int zero = 0;
-        if (cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)) != cudaSuccess) {
-            cudaGetLastError();
-            return CLUSTEN_ERR_CUDA;
-        }
-    }
-    *status = v;
-    return CLUSTEN_OK;
-}
 
 bool tiled_sum_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c) {
     return gather_supported(dtype, {W, X, out}, n, m, c);

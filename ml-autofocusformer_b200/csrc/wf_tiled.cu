@@ -301,6 +301,7 @@ wf_tiles_kernel(const WfParams p) {
         if (lane < kT) {
             int r = -1;
             if (i0 + lane < n_out) r = p.order ? p.order[brow + i0 + lane] : i0 + lane;
+            if ((unsigned)r >= (unsigned)n_out) r = -1;     // an entry that is no row number: treated as absent
             rowsS[lane] = r;
         }
         __syncwarp();
@@ -980,16 +981,9 @@ int wf_dfeat_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfScatterSmem::kTotal;
     auto kernel = p.m != kMmax ? wf_dfeat_kernel<T, ICT, false, false>
                                : (p.c == kCG ? wf_dfeat_kernel<T, ICT, true, true> : wf_dfeat_kernel<T, ICT, true, false>);
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kWarps, smem);
+    if (per_sm < 0) return per_sm;
+    long long grid = (long long)sm_count() * per_sm;
     const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);
@@ -1013,16 +1007,9 @@ int wf_tiles_t(const char* label, const WfParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfSmem<MODE>::kTotal;
     auto kernel = p.m != kMmax ? wf_tiles_kernel<T, MODE, ICT, false, false>
                                : (p.c == kCG ? wf_tiles_kernel<T, MODE, ICT, true, true> : wf_tiles_kernel<T, MODE, ICT, true, false>);
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 32 * kWarps, smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
-    long long grid = (long long)sm_count() * (per_sm > 0 ? per_sm : 1);
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kWarps, smem);
+    if (per_sm < 0) return per_sm;
+    long long grid = (long long)sm_count() * per_sm;
     const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);

@@ -1,36 +1,76 @@
 #!/usr/bin/env python3
-"""Compile the upstream CLUSTEN CUDA extension, unmodified, into oracle/_ref/.
+"""Compile the upstream CLUSTEN CUDA extension and byte-compile the upstream caller
+modules, unmodified, into oracle/_ref/.
 
-TEST INFRASTRUCTURE ONLY.  The three extension modules this recipe produces
-(`clustenqk_cuda`, `clustenav_cuda`, `clustenwf_cuda`) are the reference's own
-kernels (clusten/src/*.cu, *.cpp of apple/ml-autofocusformer) compiled for
-sm_100a straight from the read-only checkout.  They are used as a checker for
-the oracle and for the parity tests, and as a speed bar in the benchmark; the
-product never loads them.
+TEST AND MEASUREMENT INFRASTRUCTURE ONLY.  Two things are produced, all from the
+read-only checkout of apple/ml-autofocusformer, nothing of it is copied as source:
 
-No source file is copied: nvcc / g++ read the sources where they lie and only
-object files and the three shared objects are written (all below oracle/_ref/,
-which is git-ignored).  The upstream setup.py is not run; the commands below
-are what it would amount to (three CUDAExtension modules, no extra flags:
-clusten/src/setup.py:15-28) plus an explicit sm_100a target.
+  * the three extension modules `clustenqk_cuda`, `clustenav_cuda`, `clustenwf_cuda`:
+    the reference's own kernels (clusten/src/*.cu, *.cpp) compiled for sm_100a.  They
+    check the oracle and the parity tests and serve as a speed bar in the benchmark.
+  * Python bytecode (.pyc) of the modules that CALL the operators: models/aff_transformer.py
+    and models/point_utils.py (the AutoFocusFormer model, the caller of this repository's
+    `clusten` package in the model-level benchmark) and clusten/clusten.py + clusten/__init__.py
+    (the reference's autograd wrappers, so that the same model can also run on the
+    reference's kernels).  They land in oracle/_ref/aff_model/models/ and
+    oracle/_ref/ref_clusten/clusten/ and are imported as sourceless modules.
 
-Usage:  python oracle/build_ref.py [--src /path/to/reference/clusten/src] [-j N]
-When the source directory does not exist the script exits 0 without doing
-anything, so a prebuilt oracle/_ref/ is used as is.
+nvcc / g++ / py_compile read the sources where they lie and only objects, shared
+objects and bytecode are written (all below oracle/_ref/, which is git-ignored).  The
+upstream setup.py is not run; the commands below are what it would amount to (three
+CUDAExtension modules, no extra flags: clusten/src/setup.py:15-28) plus an explicit
+sm_100a target.
+
+Usage:  python oracle/build_ref.py [--root /path/to/ml-autofocusformer] [-j N] [--force]
+The checkout is looked for at --root, else $CLUSTEN_REFERENCE_ROOT, else a directory
+named `reference` beside this repository.  When it does not exist the script exits 0
+without doing anything, so a prebuilt oracle/_ref/ is used as is.
 """
 import argparse
 import os
+import py_compile
 import subprocess
 import sys
 import sysconfig
 from concurrent.futures import ThreadPoolExecutor
 
-# where the reference checkout keeps the extension sources (override with CLUSTEN_REFERENCE_SRC)
-DEFAULT_SRC = os.environ.get("CLUSTEN_REFERENCE_SRC", "/root/reference/clusten/src")
-
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 MODULES = ("clustenqk_cuda", "clustenav_cuda", "clustenwf_cuda")
+# (source inside the checkout, bytecode below oracle/_ref/)
+BYTECODE = (
+    ("models/aff_transformer.py", "aff_model/models/aff_transformer.pyc"),
+    ("models/point_utils.py", "aff_model/models/point_utils.pyc"),
+    ("clusten/clusten.py", "ref_clusten/clusten/clusten.pyc"),
+    ("clusten/__init__.py", "ref_clusten/clusten/__init__.pyc"),
+)
+
+
+def reference_root(arg=None):
+    """Where the checkout of apple/ml-autofocusformer is expected."""
+    if arg:
+        return arg
+    env = os.environ.get("CLUSTEN_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
+
+
+def byte_compile(root, force=False):
+    """models/*.py and clusten/*.py of the checkout -> sourceless .pyc below oracle/_ref/."""
+    for src_rel, dst_rel in BYTECODE:
+        src, dst = os.path.join(root, src_rel), os.path.join(OUT, dst_rel)
+        if not os.path.exists(src):
+            continue
+        if force or not os.path.exists(dst) or os.path.getmtime(dst) < os.path.getmtime(src):
+            os.makedirs(os.path.dirname(dst), exist_ok=True)
+            py_compile.compile(src, cfile=dst, dfile=src_rel, doraise=True)
+            print("byte-compiled", src_rel, "->", dst, flush=True)
+    # the model package gets an empty __init__ of its own: the upstream one imports the
+    # training-side builder (models/__init__.py:8), which is not part of the measured path
+    init = os.path.join(OUT, "aff_model", "models", "__init__.py")
+    if os.path.isdir(os.path.dirname(init)) and not os.path.exists(init):
+        open(init, "w").close()
 
 
 def _run(cmd):
@@ -40,13 +80,17 @@ def _run(cmd):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--src", default=DEFAULT_SRC)
+    ap.add_argument("--root", default=None, help="checkout of apple/ml-autofocusformer")
     ap.add_argument("-j", type=int, default=3)
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args()
+    root = reference_root(args.root)
+    args.src = os.path.join(root, "clusten", "src")
     if not os.path.isdir(args.src):
         print(f"build_ref: {args.src} not present; keeping whatever is in {OUT}")
         return 0
+    os.makedirs(OUT, exist_ok=True)
+    byte_compile(root, args.force)
 
     import torch  # noqa: F401  (only for its headers and libraries)
     from torch.utils.cpp_extension import include_paths, library_paths

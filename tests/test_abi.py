@@ -46,8 +46,9 @@ def test_argument_checks_come_before_any_device_work(lib):
     assert lib.clusten_av_forward(ctypes.c_void_p(258), p, p, p, 1, 1, 8, 4, 32, 0, None) == -4  # alignment
     assert lib.clusten_wf_forward(p, p, p, None, p, 1, 8, 8, 4, 0, 32, 0, None) == -2
     assert lib.clusten_inverse_bytes(2, 100, 48, 100) > 0
-    assert lib.clusten_inverse_bytes(2, 100, 48, 10 ** 6) == 0                     # too many targets
-    assert lib.clusten_inverse_build(p, 2, 100, 48, 10 ** 6, p, 1 << 30, None) == -6
+    assert lib.clusten_inverse_bytes(2, 100, 48, 20000) > lib.clusten_inverse_bytes(2, 100, 48, 18000)
+    assert lib.clusten_inverse_bytes(2, 100, 48, 2 * 10 ** 6) == 0                 # too many targets
+    assert lib.clusten_inverse_build(p, 2, 100, 48, 2 * 10 ** 6, p, 1 << 30, None) == -6
     assert lib.clusten_inverse_build(p, 2, 100, 48, 100, p, 16, None) == -5        # buffer too small
     assert lib.clusten_qk_backward(p, p, p, p, None, p, p, 1, 1, 8, 4, 32, 0, None) == -3
 

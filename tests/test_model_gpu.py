@@ -1,0 +1,67 @@
+"""Model-level parity on the GPU: the reference's AutoFocusFormer (unmodified, bytecode in
+oracle/_ref/aff_model) gives the same logits on this package's operators as on the PyTorch gather
+formulation -- and, where the reference's own CUDA extension is built, as on the reference's kernels --
+with the same weights, images and neighbourhood stand-ins.  Tolerances (max |x - ref| / max |ref| over the
+logits, accumulated over all blocks): fp32 1e-4, bf16 autocast 5e-2."""
+import pytest
+import torch
+
+import aff_harness
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not aff_harness.available(), reason="oracle/_ref/aff_model is not built")]
+
+DEV = "cuda"
+
+
+def _rel(x, ref):
+    return ((x.double() - ref.double()).abs().max() / ref.double().abs().max()).item()
+
+
+@pytest.mark.parametrize("config,batch,dtype,tol", [
+    ("tiny224", 6, torch.float32, 1e-4),
+    ("tiny224", 6, torch.bfloat16, 5e-2),
+    ("base384", 2, torch.float32, 1e-4),
+    ("base384", 2, torch.bfloat16, 5e-2),
+], ids=["tiny224-fp32", "tiny224-bf16", "base384-fp32", "base384-bf16"])
+def test_logits_match_the_formula_operators(lib, config, batch, dtype, tol, capsys):
+    from clusten import _lib
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    aff_harness.use_implementation("b200")
+    model = aff_harness.build_model(config, DEV, seed=0)
+    x = aff_harness.synthetic_images(config, batch, DEV, seed=1)
+    before = _lib.launch_count()
+    got = aff_harness.forward(model, x, dtype)
+    launched = _lib.launch_count() - before
+    depths = aff_harness.CONFIGS[config]["depths"]
+    # every block of a local-attention stage calls QK and AV once, every merge calls WF once
+    assert launched >= 2 * sum(depths[:3]) + 3, launched
+    aff_harness.use_implementation("formula", formula_chunk=1)
+    want = aff_harness.forward(model, x, dtype)
+    err = _rel(got, want)
+    agree = (got.argmax(1) == want.argmax(1)).float().mean().item()
+    with capsys.disabled():
+        print(f"\n{config} {dtype}: logits rel err {err:.2e}, top-1 agreement {agree:.2f}, "
+              f"{launched} library kernel launches")
+    assert got.shape == (batch, 1000) and torch.isfinite(got.float()).all()
+    assert err <= tol, err
+    aff_harness.use_implementation("b200")
+
+
+def test_logits_match_the_reference_kernels(lib, capsys):
+    if not aff_harness.reference_kernels_available():
+        pytest.skip("the reference's CUDA extension (oracle/_ref) is not built")
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    aff_harness.use_implementation("b200")
+    model = aff_harness.build_model("tiny224", DEV, seed=3)
+    x = aff_harness.synthetic_images("tiny224", 4, DEV, seed=4)
+    got = aff_harness.forward(model, x)
+    aff_harness.use_implementation("reference")
+    want = aff_harness.forward(model, x)
+    aff_harness.use_implementation("b200")
+    err = _rel(got, want)
+    with capsys.disabled():
+        print(f"\ntiny224 fp32 vs the reference's kernels: logits rel err {err:.2e}")
+    assert err <= 1e-4, err

@@ -45,6 +45,13 @@ ATT_SHAPES = [
     (1, 1, 40, 9, 24),
     (1, 2, 96, 24, 64),
     (1, 1, 5, 12, 7),
+    # config 0 of the benchmark (QK forward on CPU there), the stage shapes of the per-stage sweep at small
+    # batch (h = 8 / n = 196, h = 16 / n = 49 with m = 49) and the padded stages of the 384 x 384 model
+    (2, 2, 3136, 48, 32),
+    (2, 8, 196, 48, 32),
+    (2, 16, 49, 49, 32),
+    (1, 16, 368, 48, 32),
+    (2, 32, 73, 48, 32),
 ]
 
 
@@ -91,6 +98,13 @@ WF_SHAPES = [
     (1, 33, 90, 13, 2, 128),
     (1, 20, 100, 16, 3, 24),
     (1, 7, 30, 5, 2, 9),
+    # m above 48 on the tiled d_feat path; ic = 3 and ic = 16 with 32-channel slabs on the tiled scatter path
+    (1, 20, 100, 80, 4, 64),
+    (1, 20, 100, 16, 3, 32),
+    (1, 12, 60, 24, 16, 32),
+    # the merges of the 384 x 384 model at 1/5 retention: 1843 -> 368 and 368 -> 73 rows
+    (1, 368, 1843, 48, 4, 64),
+    (2, 73, 368, 48, 4, 128),
 ]
 
 
@@ -299,31 +313,35 @@ def test_against_the_reference_cuda_extension(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
-def test_full_size_adjoint_identities(ops, dtype):
+@pytest.mark.parametrize("regime", ["shared", "model"])
+def test_full_size_adjoint_identities(ops, regime, dtype):
     """Stage-1 shapes of the benchmark (b=128, h=2, n=3136, m=48, c=32; WF n_=784, c=64, ic=4),
     where the oracle is too slow: each operator is bilinear, so <op(x, y), g> must equal
     <x, grad_x> and <y, grad_y>, which ties forward, both gradients and the inverse index
-    together at full size."""
+    together at full size.  Two batch elements are also compared, forward and all gradients, with the
+    gather formulation evaluated in fp32 on the GPU."""
     b, h, n, m, c = 128, 2, 3136, 48, 32
-    idx = workloads.shared_cluster_rows(b, n, m, 71, DEV)
+    idx = workloads.make_index(regime, b, n, m, 71, DEV)
     q, k, v, attn, g_attn, g_feat = workloads.attention_operands(b, h, n, m, c, dtype, 72, DEV)
     tol = 1e-4 if dtype == torch.float32 else 3e-2
 
     def dot(x, y):
         return (x.double() * y.double()).sum().item()
 
+    sl = slice(5, 7)
+    f32 = lambda *ts: [t[sl].float() for t in ts]
     out = ops.qk_forward(q, k, idx)
     dq, dk = ops.qk_backward(g_attn, q, k, idx)
     lhs = dot(out, g_attn)
     assert abs(dot(q, dq) - lhs) <= tol * abs(lhs) and abs(dot(k, dk) - lhs) <= tol * abs(lhs)
+    ro, rq, rk = formula.forward_backward("qk", *f32(q, k), idx[sl], g_attn[sl].float())
+    assert rel_err(out[sl], ro) <= TOL[dtype] and rel_err(dq[sl], rq) <= TOL[dtype] and rel_err(dk[sl], rk) <= TOL[dtype]
     feat = ops.av_forward(attn, v, idx)
     da, dv = ops.av_backward(g_feat, attn, v, idx)
     lhs = dot(feat, g_feat)
     assert abs(dot(attn, da) - lhs) <= tol * abs(lhs) and abs(dot(v, dv) - lhs) <= tol * abs(lhs)
-    # spot-check a slice of the batch against the gather formulation evaluated on the GPU
-    sl = slice(5, 7)
-    ref = formula.av(attn[sl].float(), v[sl].float(), idx[sl])
-    assert rel_err(feat[sl], ref) <= TOL[dtype]
+    ro, ra, rv = formula.forward_backward("av", *f32(attn, v), idx[sl], g_feat[sl].float())
+    assert rel_err(feat[sl], ro) <= TOL[dtype] and rel_err(da[sl], ra) <= TOL[dtype] and rel_err(dv[sl], rv) <= TOL[dtype]
 
     n_out, ic, cw = 784, 4, 64
     idx_w = workloads.select_rows(idx, n_out, 73)
@@ -332,5 +350,133 @@ def test_full_size_adjoint_identities(ops, dtype):
     dw, df = ops.wf_backward(g, w, f, idx_w)
     lhs = dot(out, g)
     assert abs(dot(w, dw) - lhs) <= tol * abs(lhs) and abs(dot(f, df) - lhs) <= tol * abs(lhs)
-    ref = formula.wf(w[sl].float(), f[sl].float(), idx_w[sl])
-    assert rel_err(out[sl], ref) <= TOL[dtype]
+    ro, rw, rf = formula.forward_backward("wf", *f32(w, f), idx_w[sl], g[sl].float())
+    assert rel_err(out[sl], ro) <= TOL[dtype] and rel_err(dw[sl], rw) <= TOL[dtype] and rel_err(df[sl], rf) <= TOL[dtype]
+
+
+# ----------------------------------------------------------------------------- paths that ordinary tables do not reach
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16], ids=["float32", "bfloat16", "float16"])
+@pytest.mark.parametrize("repeats", [1, 3])
+def test_hot_token_segments_span_several_chunks(ops, repeats, dtype):
+    """Every row names token 0 (once, or three times as the padded stages do, models/point_utils.py:189-206
+    of the reference), so the tile of targets 0..7 has far more edges than the scatter kernels take at a
+    time: later chunks accumulate onto what earlier ones wrote."""
+    b, h, n, m, c = 2, 2, 648, 48, 32
+    for regime in ("model", "random"):
+        idx, q, k, v, attn, g_attn, g_feat = _attention_case(regime, b, h, n, m, c, dtype, 300 + repeats)
+        idx[:, :, -repeats:] = 0
+        dq, dk = ops.qk_backward(g_attn, q, k, idx)
+        rq, rk = exact("qk", "backward", g_attn, q, k, idx)
+        assert_close(dq, rq, dtype, f"d_query ({regime})")
+        assert_close(dk, rk, dtype, f"d_key ({regime})")
+        da, dv = ops.av_backward(g_feat, attn, v, idx)
+        ra, rv = exact("av", "backward", g_feat, attn, v, idx)
+        assert_close(da, ra, dtype, f"d_attn ({regime})")
+        assert_close(dv, rv, dtype, f"d_value ({regime})")
+    # the merge operator with 408 rows that all name token 0
+    n_out, ic, cw = 408, 4, 64
+    idx_w = workloads.select_rows(workloads.make_index("model", b, n, m, 310), n_out, 311).to(DEV)
+    idx_w[:, :, -repeats:] = 0
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, cw, dtype, 312))
+    assert_close(ops.wf_forward(w, feat, idx_w), exact("wf", "forward", w, feat, idx_w), dtype, "wf forward")
+    dw, df = ops.wf_backward(g, w, feat, idx_w)
+    rw, rf = exact("wf", "backward", g, w, feat, idx_w)
+    assert_close(dw, rw, dtype, "d_weights")
+    assert_close(df, rf, dtype, "d_feat")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+def test_token_ids_beyond_8192(ops, regime, dtype):
+    """Stage 1 of the 384 x 384 model has 9216 tokens: the ids of one tile of random rows then span more
+    than the de-duplication bitmap covers (one slot per edge instead), and the merge gathers from
+    9216 tokens into 1843 rows (1/5 retention, not a multiple of 8)."""
+    b, h, n, m, c = 1, 4, 9216, 48, 32
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case(regime, b, h, n, m, c, dtype, 320)
+    assert_close(ops.qk_forward(q, k, idx), exact("qk", "forward", q, k, idx), dtype, "qk forward")
+    dq, dk = ops.qk_backward(g_attn, q, k, idx)
+    rq, rk = exact("qk", "backward", g_attn, q, k, idx)
+    assert_close(dq, rq, dtype, "d_query")
+    assert_close(dk, rk, dtype, "d_key")
+    assert_close(ops.av_forward(attn, v, idx), exact("av", "forward", attn, v, idx), dtype, "av forward")
+    da, dv = ops.av_backward(g_feat, attn, v, idx)
+    ra, rv = exact("av", "backward", g_feat, attn, v, idx)
+    assert_close(da, ra, dtype, "d_attn")
+    assert_close(dv, rv, dtype, "d_value")
+    n_out, ic, cw = 1843, 4, 128
+    idx_w = workloads.select_rows(idx.cpu(), n_out, 321).to(DEV) if regime != "random" else \
+        workloads.random_rows(b, n_out, n, m, 321).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, cw, dtype, 322))
+    assert_close(ops.wf_forward(w, feat, idx_w), exact("wf", "forward", w, feat, idx_w), dtype, "wf forward")
+    dw, df = ops.wf_backward(g, w, feat, idx_w)
+    rw, rf = exact("wf", "backward", g, w, feat, idx_w)
+    assert_close(dw, rw, dtype, "d_weights")
+    assert_close(df, rf, dtype, "d_feat")
+
+
+def test_wf_rows_that_repeat_a_neighbour(ops):
+    """Merge rows that name one token several times, on the tiled paths with ic = 3, ic = 16 and m = 80."""
+    for (b, n_out, n, m, ic, c) in [(1, 20, 100, 16, 3, 32), (1, 12, 60, 24, 16, 32), (1, 20, 100, 80, 4, 64)]:
+        idx = workloads.random_rows(b, n_out, n, m, 330).to(DEV)
+        idx[:, :, 1] = idx[:, :, 0]
+        idx[:, ::2, -1] = idx[:, ::2, 2]
+        w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, torch.float32, 331))
+        assert_close(ops.wf_forward(w, feat, idx), exact("wf", "forward", w, feat, idx), torch.float32, "wf forward")
+        dw, df = ops.wf_backward(g, w, feat, idx)
+        rw, rf = exact("wf", "backward", g, w, feat, idx)
+        assert_close(dw, rw, torch.float32, "d_weights")
+        assert_close(df, rf, torch.float32, "d_feat")
+
+
+def test_fp32_products_with_widely_spread_magnitudes(ops, capsys):
+    """FP32 inputs are multiplied as three TF32 passes (high x high, high x low, low x high).  With
+    magnitudes spread over 2^-20 .. 2^20 the error must still stay inside the fp32 tolerance; the margin
+    is printed."""
+    b, h, n, m, c = 2, 2, 392, 48, 32
+    idx, q, k, v, attn, g_attn, g_feat = _attention_case("shared", b, h, n, m, c, torch.float32, 340)
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(341)
+
+    def spread(t):
+        e = torch.randint(-20, 21, t.shape, generator=gen, device=DEV).float()
+        return t * torch.exp2(e)
+
+    q, k, v, g_attn, g_feat = (spread(t) for t in (q, k, v, g_attn, g_feat))
+    errs = {"qk forward": rel_err(ops.qk_forward(q, k, idx), exact("qk", "forward", q, k, idx)),
+            "av forward": rel_err(ops.av_forward(attn, v, idx), exact("av", "forward", attn, v, idx))}
+    dq, dk = ops.qk_backward(g_attn, q, k, idx)
+    rq, rk = exact("qk", "backward", g_attn, q, k, idx)
+    da, dv = ops.av_backward(g_feat, attn, v, idx)
+    ra, rv = exact("av", "backward", g_feat, attn, v, idx)
+    errs.update({"d_query": rel_err(dq, rq), "d_key": rel_err(dk, rk), "d_attn": rel_err(da, ra),
+                 "d_value": rel_err(dv, rv)})
+    with capsys.disabled():
+        print("\nfp32 three-pass TF32 products, inputs scaled by 2^[-20, 20]:",
+              {k_: f"{e:.2e} ({TOL[torch.float32] / max(e, 1e-30):.1f}x inside)" for k_, e in errs.items()})
+    assert max(errs.values()) <= TOL[torch.float32], errs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def test_more_targets_than_fit_in_shared_memory(ops, dtype):
+    """n = 20000 tokens (a 640 x 640 input): the inverse build keeps its per-target counters in global
+    memory; the reference's atomicAdd scatter has no size limit (clusten/src/clustenqk_cuda_kernel.cu:125)."""
+    b, h, n, m, c = 1, 2, 20000, 16, 32
+    for regime in ("model", "random"):
+        idx, q, k, v, attn, g_attn, g_feat = _attention_case(regime, b, h, n, m, c, dtype, 350)
+        if regime == "random":
+            idx[:, :, -2:] = 0
+        dq, dk = ops.qk_backward(g_attn, q, k, idx)
+        rq, rk = exact("qk", "backward", g_attn, q, k, idx)
+        assert_close(dq, rq, dtype, f"d_query ({regime})")
+        assert_close(dk, rk, dtype, f"d_key ({regime})")
+        da, dv = ops.av_backward(g_feat, attn, v, idx)
+        ra, rv = exact("av", "backward", g_feat, attn, v, idx)
+        assert_close(da, ra, dtype, f"d_attn ({regime})")
+        assert_close(dv, rv, dtype, f"d_value ({regime})")
+    n_out, ic, cw = 4000, 4, 64
+    idx_w = workloads.random_rows(b, n_out, n, m, 351).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, cw, dtype, 352))
+    dw, df = ops.wf_backward(g, w, feat, idx_w)
+    rw, rf = exact("wf", "backward", g, w, feat, idx_w)
+    assert_close(dw, rw, dtype, "d_weights")
+    assert_close(df, rf, dtype, "d_feat")

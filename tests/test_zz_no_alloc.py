@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import workloads
-from helpers import assert_close
+from helpers import assert_close, exact
 
 pytestmark = pytest.mark.gpu
 
@@ -44,6 +44,35 @@ def test_noalloc_matches_regular_entry_point_twice(lib, dtype):
         assert_close(d_attn, ref_attn, dtype, f"d_attn ({regime})")
         assert_close(d_v, ref_v, dtype, f"d_value ({regime})")
         assert torch.equal(d_v, ref_v), "same kernels, same index: results must be bit-identical"
+        want_attn, want_v = exact("av", "backward", g_feat, attn, v, idx)
+        assert_close(d_attn, want_attn, dtype, f"d_attn vs the oracle ({regime})")
+        assert_close(d_v, want_v, dtype, f"d_value vs the oracle ({regime})")
+
+
+def test_noalloc_at_and_just_above_its_capacity(lib):
+    """The largest stage-1 problem (n = 3136, m = 48) whose inverse index the built-in array holds, and one
+    batch element more, which is refused.  A rejected call must leave its outputs untouched."""
+    dev = "cuda"
+    h, n, m = 2, 3136, 48
+    capacity = 3407936 * 4                      # CLUSTEN_NOALLOC_MAX_INTS ints
+    b = max(x for x in range(1, 64) if lib.clusten_inverse_bytes(x, n, m, n) <= capacity)
+    assert lib.clusten_inverse_bytes(b + 1, n, m, n) > capacity
+    idx = workloads.make_index("shared", b + 1, n, m, 21, dev)
+    _, _, v, attn, _, g_feat = workloads.attention_operands(b + 1, h, n, m, 32, torch.float16, 22, dev)
+    status, d_attn, d_v = _call_noalloc(lib, g_feat[:b].contiguous(), attn[:b].contiguous(), v[:b].contiguous(),
+                                        idx[:b].contiguous())
+    assert status == 0, lib.clusten_status_string(status)
+    from clusten import ops
+    ref_attn, ref_v = ops.av_backward(g_feat[:b].contiguous(), attn[:b].contiguous(), v[:b].contiguous(),
+                                      idx[:b].contiguous())
+    assert torch.equal(d_v, ref_v) and torch.equal(d_attn, ref_attn)
+    status, d_attn, d_v = _call_noalloc(lib, g_feat, attn, v, idx)
+    assert status == -8
+    assert torch.isnan(d_attn).all() and torch.isnan(d_v).all()
+    # a NULL output is refused before anything is launched
+    st = lib.clusten_av_backward_noalloc(g_feat.data_ptr(), attn.data_ptr(), v.data_ptr(), idx.data_ptr(), None,
+                                         d_v.data_ptr(), 2, h, n, m, 32, 1, torch.cuda.current_stream().cuda_stream)
+    assert st == -3
 
 
 def test_noalloc_rejects_sizes_beyond_its_array(lib):
