@@ -3,6 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype fp32|bf16] [--impl b200|reference]
     python bench.py --ops            # per-operator table (fp32 and bf16, three index regimes)
+    python bench.py --workload config2   # per-stage chain QK -> +bias -> softmax -> AV, WF between stages (b=256, bf16)
+    python bench.py --no-model       # leave out the model-level (images/sec) legs
 
 A step is one pass of the hot path over one batch of synthetic input at the stage-1 shapes
 of AutoFocusFormer (224^2 image, batch 128 per GPU): CLUSTENAV forward + backward on
@@ -15,6 +17,13 @@ The metric is GB/s of algorithmic bytes (each input read once, each output writt
 int64 indices, nothing for workspaces) summed over the step; one JSON line is printed by
 rank 0.  With N > 1 every rank runs its own batch (weak scaling, no collective on the data
 path) and the time is the maximum over ranks.
+
+Beside the step the line carries sub-records: `bf16` (the same step in bf16), `config0` (QK forward
+[2,2,3136,32], m=48: the PyTorch formulation on the host cores next to the kernel), `config2` (the
+per-stage chain at batch 256 in bf16) and `model` (forward images/sec of the reference's
+AutoFocusFormer, unmodified, on these operators: Tiny-like 224^2 at batch 256 in fp32 and bf16
+autocast, Base-like 384^2 at batch 64 in bf16 autocast; 50 warm-up + 30 timed forwards as in
+main.py:343-354 of the reference; summed over the ranks).
 
 --impl reference times the pure-PyTorch gather formulation of the reference's kernel tests on
 the host CPU cores (the reference ships no CPU implementation of these operators) on a
@@ -52,7 +61,9 @@ import workloads  # noqa: E402
 CFG = dict(b=128, h=2, n=3136, m=48, c=32, n_out=784, cw=64, ic=4)
 CPU_SAMPLE_BATCH = 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture at b=32, scaled x4 to the
-# benchmark's b=128 (traffic grows with the batch); see profiles/
+# benchmark's b=128 (traffic grows with the batch); see profiles/.  NCU_CAPTURE_BUILD names the commit whose
+# kernels were captured: the figure describes that build, not necessarily the one being timed.
+NCU_CAPTURE_BUILD = "3b5f93e"
 NCU_DRAM_BYTES_PER_LAUNCH = {("av_d_value", "fp32"): 4 * (84358656 + 10250240),
                              ("av_forward", "fp32"): 4 * (103323904 + 10757888),
                              ("wf_forward", "fp32"): 4 * (54756864 + 2429440),
@@ -294,10 +305,27 @@ def time_cpu(cfg, dtype, steps, warmup):
                       f"PyTorch gather formulation (oracle/formula.py), {steps} repeats"}
 
 
+def time_cpu_full_batch(cfg, dtype):
+    """One repeat of the whole batch on the host cores, in chunks of CPU_SAMPLE_BATCH with the chunk times
+    summed (the gathered [b,h,n,m,c] tensor of the formulation does not fit otherwise)."""
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(cores)
+    chunks = -(-cfg["b"] // CPU_SAMPLE_BATCH)
+    total = 0.0
+    for ci in range(chunks):
+        small, sample = cpu_sample(cfg, dtype, 100 + ci)
+        t0 = time.perf_counter()
+        cpu_formula_step(sample)
+        total += time.perf_counter() - t0
+    nbytes = sum(step_bytes(cfg, 4 if dtype == torch.float32 else 2).values())
+    return {"value": nbytes / total / 1e9, "unit": "GB/s", "s_per_step": total, "cores": cores,
+            "sample": f"all {cfg['b']} batch elements once, {chunks} chunks of {CPU_SAMPLE_BATCH}, chunk times summed"}
+
+
 # --------------------------------------------------------------------------- reference CUDA extension (speed bar)
 def time_reference_cuda(wl, reps=5):
     from oracle import ref_cuda
-    if not ref_cuda.available() or wl["attn"].dtype != torch.float32:
+    if wl is None or not ref_cuda.available() or wl["attn"].dtype != torch.float32:
         return None
 
     def run():
@@ -409,6 +437,229 @@ def run_reference_arm(args, dtype, rank):
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------- sub-records
+def time_step_series(ops, wl, steps, reps, barrier, reduce_max):
+    """`reps` back-to-back repetitions of a timed loop of exactly `steps` device steps, each bracketed by a
+    barrier + synchronize; per repetition the time is the maximum over the ranks.  -> ms per step, per rep."""
+    series = []
+    for _ in range(reps):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for _ in range(steps):
+            device_step(ops, wl)
+        stop.record()
+        barrier()
+        series.append(reduce_max(start.elapsed_time(stop) / steps))
+    return series
+
+
+def config0_record(device):
+    """BASELINE config 0: CLUSTENQK forward, fp32, q,k [2,2,3136,32], nbhd_idx [2,3136,48] (clustered,
+    shared rows).  The PyTorch gather formulation on the host cores next to the kernel on the GPU, and
+    their agreement."""
+    from clusten import ops
+    from oracle import formula
+    b, h, n, m, c = 2, 2, 3136, 48, 32
+    idx = workloads.shared_cluster_rows(b, n, m, 0)
+    q, k, _, _, _, _ = workloads.attention_operands(b, h, n, m, c, torch.float32, 1)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(cores)
+    formula.qk(q, k, idx)
+    times = []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        ref = formula.qk(q, k, idx)
+        times.append(time.perf_counter() - t0)
+    cpu_ms = statistics.median(times) * 1e3
+    qd, kd, idxd = q.to(device), k.to(device), idx.to(device)
+    gpu_ms = _time(lambda: ops.qk_forward(qd, kd, idxd), reps=30, warmup=5)
+    out = ops.qk_forward(qd, kd, idxd).cpu()
+    err = ((out.double() - ref.double()).abs().max() / ref.double().abs().max()).item()
+    nbytes = workloads.algorithmic_bytes("qk", "fwd", b=b, h=h, n=n, m=m, c=c, s=4)
+    return {"workload": "config0: CLUSTENQK forward fp32 [2,2,3136,32], m=48", "MB": round(nbytes / 1e6, 2),
+            "cpu_formula_ms": round(cpu_ms, 3), "cpu_cores": cores, "cpu_GBps": round(nbytes / cpu_ms / 1e6, 2),
+            "gpu_ms": round(gpu_ms, 4), "gpu_GBps": round(nbytes / gpu_ms / 1e6, 1),
+            "note": "8 MB: fits in L2, launch-latency bound on the GPU", "rel_err_vs_cpu_formula": err}
+
+
+CONFIG2_STAGES = [  # tokens, heads, channels, neighbours
+    dict(n=3136, h=2, C=64, m=48), dict(n=784, h=4, C=128, m=48),
+    dict(n=196, h=8, C=256, m=48), dict(n=49, h=16, C=512, m=49)]
+
+
+def config2_records(device, batch=256, dtype=torch.bfloat16, reps=12):
+    """BASELINE config 2: per stage the chain QK -> + position bias -> softmax -> AV (the local-attention
+    operators as models/aff_transformer.py:117-155 of the reference strings them together; bias add and
+    softmax are torch kernels) and the WF merge to the next stage (:361), batch 256, bf16, clustered shared
+    rows; stage 4 has m = 49 = every token.  Stages whose operands fit in L2 rotate over several buffer
+    sets.  -> one record per stage."""
+    from clusten import ops
+    peak, _ = _peaks()
+    out = []
+    s = 2
+    for si, st in enumerate(CONFIG2_STAGES):
+        n, h, m, C = st["n"], st["h"], st["m"], st["C"]
+        per_set = batch * (3 * h * n * 32 * s + 2 * h * n * m * s + n * m * 8)
+        sets = max(1, min(8, -(-4 * 126_000_000 // per_set))) if per_set < 4 * 126_000_000 else 1
+        bufs = []
+        for k_ in range(sets):
+            idx = workloads.shared_cluster_rows(batch, n, m, 40 + 10 * si + k_, device)
+            q, k, v, _, _, _ = workloads.attention_operands(batch, h, n, m, 32, dtype, 41 + 10 * si + k_, device)
+            bias = torch.randn(batch, h, n, m, device=device, dtype=dtype)
+            bufs.append((idx, q, k, v, bias))
+        rec = {"stage": si + 1, "tokens": n, "heads": h, "m": m, "buffer_sets": sets}
+        timers = {}
+
+        def timed(name, fn, i):
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            r = fn()
+            b_.record()
+            timers.setdefault(name, []).append((a, b_))
+            return r
+
+        def chain(i):
+            idx, q, k, v, bias = bufs[i % sets]
+            attn = timed("qk_ms", lambda: ops.qk_forward(q, k, idx), i)
+            attn = timed("bias_softmax_ms", lambda: torch.softmax(attn + bias, -1), i)
+            return timed("av_ms", lambda: ops.av_forward(attn, v, idx), i)
+
+        for i in range(3):
+            chain(i)
+        timers.clear()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record()
+        for i in range(reps):
+            chain(i)
+        t1.record()
+        torch.cuda.synchronize()
+        rec["chain_ms"] = round(t0.elapsed_time(t1) / reps, 4)
+        for name, evs in timers.items():
+            rec[name] = round(statistics.median(a.elapsed_time(b_) for a, b_ in evs), 4)
+        ab = workloads.algorithmic_bytes("qk", "fwd", b=batch, h=h, n=n, m=m, c=32, s=s)
+        rec["qk_av_MB"] = round(ab / 1e6, 1)
+        rec["qk_frac_of_hbm_peak"] = round(ab / rec["qk_ms"] / 1e6 / peak, 3)
+        rec["av_frac_of_hbm_peak"] = round(ab / rec["av_ms"] / 1e6 / peak, 3)
+        del bufs
+        if si < 3:
+            n_out, ic = CONFIG2_STAGES[si + 1]["n"], 4
+            wsets = []
+            for k_ in range(sets):
+                idx = workloads.shared_cluster_rows(batch, n, 48, 45 + 10 * si + k_, device)
+                idx_w = workloads.select_rows(idx, n_out, 46 + 10 * si + k_)
+                w, feat, _ = workloads.merge_operands(batch, n_out, n, 48, ic, C, dtype, 47 + 10 * si + k_, device)
+                wsets.append((w, feat, idx_w))
+            del idx
+            for i in range(3):
+                ops.wf_forward(*wsets[i % sets])
+            torch.cuda.synchronize()
+            t0.record()
+            for i in range(reps):
+                ops.wf_forward(*wsets[i % sets])
+            t1.record()
+            torch.cuda.synchronize()
+            wf_ms = t0.elapsed_time(t1) / reps
+            wb = workloads.algorithmic_bytes("wf", "fwd", b=batch, n=n, m=48, c=C, s=s, n_out=n_out, ic=ic)
+            rec.update({"wf_ms": round(wf_ms, 4), "wf_MB": round(wb / 1e6, 1),
+                        "wf_frac_of_hbm_peak": round(wb / wf_ms / 1e6 / peak, 3),
+                        "wf_note": "row order built once per index tensor (cached), as the operator does"})
+            del wsets
+        torch.cuda.empty_cache()
+        out.append(rec)
+    return out
+
+
+MODEL_LEGS = [("tiny224", 256, "fp32"), ("tiny224", 256, "bf16"), ("base384", 64, "bf16")]
+
+
+def model_records(device, world, barrier, reduce_max, warmup=50, steps=30, legs=MODEL_LEGS, with_reference=True):
+    """Forward images/sec of the reference's AutoFocusFormer (unmodified; bytecode in oracle/_ref/aff_model)
+    on this package's operators, by the protocol of main.py:343-354 of the reference: `warmup` untimed
+    forwards, then `steps` timed ones on one resident batch, images/sec = steps * batch / time; here with
+    CUDA events, the maximum time over the ranks, and the batch per rank fixed (weak scaling), so the value
+    is world * steps * batch / time.  16-bit legs run under autocast as the reference does (main.py:344).
+    Also per leg: an end-to-end figure whose timed region copies the images from pinned host memory and
+    the logits back every step, and the logits' agreement with the same model on the PyTorch gather
+    formulation at a small batch."""
+    import aff_harness
+    if not aff_harness.available():
+        return {"unavailable": "oracle/_ref/aff_model (bytecode of the reference's model) is not built"}
+    records = []
+    for config, batch, dname in legs:
+        dtype = torch.float32 if dname == "fp32" else torch.bfloat16
+        rec = {"config": config, "batch_per_gpu": batch, "dtype": dname,
+               "precision": "fp32" if dname == "fp32" else "torch.autocast(bfloat16)"}
+        try:
+            aff_harness.use_implementation("b200")
+            model = aff_harness.build_model(config, device, seed=0)
+            # parity at a small batch (the formulation materialises [b,h,n,m,c])
+            xs = aff_harness.synthetic_images(config, 2, device, seed=1)
+            got = aff_harness.forward(model, xs, dtype)
+            aff_harness.use_implementation("formula", formula_chunk=1)
+            want = aff_harness.forward(model, xs, dtype)
+            aff_harness.use_implementation("b200")
+            rec["logits_rel_err_vs_formula"] = ((got.double() - want.double()).abs().max()
+                                                / want.double().abs().max()).item()
+            rec["top1_agreement"] = (got.argmax(1) == want.argmax(1)).float().mean().item()
+            del model, xs, got, want
+            model = aff_harness.build_model(config, device, seed=0)      # fresh stage-1 clustering cache for this batch
+            images = aff_harness.synthetic_images(config, batch, device, seed=2)
+            from clusten import _lib
+            for _ in range(warmup):
+                aff_harness.forward(model, images, dtype)
+            l0 = _lib.launch_count()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            t0.record()
+            for _ in range(steps):
+                aff_harness.forward(model, images, dtype)
+            t1.record()
+            barrier()
+            ms = reduce_max(t0.elapsed_time(t1))
+            rec["images_per_sec"] = world * steps * batch / (ms * 1e-3)
+            rec["ms_per_forward"] = ms / steps
+            rec["library_launches_per_forward"] = (_lib.launch_count() - l0) / steps
+            # end to end: images from pinned host memory in, logits out, every step
+            host = images.cpu().pin_memory()
+            out_host = torch.empty(batch, 1000, dtype=torch.float32).pin_memory()
+            e_steps = max(3, steps // 3)
+            barrier()
+            t0.record()
+            for _ in range(e_steps):
+                images.copy_(host, non_blocking=True)
+                out_host.copy_(aff_harness.forward(model, images, dtype).float(), non_blocking=True)
+            t1.record()
+            barrier()
+            ms = reduce_max(t0.elapsed_time(t1))
+            rec["e2e_images_per_sec"] = world * e_steps * batch / (ms * 1e-3)
+            rec["e2e_h2d_bytes_per_step"] = host.numel() * 4
+            rec["e2e_d2h_bytes_per_step"] = out_host.numel() * 4
+            if with_reference and world == 1 and dname == "fp32" and aff_harness.reference_kernels_available():
+                # the same model on the reference's own kernels (compiled unmodified into oracle/_ref), same GPU
+                aff_harness.use_implementation("reference")
+                for _ in range(5):
+                    aff_harness.forward(model, images, dtype)
+                torch.cuda.synchronize()
+                t0.record()
+                for _ in range(10):
+                    aff_harness.forward(model, images, dtype)
+                t1.record()
+                torch.cuda.synchronize()
+                rec["reference_kernels_images_per_sec"] = 10 * batch / (t0.elapsed_time(t1) * 1e-3)
+                aff_harness.use_implementation("b200")
+            del model, images
+        except Exception as e:  # a leg that cannot run is reported, not hidden
+            rec["error"] = f"{type(e).__name__}: {e}"[:300]
+        torch.cuda.empty_cache()
+        records.append(rec)
+    return {"protocol": f"{warmup} warm-up + {steps} timed forwards, eval, no_grad; seeded random weights, N(0,1) "
+                        "images of ImageNet's shape (dataset and checkpoints are not available)",
+            "standins": "timm DropPath/trunc_normal_, cdist+topk for pykeops KNN (aff_harness.py)",
+            "legs": records}
+
+
 def run_b200_arm(args, dtype, rank, local_rank, world):
     from clusten import _lib, ops
     device = torch.device("cuda", local_rank)
@@ -431,7 +682,8 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         return t.item()
 
-    # ---- device-resident timing
+    # ---- device-resident timing: `reps` repetitions of exactly `steps` steps; the first repetition also
+    #      carries the per-kernel CUDA events of the library
     for _ in range(args.warmup):
         device_step(ops, wl)
     barrier()
@@ -440,17 +692,12 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
     _lib.timing_enable(True)
     _lib.timing_collect()
     launches0 = _lib.launch_count()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for _ in range(args.steps):
-        device_step(ops, wl)
-    stop.record()
-    barrier()
+    first = time_step_series(ops, wl, args.steps, 1, barrier, reduce_max)
     launches = _lib.launch_count() - launches0
     kernel_ms = _lib.timing_collect()
     _lib.timing_enable(False)
-    ms = reduce_max(start.elapsed_time(stop) / args.steps)
+    series = first + time_step_series(ops, wl, args.steps, max(0, args.reps - 1), barrier, reduce_max)
+    ms = statistics.median(series)
 
     # ---- end to end with host buffers
     e2e = EndToEnd(wl)
@@ -459,6 +706,7 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
     e2e.finish()
     barrier()
     e_steps = max(1, min(args.steps, 10))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(e_steps):
         e2e.step()
@@ -467,25 +715,75 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
     barrier()
     clocks = sampler.stop()
     e2e_ms = reduce_max(start.elapsed_time(stop) / e_steps)
+    e2e_h2d, e2e_d2h = e2e.h2d, e2e.d2h
+    del e2e
+    torch.cuda.empty_cache()
+
+    # ---- the same step in the other 16/32-bit type
+    other = torch.bfloat16 if dtype == torch.float32 else torch.float32
+    other_name = "bf16" if dtype == torch.float32 else "f32"
+    del wl
+    torch.cuda.empty_cache()
+    wl2 = make_workload(cfg, other, device, 1234 + rank)
+    for _ in range(max(3, args.warmup)):
+        device_step(ops, wl2)
+    _lib.timing_enable(True)
+    _lib.timing_collect()
+    o_first = time_step_series(ops, wl2, args.steps, 1, barrier, reduce_max)
+    o_kernel_ms = _lib.timing_collect()
+    _lib.timing_enable(False)
+    o_series = o_first + time_step_series(ops, wl2, args.steps, max(0, min(args.reps, 5) - 1), barrier, reduce_max)
+    o_esize = 6 - esize
+    o_total = sum(step_bytes(cfg, o_esize).values())
+    ref_ms = time_reference_cuda(wl2 if other == torch.float32 else None) if world == 1 else None
+    del wl2
+    torch.cuda.empty_cache()
+    if world == 1 and ref_ms is None and dtype == torch.float32:
+        wl = make_workload(cfg, dtype, device, 1234 + rank)
+        ref_ms = time_reference_cuda(wl)
+        del wl
+        torch.cuda.empty_cache()
+
+    model = None
+    if not args.no_model:
+        model = model_records(device, world, barrier, reduce_max, args.model_warmup, args.model_steps)
+    config2 = config0 = None
+    if world == 1 and rank == 0:
+        config2 = config2_records(device)
+        config0 = config0_record(device)
 
     if rank != 0:
         return
     peak, peak_kind = _peaks()
-    kb = kernel_bytes(cfg, esize)
-    # the library reports times per kernel name; split the names that serve several operators
-    per_kernel = {}
-    for name, (cnt, tot) in kernel_ms.items():
-        per_kernel[name] = {"launches": cnt, "ms_per_step": tot / args.steps}
+
+    def kernel_table(kms, es):
+        kb = kernel_bytes(cfg, es)
+        t = {}
+        for name, (cnt, tot) in kms.items():
+            t[name] = {"launches": cnt, "ms_per_step": tot / args.steps}
+            if name in kb:
+                t[name]["frac_of_hbm_peak"] = kb[name] / (tot / args.steps * 1e-3) / 1e9 / peak
+        return t, kb
+
+    per_kernel, kb = kernel_table(kernel_ms, esize)
     dominant = max(per_kernel, key=lambda k_: per_kernel[k_]["ms_per_step"]) if per_kernel else None
     roof = None
     if dominant is not None:
         dom_bytes = kb[dominant]
         dom_ms = per_kernel[dominant]["ms_per_step"]
         achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        traffic = NCU_DRAM_BYTES_PER_LAUNCH.get((dominant, args.dtype))
         roof = {"kernel": dominant, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((dominant, args.dtype)),
+                "traffic": traffic,
+                "traffic_source": (f"ncu capture at b=32 scaled x4, kernels of build {NCU_CAPTURE_BUILD}"
+                                   if traffic else None),
+                "limiter": "by the roofline model the kernel is HBM-bound; the ncu summaries in profiles/ name what "
+                           "actually limits it (instruction issue on index work where frac is low)",
                 "ms_per_step": dom_ms, "bytes_per_step": dom_bytes}
+    o_table, o_kb = kernel_table(o_kernel_ms, o_esize)
+    o_ms = statistics.median(o_series)
+    o_dom = max(o_table, key=lambda k_: o_table[k_]["ms_per_step"]) if o_table else None
     line = {
         "metric": "clusten_av_wf_fwd_bwd_algorithmic_bandwidth",
         "value": world * total_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
@@ -495,24 +793,48 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
         "config": {"workload": "config1: CLUSTENAV + CLUSTENWF(ic=4) forward+backward at stage-1 shapes, "
                                "inverse index rebuilt every step", **cfg,
                    "l2": "inputs larger than L2 (step touches > 1.5 GB)", "index_regime": "shared cluster rows"},
+        "repetitions": {"count": len(series), "steps_each": args.steps, "ms_per_step_median": ms,
+                        "ms_per_step_min": min(series), "ms_per_step_max": max(series)},
         "bytes_per_step": sbytes,
         "hbm_frac_of_step": total_bytes / (ms * 1e-3) / 1e9 / peak,
         "roofline": roof,
         "kernels": per_kernel,
         "e2e": {"value": world * total_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
-                "ms_per_step": e2e_ms, "h2d_bytes_per_step": e2e.h2d, "d2h_bytes_per_step": e2e.d2h},
+                "ms_per_step": e2e_ms, "h2d_bytes_per_step": e2e_h2d, "d2h_bytes_per_step": e2e_d2h,
+                "pcie_GBps_per_rank": (e2e_h2d + e2e_d2h) / (e2e_ms * 1e-3) / 1e9},
         "gpu_launches": launches * world,          # every rank launches the same kernels
         "clocks": clocks,
+        other_name: {"ms_per_step": o_ms, "value": world * o_total / (o_ms * 1e-3) / 1e9, "unit": "GB/s",
+                     "hbm_frac_of_step": o_total / (o_ms * 1e-3) / 1e9 / peak,
+                     "repetitions": len(o_series), "dominant_kernel": o_dom,
+                     "dominant_frac_of_hbm_peak": o_table[o_dom].get("frac_of_hbm_peak") if o_dom else None,
+                     "kernels": o_table},
     }
+    if model is not None:
+        line["model"] = model
+    if config2 is not None:
+        line["config2"] = config2
+    if config0 is not None:
+        line["config0"] = config0
     if world == 1:
-        line["cpu_baseline"] = {k: v for k, v in time_cpu(cfg, dtype, 3, 1).items() if k != "ms_per_step"}
-        ref_ms = time_reference_cuda(wl)
+        cpu = time_cpu(cfg, dtype, 3, 1)
+        line["cpu_baseline"] = {k: v for k, v in cpu.items() if k != "ms_per_step"}
+        line["cpu_baseline"]["full_batch"] = time_cpu_full_batch(cfg, dtype)
         if ref_ms is not None:
             line["reference_cuda_ext"] = {"ms_per_step": ref_ms,
                                           "value": total_bytes / (ref_ms * 1e-3) / 1e9, "unit": "GB/s",
                                           "note": "the reference's own kernels (oracle/_ref), same step "
                                                   "without an inverse index, fp32"}
     print(json.dumps(line), flush=True)
+
+
+def run_config2(args):
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peak, kind = _peaks()
+    print(json.dumps({"workload": "config2: per-stage chain QK -> +bias -> softmax -> AV, WF between stages",
+                      "batch": 256, "dtype": "bf16", "index_regime": "shared cluster rows",
+                      "peak": f"{peak} GB/s {kind}", "stages": config2_records(device)}), flush=True)
 
 
 def main():
@@ -523,6 +845,11 @@ def main():
     ap.add_argument("--dtype", choices=["fp32", "bf16"], default="fp32")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--ops", action="store_true", help="print the per-operator table instead")
+    ap.add_argument("--workload", choices=["config1", "config2"], default="config1")
+    ap.add_argument("--reps", type=int, default=9, help="repetitions of the timed loop (median reported)")
+    ap.add_argument("--no-model", action="store_true", help="skip the model-level images/sec legs")
+    ap.add_argument("--model-warmup", type=int, default=50)
+    ap.add_argument("--model-steps", type=int, default=30)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
@@ -536,6 +863,9 @@ def main():
         return
     if args.ops:
         per_operator_table()
+        return
+    if args.workload == "config2":
+        run_config2(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the operators have no CPU path)")

@@ -27,6 +27,8 @@ Configurations (BASELINE configs 3 and 4):
            (configs/aff_base_22kto1k_384.yaml:6-12), cluster 8, nbhd 48/48/48/49, ds_rate 1/5, 384 x 384
 """
 import importlib
+import importlib.machinery
+import importlib.util
 import os
 import sys
 import types
@@ -50,7 +52,21 @@ CONFIGS = {
 
 def available():
     """Is the reference's model bytecode there (oracle/build_ref.py has run)?"""
-    return os.path.exists(os.path.join(MODEL_DIR, "models", "aff_transformer.pyc"))
+    return os.path.exists(os.path.join(MODEL_DIR, "models", "aff_transformer.bytecode"))
+
+
+def _load_bytecode(name, path):
+    """Import the sourceless module stored at `path` (.pyc format) as `name`."""
+    loader = importlib.machinery.SourcelessFileLoader(name, path)
+    spec = importlib.util.spec_from_loader(name, loader, origin=path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    try:
+        loader.exec_module(mod)
+    except BaseException:
+        sys.modules.pop(name, None)
+        raise
+    return mod
 
 
 # ----------------------------------------------------------------------------- stand-ins
@@ -141,16 +157,14 @@ def _implementation(name, formula_chunk=8):
         # the reference's clusten/clusten.py (bytecode) on its own extension modules in oracle/_ref/
         if _REF not in sys.path:
             sys.path.insert(0, _REF)
-        spec = importlib.util.spec_from_file_location(
-            "ref_clusten_pkg", os.path.join(REF_CLUSTEN_DIR, "clusten", "clusten.pyc"))
-        mod = importlib.util.module_from_spec(spec)
-        spec.loader.exec_module(mod)
+        mod = sys.modules.get("reference_clusten_wrappers") or _load_bytecode(
+            "reference_clusten_wrappers", os.path.join(REF_CLUSTEN_DIR, "clusten", "clusten.bytecode"))
         return mod.CLUSTENQKFunction, mod.CLUSTENAVFunction, mod.CLUSTENWFFunction
     raise ValueError(name)
 
 
 def reference_kernels_available():
-    if not os.path.exists(os.path.join(REF_CLUSTEN_DIR, "clusten", "clusten.pyc")):
+    if not os.path.exists(os.path.join(REF_CLUSTEN_DIR, "clusten", "clusten.bytecode")):
         return False
     try:
         _implementation("reference")
@@ -171,12 +185,17 @@ def model_module():
                                "checkout of apple/ml-autofocusformer is present")
         _install_timm_standin()
         import clusten  # noqa: F401  this package's operators: what `from clusten import ...` in the model resolves to
-        if MODEL_DIR not in sys.path:
-            sys.path.insert(0, MODEL_DIR)
-        point_utils = importlib.import_module("models.point_utils")
+        # a package `models` holding exactly the two modules of the measured path
+        pkg_dir = os.path.join(MODEL_DIR, "models")
+        pkg = types.ModuleType("models")
+        pkg.__path__ = [pkg_dir]
+        sys.modules["models"] = pkg
+        point_utils = _load_bytecode("models.point_utils", os.path.join(pkg_dir, "point_utils.bytecode"))
         point_utils.knn_keops = knn
-        _aff = importlib.import_module("models.aff_transformer")
+        pkg.point_utils = point_utils
+        _aff = _load_bytecode("models.aff_transformer", os.path.join(pkg_dir, "aff_transformer.bytecode"))
         _aff.knn_keops = knn
+        pkg.aff_transformer = _aff
     return _aff
 
 

@@ -76,6 +76,7 @@ int resident_ctas(const void* kernel, int threads, size_t smem) {
     };
     static std::mutex mu;
     static std::map<Key, int> cache;
+    static std::map<std::pair<const void*, int>, size_t> limit;      // dynamic shared-memory limit set so far
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) {
         cudaGetLastError();
@@ -83,13 +84,18 @@ int resident_ctas(const void* kernel, int threads, size_t smem) {
     }
     const Key key{kernel, dev, smem, threads};
     std::lock_guard<std::mutex> lk(mu);
+    // the limit is one number per kernel and device: it is only ever raised, so that a launch with a
+    // smaller request does not take it away from a later launch with a larger one
+    size_t& cur = limit[{kernel, dev}];
+    if (smem > 48 * 1024 && smem > cur) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return CLUSTEN_ERR_CUDA;
+        }
+        cur = smem;
+    }
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
-    if (smem > 48 * 1024 &&
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return CLUSTEN_ERR_CUDA;
-    }
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) {
         cudaGetLastError();

@@ -52,12 +52,26 @@ __device__ __forceinline__ void st_vec(T* p, const Vec<T, V>& x) {
 //   rowptr  [b][n_targets + 1]    segment start of target t inside its batch element's entries
 //   seglen  [b][n_targets]        entries in the segment (<= rowptr[t+1]-rowptr[t])
 //   entries [b][n_rows * m]       row * m + slot of one (row, slot) with nbhd_idx == t.
+//   tileflag [b][1 + ceil(n_targets / 8)]   [0]: which build handled the batch element (kBuild*);
+//                                 [1 + i]: structure of the tile of targets 8i .. 8i+7 (kTile*)
+//   (n_targets > kInvSmemTargets only)  scratch [b][3 * n_targets]  counters of the build
 // A target that occurs several times in one row gets ONE entry, row * m with
 // kDupFlag set; the consumer then scans that row of nbhd_idx for all its
 // slots.  Segments are ordered by row, so every reduction order is fixed.
+//
+// Tile structures (recorded by the structured build, inverse_struct.cu; the general build writes
+// kTileGeneral everywhere):
+//   kTileRuns      the 8 targets are named by the same rows, once each, target q at slot j0 + q: their
+//                  segments have one length and entry k of target q is entry k of target 0 plus q
+//   kTileClusters  every segment consists of whole clusters: entries 8k .. 8k+7 are the rows 8c .. 8c+7
+//                  at one slot; no row names a target twice; at most kStructMaxPairs (cluster, slot)
+//                  pairs in the tile
 constexpr int kInvHeaderInts = 64;
 constexpr uint32_t kInvMagic = 0x434c5354u;
 constexpr uint32_t kDupFlag = 0x80000000u;
+constexpr int kBuildGeneral = 0, kBuildRuns = 1, kBuildClusters = 2;
+constexpr int kTileGeneral = 0, kTileRuns = 1, kTileClusters = 2;
+constexpr int kStructMaxPairs = 96;
 constexpr int kInvSmemTargets = 18000;       // up to here the build keeps its per-target counters in shared memory
 constexpr int kInvMaxTargets = 1 << 20;      // beyond kInvSmemTargets they live behind the entries, in the buffer itself
 
@@ -65,7 +79,11 @@ struct InverseView {
     const int* rowptr;    // [b][nt + 1]
     const int* seglen;    // [b][nt]
     const int* entries;   // [b][n_rows * m]
+    const int* tileflag;  // [b][1 + ntiles]
+    int ntiles;           // ceil(nt / 8)
 };
+
+__host__ __device__ inline int inverse_tiles(int nt) { return (nt + 7) / 8; }
 
 __host__ __device__ inline size_t inv_align(size_t x) { return (x + 63) & ~size_t(63); }
 
@@ -76,7 +94,8 @@ inline size_t inverse_scratch_ints(int b, int nt) {
 
 inline size_t inverse_ints(int b, int n_rows, int m, int nt) {
     return kInvHeaderInts + inv_align(size_t(b) * (nt + 1)) + inv_align(size_t(b) * nt) +
-           inv_align(size_t(b) * n_rows * m) + inverse_scratch_ints(b, nt);
+           inv_align(size_t(b) * n_rows * m) + inv_align(size_t(b) * (1 + inverse_tiles(nt))) +
+           inverse_scratch_ints(b, nt);
 }
 
 inline InverseView inverse_view(const void* buf, int b, int n_rows, int m, int nt) {
@@ -85,6 +104,8 @@ inline InverseView inverse_view(const void* buf, int b, int n_rows, int m, int n
     v.rowptr = p + kInvHeaderInts;
     v.seglen = v.rowptr + inv_align(size_t(b) * (nt + 1));
     v.entries = v.seglen + inv_align(size_t(b) * nt);
+    v.tileflag = v.entries + inv_align(size_t(b) * n_rows * m);
+    v.ntiles = inverse_tiles(nt);
     return v;
 }
 
@@ -141,5 +162,7 @@ int validate_av_backward(const void* d_feat, const void* attn, const void* value
 
 // inverse.cu
 int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s);
+// inverse_struct.cu: the build for cluster- and run-structured tables; runs first, marks what it handled
+int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s);
 
 }  // namespace clusten

@@ -21,7 +21,7 @@ template <int P>
 __global__ void __launch_bounds__(kThreads)
 inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int* __restrict__ header,
                      int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries,
-                     int* __restrict__ scratch) {
+                     int* __restrict__ scratch, int* __restrict__ tileflag, int ntiles) {
     extern __shared__ int sm[];
     // the three per-target arrays: in shared memory, or (more targets than fit there) in this batch
     // element's part of the global scratch; the block barriers below order the accesses either way
@@ -46,6 +46,11 @@ inverse_build_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt,
         header[2] = n_rows;
         header[3] = m;
         header[4] = nt;
+    }
+    {   // batch elements the structured build has done are skipped; the others have no structured tile
+        int* tf = tileflag + (long long)b * (1 + ntiles);
+        if (tf[0] != kBuildGeneral) return;
+        for (int t = tid; t < ntiles; t += kThreads) tf[1 + t] = kTileGeneral;
     }
     for (int t = tid; t < nt; t += kThreads) {
         base[t] = 0;
@@ -214,7 +219,8 @@ constexpr int kGroupRows = kWarps * kR;  // 128
 template <int P, bool M48>
 __global__ void __launch_bounds__(kThreads)
 inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, int nt, int* __restrict__ header,
-                        int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries) {
+                        int* __restrict__ rowptr, int* __restrict__ seglen, int* __restrict__ entries,
+                        int* __restrict__ tileflag, int ntiles) {
     const int m = M48 ? 48 : m_arg;
     extern __shared__ __align__(16) int sm128[];
     unsigned* mask = reinterpret_cast<unsigned*>(sm128);             // [nt][4] rows of the current group that hit t
@@ -232,6 +238,11 @@ inverse_build128_kernel(const int64_t* __restrict__ idx, int n_rows, int m_arg, 
         header[2] = n_rows;
         header[3] = m;
         header[4] = nt;
+    }
+    {
+        int* tf = tileflag + (long long)b * (1 + ntiles);
+        if (tf[0] != kBuildGeneral) return;
+        for (int t = tid; t < ntiles; t += kThreads) tf[1 + t] = kTileGeneral;
     }
     for (int t = tid; t < nt; t += kThreads) base[t] = 0;
     for (int t = tid; t < 4 * nt; t += kThreads) {
@@ -435,6 +446,11 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
         cudaGetLastError();
         return CLUSTEN_ERR_CUDA;
     }
+    // structured tables first; what that build did not take is done below
+    {
+        const int st = launch_inverse_struct(idx, b, n_rows, m, nt, buf, s);
+        if (st != CLUSTEN_OK) return st;
+    }
     if (m <= 64 && size_t(9) * nt * sizeof(int) <= 200 * 1024) {
         const size_t smem128 = size_t(9) * nt * sizeof(int);
         auto kernel128 = m == 48 ? inverse_build128_kernel<2, true>
@@ -443,20 +459,22 @@ int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, v
         if (fit < 0) return fit;
         ScopedKernelTimer timer("inverse_build", s);
         kernel128<<<b, kThreads, smem128, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
-                                               const_cast<int*>(v.seglen), const_cast<int*>(v.entries));
+                                               const_cast<int*>(v.seglen), const_cast<int*>(v.entries),
+                                               const_cast<int*>(v.tileflag), v.ntiles);
         note_launch();
         return check_launch();
     }
     int* scratch = nullptr;
     if (nt > kInvSmemTargets)
-        scratch = const_cast<int*>(v.entries) + inv_align(size_t(b) * n_rows * m);
+        scratch = const_cast<int*>(v.tileflag) + inv_align(size_t(b) * (1 + v.ntiles));
     const size_t smem = scratch ? 0 : size_t(3) * nt * sizeof(int);
     auto kernel = m <= 32 ? inverse_build_kernel<1> : (m <= 64 ? inverse_build_kernel<2> : inverse_build_kernel<0>);
     const int fit = resident_ctas(reinterpret_cast<const void*>(kernel), kThreads, smem);
     if (fit < 0) return fit;
     ScopedKernelTimer timer("inverse_build", s);
     kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, p, const_cast<int*>(v.rowptr),
-                                     const_cast<int*>(v.seglen), const_cast<int*>(v.entries), scratch);
+                                     const_cast<int*>(v.seglen), const_cast<int*>(v.entries), scratch,
+                                     const_cast<int*>(v.tileflag), v.ntiles);
     note_launch();
     return check_launch();
 }

@@ -1,0 +1,426 @@
+// Inverse neighbour index for STRUCTURED neighbour tables, 8 indices at a time.
+//
+// AutoFocusFormer's tables are never arbitrary.  Either the 8 tokens of a cluster share one row
+// ("clusters": rows 8c .. 8c+7 of nbhd_idx are identical), or every row is a concatenation of whole
+// clusters ("runs": each aligned group of 8 slots holds the tokens 8T .. 8T+7, which is what
+// models/aff_transformer.py:476-482 of the reference builds from models/point_utils.py:203-206).
+// In both cases the inverse of a batch element has an eighth of the degrees of freedom:
+//
+//   clusters   target t is named by (cluster c, slot j); its segment is the 8 rows of c, one after
+//              the other, for every such pair
+//   runs       target run T is named by (row i, run slot jr); the segments of its 8 targets list the
+//              same rows in the same order, target 8T+q at slot 8 jr + q
+//
+// One CTA per batch element checks which of the two holds (reading every index once), counts and places
+// the (c, j) or (i, jr) pairs with integer atomics in shared memory, sorts each short list (so that the
+// result does not depend on the order of the atomics) and expands it into the per-target segments of the
+// general format (common.cuh).  It also records, per tile of 8 targets, that the tile is structured,
+// which lets the scatter-side kernels skip their own analysis.  Batch elements that are neither (random
+// rows, out-of-range indices, padded tails) are left to the general build (inverse.cu).
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace clusten {
+namespace {
+
+constexpr int kThreads = 1024;
+constexpr int kWarps = kThreads / 32;
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kShortList = 24;           // lists up to this length are sorted by one thread
+constexpr int kQueue = 1024;             // longer lists wait here for a whole warp
+
+// exclusive scan of cnt[0..N) into out[0..N); returns the total in every thread.  All threads call it.
+__device__ int block_exclusive_scan(const int* cnt, int* out, int N, int* warp_tot) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = (N + kThreads - 1) / kThreads;
+    const int lo = min(tid * per, N), hi = min(lo + per, N);
+    int local = 0;
+    for (int t = lo; t < hi; ++t) local += cnt[t];
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(kFull, incl, o);
+        if (lane >= o) incl += y;
+    }
+    __syncthreads();                       // warp_tot may still be read from an earlier call
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int w = warp_tot[lane];
+        int wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, wi, o);
+            if (lane >= o) wi += y;
+        }
+        warp_tot[lane] = wi - w;
+        if (lane == 31) warp_tot[32] = wi;
+    }
+    __syncthreads();
+    int run = warp_tot[warp] + incl - local;
+    for (int t = lo; t < hi; ++t) {
+        const int c = cnt[t];
+        out[t] = run;
+        run += c;
+    }
+    const int total = warp_tot[32];
+    __syncthreads();
+    return total;
+}
+
+// ascending sort of a[0..L) by one warp, any L: the bitonic network in the form whose every
+// compare-exchange moves the smaller value to the lower position, so positions past L can stand for
+// +infinity and are simply never touched
+__device__ void warp_sort_smem(unsigned short* a, int L, int lane) {
+    int P = 2;
+    while (P < L) P <<= 1;
+    auto pass = [&](int mask_or_j, bool flip) {
+        for (int i = lane; i < P; i += 32) {
+            const int l = flip ? (i ^ mask_or_j) : (i ^ mask_or_j);
+            if (l > i && l < L) {
+                const unsigned short x = a[i], y = a[l];
+                if (x > y) {
+                    a[i] = y;
+                    a[l] = x;
+                }
+            }
+        }
+        __syncwarp();
+    };
+    for (int k = 2; k <= P; k <<= 1) {
+        pass(k - 1, true);                                 // partner: mirror image inside the block of k
+        for (int j = k >> 2; j > 0; j >>= 1) pass(j, false);
+    }
+}
+
+}  // namespace
+
+// P = passes of 32 slots over a row (m <= 32 P)
+template <int P>
+__global__ void __launch_bounds__(kThreads)
+inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int ntiles, int max_tile_pairs,
+                      int* __restrict__ header, int* __restrict__ rowptr, int* __restrict__ seglen,
+                      int* __restrict__ entries, int* __restrict__ tileflag) {
+    extern __shared__ __align__(16) int sm[];
+    int* cntS = sm;                                   // [nt]      pairs per target (clusters)
+    int* cntM = cntS + nt;                            // [ntiles]  pairs per target run (runs)
+    int* cur = cntM + ntiles;                         // [nt]      write cursor of the chosen kind
+    unsigned short* placed = reinterpret_cast<unsigned short*>(cur + nt);    // [n_rows * m / 8] the pairs, by target
+    __shared__ int warp_tot[kWarps + 1];
+    __shared__ int ok_clusters, ok_runs, q_len;
+    __shared__ int queue[kQueue];
+
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long E = (long long)n_rows * m;
+    const int64_t* ib = idx + (long long)b * E;
+    int* rp = rowptr + (long long)b * (nt + 1);
+    int* sl = seglen + (long long)b * nt;
+    int* ent = entries + (long long)b * E;
+    int* tf = tileflag + (long long)b * (1 + ntiles);
+    const int R = m >> 3;                             // run slots per row
+
+    if (b == 0 && tid == 0) {
+        header[0] = (int)kInvMagic;
+        header[1] = gridDim.x;
+        header[2] = n_rows;
+        header[3] = m;
+        header[4] = nt;
+    }
+    for (int t = tid; t < nt; t += kThreads) cntS[t] = 0;
+    for (int t = tid; t < ntiles; t += kThreads) cntM[t] = 0;
+    if (tid == 0) {
+        ok_clusters = (n_rows % 8 == 0) ? 1 : 0;
+        ok_runs = (m % 8 == 0) ? 1 : 0;
+        q_len = 0;
+    }
+    __syncthreads();
+
+    // ---- pass 1: every index once; which structure holds, and the counts of both
+    {
+        bool clusters = true, runs = true;
+        const int blocks = (n_rows + 7) >> 3;
+        for (int k = warp; k < blocks; k += kWarps) {
+            int v[8][P];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    const int j = lane + 32 * p, row = 8 * k + r;
+                    long long tk = -1;
+                    if (row < n_rows && j < m) tk = __ldg(ib + (long long)row * m + j);
+                    v[r][p] = (tk >= 0 && tk < nt) ? (int)tk : -1;
+                }
+            bool same = true, inrange = true;
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                const int j = lane + 32 * p;
+                if (j < m) {
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        if (8 * k + r < n_rows) {
+                            inrange = inrange && v[r][p] >= 0;
+                            same = same && v[r][p] == v[0][p];
+                        } else {
+                            same = false;
+                        }
+                    }
+                }
+            }
+            same = __all_sync(kFull, same && inrange);
+            inrange = __all_sync(kFull, inrange);
+            clusters = clusters && same;
+            runs = runs && inrange;
+            if (same) {
+#pragma unroll
+                for (int p = 0; p < P; ++p)
+                    if (lane + 32 * p < m) atomicAdd(&cntS[v[0][p]], 1);
+            }
+            if (inrange && (m & 7) == 0) {
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const int j = lane + 32 * p;
+                        const int v0 = __shfl_sync(kFull, v[r][p], lane & ~7);     // slot j & ~7 of the same pass
+                        if (j < m && 8 * k + r < n_rows) {
+                            const bool good = (v0 & 7) == 0 && v[r][p] == v0 + (lane & 7) && v0 + 7 < nt;
+                            runs = runs && good;
+                            if (good && (lane & 7) == 0) atomicAdd(&cntM[v0 >> 3], 1);
+                        }
+                    }
+            }
+        }
+        if (!__all_sync(kFull, clusters) && lane == 0) ok_clusters = 0;
+        if (!__all_sync(kFull, runs) && lane == 0) ok_runs = 0;
+    }
+    __syncthreads();
+    // codes of the pairs must fit in 16 bits
+    const bool fits = (long long)n_rows * m / 8 <= 65535;
+    const int mode = !fits ? kBuildGeneral : (ok_runs ? kBuildRuns : (ok_clusters ? kBuildClusters : kBuildGeneral));
+    if (mode == kBuildGeneral) {
+        if (tid == 0) tf[0] = kBuildGeneral;
+        return;
+    }
+
+    if (mode == kBuildClusters) {
+        // ---- clusters: cur = exclusive scan of cntS (in pairs; a pair is 8 entries)
+        const int total = block_exclusive_scan(cntS, cur, nt, warp_tot);
+        if (tid == 0) rp[nt] = 8 * total;
+        // ---- place the (cluster, slot) pairs: row 8k stands for its cluster
+        for (int k = warp; k < (n_rows >> 3); k += kWarps) {
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+                const int j = lane + 32 * p;
+                if (j < m) {
+                    const int t = (int)__ldg(ib + (long long)(8 * k) * m + j);
+                    const int pos = atomicAdd(&cur[t], 1);
+                    placed[pos] = (unsigned short)(k * m + j);
+                }
+            }
+        }
+        __syncthreads();
+        // ---- per target: sort its pairs, expand them into 8 entries each, flag its tile
+        const int nt32 = (nt + 31) & ~31;
+        for (int tb = warp * 32; tb < nt32; tb += kThreads) {
+            const int t = tb + lane;
+            const bool live = t < nt;
+            const int L = live ? cntS[t] : 0;
+            const int b0 = live ? cur[t] - L : 0;
+            bool plain = true;                        // no cluster names t twice, and the list was short
+            if (live) {
+                rp[t] = 8 * b0;
+                if (L > kShortList) {
+                    const int slot = atomicAdd(&q_len, 1);
+                    if (slot < kQueue) {
+                        queue[slot] = t;
+                        plain = false;
+                    }
+                }
+                if (plain) {
+                    unsigned short* a = placed + b0;
+                    for (int i = 1; i < L; ++i) {     // insertion sort
+                        const unsigned short x = a[i];
+                        int j = i - 1;
+                        while (j >= 0 && a[j] > x) {
+                            a[j + 1] = a[j];
+                            --j;
+                        }
+                        a[j + 1] = x;
+                    }
+                    int prev_c = -1;
+                    for (int i = 0; i < L; ++i) {
+                        const int c = a[i] / m;
+                        plain = plain && c != prev_c;
+                        prev_c = c;
+                    }
+                    int* dst = ent + 8 * b0;
+                    if (plain) {
+                        for (int i = 0; i < L; ++i) {
+                            const int code = a[i];
+                            const int c = code / m, j = code - c * m;
+                            const int e0 = 8 * c * m + j;
+                            *reinterpret_cast<int4*>(dst + 8 * i) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
+                            *reinterpret_cast<int4*>(dst + 8 * i + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
+                        }
+                        sl[t] = 8 * L;
+                    } else {
+                        // some cluster names t more than once: one flagged entry per row (the consumer rescans the row)
+                        int d = 0;
+                        prev_c = -1;
+                        for (int i = 0; i < L; ++i) {
+                            const int c = a[i] / m;
+                            if (c != prev_c) {
+                                for (int r = 0; r < 8; ++r) dst[8 * d + r] = (int)(kDupFlag | (unsigned)((8 * c + r) * m));
+                                ++d;
+                            }
+                            prev_c = c;
+                        }
+                        sl[t] = 8 * d;
+                    }
+                }
+            }
+            // tile of 8 targets = 8 neighbouring lanes
+            int pairs = L;
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) pairs += __shfl_xor_sync(kFull, pairs, o);
+            const unsigned good = __ballot_sync(kFull, plain && live);
+            const bool tile_ok = ((good >> (lane & ~7)) & 0xffu) == 0xffu && pairs <= max_tile_pairs;
+            if ((lane & 7) == 0 && t < nt) tf[1 + (t >> 3)] = tile_ok ? kTileClusters : kTileGeneral;
+        }
+        __syncthreads();
+        // ---- long lists, one warp each
+        const int nq = min(q_len, kQueue);
+        for (int qi = warp; qi < nq; qi += kWarps) {
+            const int t = queue[qi];
+            const int L = cntS[t], b0 = cur[t] - L;
+            unsigned short* a = placed + b0;
+            warp_sort_smem(a, L, lane);
+            int* dst = ent + 8 * b0;
+            bool dup = false;
+            for (int i = lane + 1; i < L; i += 32) dup = dup || (a[i] / m == a[i - 1] / m);
+            dup = __any_sync(kFull, dup);
+            if (!dup) {
+                for (int i = lane; i < L; i += 32) {
+                    const int code = a[i];
+                    const int c = code / m, j = code - c * m;
+                    const int e0 = 8 * c * m + j;
+                    *reinterpret_cast<int4*>(dst + 8 * i) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
+                    *reinterpret_cast<int4*>(dst + 8 * i + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
+                }
+                if (lane == 0) sl[t] = 8 * L;
+                continue;
+            }
+            // some cluster names t more than once: one flagged entry per row, distinct clusters in order
+            int d_base = 0;
+            for (int i0 = 0; i0 < L; i0 += 32) {
+                const int i = i0 + lane;
+                const int c = i < L ? a[i] / m : -1;
+                const int pc = (i > 0 && i < L) ? a[i - 1] / m : -1;
+                const bool first = i < L && c != pc;
+                const unsigned mk = __ballot_sync(kFull, first);
+                if (first) {
+                    const int d = d_base + __popc(mk & ((1u << lane) - 1u));
+                    for (int r = 0; r < 8; ++r) dst[8 * d + r] = (int)(kDupFlag | (unsigned)((8 * c + r) * m));
+                }
+                d_base += __popc(mk);
+            }
+            if (lane == 0) sl[t] = 8 * d_base;
+        }
+        if (tid == 0) tf[0] = kBuildClusters;
+        return;
+    }
+
+    // ---- runs: cur = exclusive scan of cntM (in pairs; a pair is one entry for each of the run's 8 targets)
+    const int total = block_exclusive_scan(cntM, cur, ntiles, warp_tot);
+    if (tid == 0) rp[nt] = 8 * total;
+    {
+        const int rows_per = 32 / R;                  // rows per warp and trip, R lanes each
+        const int sub = lane / R, jr = lane - sub * R;
+        const int trips = (n_rows + rows_per - 1) / rows_per;
+        for (int k = warp; k < trips; k += kWarps) {
+            const int row = k * rows_per + sub;
+            if (sub < rows_per && row < n_rows) {
+                const int T = (int)(__ldg(ib + (long long)row * m + 8 * jr) >> 3);
+                const int pos = atomicAdd(&cur[T], 1);
+                placed[pos] = (unsigned short)(row * R + jr);
+            }
+        }
+    }
+    __syncthreads();
+    for (int T = warp; T < ntiles; T += kWarps) {
+        const int L = cntM[T], b0 = cur[T] - L;
+        unsigned short* a = placed + b0;
+        if (L > 1) warp_sort_smem(a, L, lane);
+        // does a row name the run twice?
+        bool dup = false;
+        for (int i = lane + 1; i < L; i += 32) dup = dup || (a[i] / R == a[i - 1] / R);
+        dup = __any_sync(kFull, dup);
+        const int nq = min(8, nt - 8 * T);            // targets of this run that exist
+        if (!dup) {
+            for (int q = 0; q < nq; ++q) {
+                int* dst = ent + 8 * b0 + q * L;
+                for (int i = lane; i < L; i += 32) {
+                    const int code = a[i];
+                    const int row = code / R, r = code - row * R;
+                    dst[i] = row * m + 8 * r + q;
+                }
+                if (lane == 0) {
+                    rp[8 * T + q] = 8 * b0 + q * L;
+                    sl[8 * T + q] = L;
+                }
+            }
+        } else {
+            int d_base = 0;
+            for (int i0 = 0; i0 < L; i0 += 32) {
+                const int i = i0 + lane;
+                const int row = i < L ? a[i] / R : -1;
+                const int prow = (i > 0 && i < L) ? a[i - 1] / R : -1;
+                const bool first = i < L && row != prow;
+                const unsigned mk = __ballot_sync(kFull, first);
+                if (first) {
+                    const int d = d_base + __popc(mk & ((1u << lane) - 1u));
+                    for (int q = 0; q < nq; ++q) ent[8 * b0 + q * L + d] = (int)(kDupFlag | (unsigned)(row * m));
+                }
+                d_base += __popc(mk);
+            }
+            if (lane == 0)
+                for (int q = 0; q < nq; ++q) {
+                    rp[8 * T + q] = 8 * b0 + q * L;
+                    sl[8 * T + q] = d_base;
+                }
+        }
+        if (lane == 0) tf[1 + T] = (!dup && nq == 8) ? kTileRuns : kTileGeneral;
+    }
+    if (tid == 0) tf[0] = kBuildRuns;
+}
+
+// Launches the structured build for every batch element; tileflag[b][0] tells afterwards which elements
+// it handled.  Returns CLUSTEN_OK also when the sizes rule it out (the flags then say "general").
+int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s) {
+    int* p = static_cast<int*>(buf);
+    InverseView v = inverse_view(buf, b, n_rows, m, nt);
+    const int ntiles = inverse_tiles(nt);
+    int* tf = const_cast<int*>(v.tileflag);
+    const size_t smem = size_t(2 * nt + ntiles) * sizeof(int) + ((size_t(n_rows) * m / 8 + 1) & ~size_t(1)) * sizeof(unsigned short);
+    const bool possible = m <= 64 && smem <= 200 * 1024 && (long long)n_rows * m / 8 <= 65535 &&
+                          (m % 8 == 0 || n_rows % 8 == 0);
+    if (!possible) {
+        // every batch element and tile is "general"
+        if (cudaMemsetAsync(tf, 0, size_t(b) * (1 + ntiles) * sizeof(int), s) != cudaSuccess) {
+            cudaGetLastError();
+            return CLUSTEN_ERR_CUDA;
+        }
+        return CLUSTEN_OK;
+    }
+    auto kernel = m <= 32 ? inverse_struct_kernel<1> : inverse_struct_kernel<2>;
+    const int fit = resident_ctas(reinterpret_cast<const void*>(kernel), kThreads, smem);
+    if (fit < 0) return fit;
+    ScopedKernelTimer timer("inverse_build", s);
+    kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, ntiles, kStructMaxPairs, p, const_cast<int*>(v.rowptr),
+                                     const_cast<int*>(v.seglen), const_cast<int*>(v.entries), tf);
+    note_launch();
+    return check_launch();
+}
+
+}  // namespace clusten

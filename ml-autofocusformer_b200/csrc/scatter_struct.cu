@@ -1,0 +1,372 @@
+// Scatter-side gradients of QK / AV (d_key, d_value) on STRUCTURED tiles of the inverse index:
+//
+//   out[b, h, t, :] = sum over entries (i, j) of target t:  W[b, h, i, j] * X[b, h, i, :]        (head_dim 32)
+//
+// The inverse build marks the tiles of 8 consecutive targets whose segments have one of the two
+// shapes AutoFocusFormer's neighbour tables produce (common.cuh, kTileRuns / kTileClusters).  For such
+// a tile nothing has to be analysed per edge:
+//
+//   runs      the 8 targets are named by the same L rows, target q at slot j0 + q.  The source rows are
+//             the staged rows, and the 8 weights of a row are 8 neighbouring elements of W: one or
+//             two 16-byte copies per row fill the dense [L x 8] weight tile.
+//   clusters  every segment is made of whole clusters (8 rows 8c .. 8c+7 at one slot).  The (cluster,
+//             slot) pairs of the tile, at most 96, are de-duplicated by cluster (about ten distinct
+//             ones); each distinct cluster is staged as 8 consecutive rows (one contiguous kilobyte in
+//             fp32) and a pair contributes one column of 8 weights.
+//
+// Either way the product out[8 x 32] = Wd[8 x K] * X[K x 32] runs on the tensor cores, 48 staged rows
+// at a time (mma.sync: TF32 in three passes for FP32 inputs, m16n8k16 for FP16 / BF16), with a fixed
+// summation order.  Every warp works alone on one tile and all heads.  Tiles that are not marked are
+// left to scatter_tiles_kernel (tiled_fwd.cu).  The reference adds every (row, slot, channel) term
+// with atomicAdd (clusten/src/clustenqk_cuda_kernel.cu:117-127, clustenav_cuda_kernel.cu:113-123).
+#include "tile_core.cuh"
+
+namespace clusten {
+namespace {
+
+constexpr int kSR = 48;                  // staged rows per stage
+constexpr int kPairs = kStructMaxPairs;  // (cluster, slot) pairs of a clusters tile
+
+template <typename T> struct StructSmem {
+    static constexpr bool kIsFloat = std::is_same<T, float>::value;
+    static constexpr int kX = kSR * kC * (int)sizeof(T);      // staged rows; de-duplication scratch before that
+    static constexpr int kW = kSR * kT * (int)sizeof(T);      // dense weights [staged row][target]
+    static constexpr int kOut = kT * kOLD * 4;                // output tile
+    static constexpr int kSrc = kSR * 4;                      // runs: source row of each staged row
+    static constexpr int kWoff = kSR * 4;                     // runs: offset of the row's 8 weights
+    static constexpr int kCode = kPairs * 4;                  // clusters: offset of a pair's first weight
+    static constexpr int kSlotq = kPairs * 2;                 // clusters: slot of the pair's cluster | target << 12
+    static constexpr int kUniq = kPairs * 2;                  // clusters: slot -> cluster
+    static constexpr int kTotal = kX + kW + kOut + kSrc + kWoff + kCode + kSlotq + kUniq;
+};
+// scratch of dedup_tokens (tok, bm, pre, rowbm) lives in the row buffer while a tile is analysed
+static_assert(kPairs * 2 + kBMW * 4 + kBMW * 2 + 64 <= kSR * kC * 2, "de-duplication scratch must fit in the row buffer");
+
+struct StructParams {
+    const void* W;      // [batch][heads][n][m]
+    const void* X;      // [batch][heads][n][32]
+    void* out;          // [batch][heads][n][32]
+    InverseView inv;
+    int batch, heads, n, m, tiles;
+    unsigned m_magic, m_shift;
+};
+
+__device__ __forceinline__ unsigned struct_div(unsigned x, unsigned magic, unsigned shift) {
+    return (__umulhi(magic, x) + x) >> shift;
+}
+
+// D[ch][q] += sum_u Xs[u][ch] * Ws[u][q] over 8 * ksteps staged rows, FP32 inputs as three TF32 passes.
+// Xs rows are [32] floats with 16-byte chunk c of row r at c ^ ((r & 3) << 1); Ws is [row][8].
+struct StructAddr {
+    unsigned w;          // &Ws[t][g]
+    unsigned x[2][2];    // &Xs[t][16 mt + 8 h + g]
+};
+__device__ __forceinline__ StructAddr make_struct_addr(const float* Ws, const float* Xs, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    StructAddr a;
+    a.w = smem_u32(Ws + t * kT + g);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c = 16 * mt + 8 * h + g;
+            a.x[mt][h] = smem_u32(Xs + t * kC + ((((c >> 2) ^ (t << 1)) << 2) + (c & 3)));
+        }
+    return a;
+}
+template <int KS>
+__device__ __forceinline__ void struct_load(const StructAddr& sa, float (&b)[2], float (&a)[2][4]) {
+    asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(b[0]) : "r"(sa.w), "n"(KS * 8 * kT * 4));
+    asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(b[1]) : "r"(sa.w), "n"((KS * 8 + 4) * kT * 4));
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][0]) : "r"(sa.x[mt][0]), "n"(KS * 8 * kC * 4));
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][1]) : "r"(sa.x[mt][1]), "n"(KS * 8 * kC * 4));
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][2]) : "r"(sa.x[mt][0]), "n"((KS * 8 + 4) * kC * 4));
+        asm volatile("ld.shared.f32 %0, [%1+%2];\n" : "=f"(a[mt][3]) : "r"(sa.x[mt][1]), "n"((KS * 8 + 4) * kC * 4));
+    }
+}
+template <int KS>
+__device__ __forceinline__ void struct_steps(const StructAddr& sa, int ksteps, float (&acc)[2][4]) {
+    if constexpr (KS < kSR / 8) {
+        if (KS < ksteps) {
+            float b[2], a[2][4];
+            struct_load<KS>(sa, b, a);
+            mma_pair<true>(acc, a, b);
+            struct_steps<KS + 1>(sa, ksteps, acc);
+        }
+    }
+}
+
+// 16-bit inputs: Xraw rows [32] elements, 16-byte chunk c of row r at c ^ ((r >> 1) & 3) (swz16);
+// Ws16 is [row][8].  A = X^T through ldmatrix.trans, B = Ws16 through ldmatrix.trans (8 x 8 blocks of
+// [row][target] give the (k = row pair, n = target) fragment).
+template <typename T>
+__device__ __forceinline__ void struct_product16(const T* Xraw, const T* Ws16, int ksteps16, int lane, float (&acc)[2][4]) {
+    const int mi = lane >> 3, rr = lane & 7;
+    unsigned xa[2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) xa[mt] = smem_u32(Xraw + swz16((mi >> 1) * 8 + rr, 2 * mt + (mi & 1)));
+    // lanes 0..15 address rows 0..15 of the step (matrix 0: rows 0..7, matrix 1: rows 8..15)
+    const unsigned wa = smem_u32(Ws16 + (lane & 15) * kT);
+#pragma unroll
+    for (int ks = 0; ks < kSR / 16; ++ks) {
+        if (ks < ksteps16) {
+            unsigned b[2];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                         : "=r"(b[0]), "=r"(b[1]) : "r"(wa + ks * 16 * kT * 2));
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                unsigned a[4];
+                ldsm_x4_trans(a, xa[mt] + ks * 16 * kC * 2);
+                mma16(acc[mt], a, b, static_cast<const T*>(nullptr));
+            }
+        }
+    }
+}
+
+template <typename T, bool M48>
+__global__ void __launch_bounds__(32 * kWarps, 4)
+scatter_struct_kernel(const StructParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    using WS = StructSmem<T>;
+    constexpr bool kIsFloat = WS::kIsFloat;
+    constexpr int kPer = 16 / (int)sizeof(T);           // elements per 16-byte piece
+    constexpr int kLanesPerRow = kC / kPer;             // 8 (fp32) or 4 (16-bit)
+    constexpr int kRowsPerPass = 32 / kLanesPerRow;     // 4 or 8
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
+    T* Xs = reinterpret_cast<T*>(base);
+    T* Ws = reinterpret_cast<T*>(base + WS::kX);
+    float* Ot = reinterpret_cast<float*>(base + WS::kX + WS::kW);
+    int* src = reinterpret_cast<int*>(base + WS::kX + WS::kW + WS::kOut);
+    int* woff = src + kSR;
+    unsigned* code = reinterpret_cast<unsigned*>(woff + kSR);
+    unsigned short* slotq = reinterpret_cast<unsigned short*>(code + kPairs);
+    unsigned short* uniq = slotq + kPairs;
+    DedupScratch ds;
+    ds.tok = reinterpret_cast<unsigned short*>(base);
+    ds.bm = reinterpret_cast<unsigned*>(base + kPairs * 2);
+    ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
+    ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
+    ds.uniq = uniq;
+
+    const int m = M48 ? 48 : p.m, n = p.n, heads = p.heads;
+    auto div_m = [&](unsigned x) { return M48 ? x / 48u : struct_div(x, p.m_magic, p.m_shift); };
+    const T* Wg = static_cast<const T*>(p.W);
+    const T* Xg = static_cast<const T*>(p.X);
+    T* Og = static_cast<T*>(p.out);
+    const int pr = lane / kLanesPerRow, pc = lane % kLanesPerRow;       // staging: row within a pass, 16-byte piece
+    // chunk swizzle of staged row r (see the product routines)
+    auto xdst = [&](int r) {
+        if (kIsFloat) return Xs + r * kC + ((pc ^ ((r & 3) << 1)) << 2);
+        return Xs + swz16(r, pc);
+    };
+    StructAddr sa{};
+    if (kIsFloat) sa = make_struct_addr(reinterpret_cast<const float*>(Ws), reinterpret_cast<const float*>(Xs), lane);
+
+    const unsigned total = (unsigned)p.batch * (unsigned)p.tiles;
+    const unsigned nwarps = gridDim.x * kWarps;
+    for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
+        const int b = (int)(task / (unsigned)p.tiles);
+        const int tile = (int)(task - (unsigned)b * (unsigned)p.tiles);
+        const int kind = p.inv.tileflag[(long long)b * (1 + p.inv.ntiles) + 1 + tile];
+        if (kind == kTileGeneral) continue;
+        const int t0 = tile * kT;
+        const int* entries = p.inv.entries + (long long)b * n * m;
+        int len = 0, start = 0;
+        if (lane < kT) {
+            len = p.inv.seglen[(long long)b * n + t0 + lane];
+            start = p.inv.rowptr[(long long)b * (n + 1) + t0 + lane];
+        }
+        __syncwarp();
+
+        int L = 0, UC = 0;                 // runs: rows of the tile;  clusters: distinct clusters
+        int start0 = 0;
+        if (kind == kTileRuns) {
+            L = __shfl_sync(kFull, len, 0);
+            start0 = __shfl_sync(kFull, start, 0);
+        } else {
+            // ---- the tile's (cluster, slot) pairs: first entry of every group of 8
+            const int pairs = len >> 3;
+            int incl = pairs;
+#pragma unroll
+            for (int o = 1; o < kT; o <<= 1) {
+                const int y = __shfl_up_sync(kFull, incl, o);
+                if (lane >= o) incl += y;
+            }
+            const int CE = __shfl_sync(kFull, incl, kT - 1);
+            int lo = INT_MAX, hi = -1;
+            unsigned myq[(kPairs + 31) / 32];
+#pragma unroll
+            for (int i = 0; i < (kPairs + 31) / 32; ++i) {
+                const int x = lane + 32 * i;
+                int q = 0, off = 0, st = __shfl_sync(kFull, start, 0);
+#pragma unroll
+                for (int j = 1; j < kT; ++j) {
+                    const int oj = __shfl_sync(kFull, incl - pairs, j);
+                    const int sj = __shfl_sync(kFull, start, j);
+                    if (x >= oj) {
+                        q = j;
+                        off = oj;
+                        st = sj;
+                    }
+                }
+                myq[i] = (unsigned)q;
+                if (x < CE) {
+                    const unsigned e = (unsigned)__ldg(entries + st + 8 * (x - off));
+                    const int c = (int)(div_m(e) >> 3);
+                    code[x] = e;
+                    ds.tok[x] = (unsigned short)c;
+                    lo = min(lo, c);
+                    hi = max(hi, c);
+                }
+            }
+            bool unused = false;
+            unsigned short* slots = slotq;                // slot first, the target is merged in below
+            UC = CE > 0 ? dedup_tokens(ds, slots, CE, m, false, &unused, lane, lo, hi) : 0;
+#pragma unroll
+            for (int i = 0; i < (kPairs + 31) / 32; ++i) {
+                const int x = lane + 32 * i;
+                if (x < CE) slotq[x] = (unsigned short)(slotq[x] | (myq[i] << 12));
+            }
+            L = CE;
+            __syncwarp();
+        }
+
+        const int nstages = kind == kTileRuns ? (L + kSR - 1) / kSR : (UC + 5) / 6;
+        for (int g = 0; g < heads; ++g) {
+            const long long bh = (long long)b * heads + g;
+            const T* Wh = Wg + bh * n * m;
+            const T* Xh = Xg + bh * n * kC;
+            float acc[2][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
+            for (int s = 0; s < nstages; ++s) {
+                int rows;                                  // staged rows of this stage
+                __syncwarp();
+                if (kind == kTileRuns) {
+                    const int k0 = s * kSR;
+                    rows = min(kSR, L - k0);
+                    if (g == 0 || nstages > 1) {
+                        // source row and weight offset of every staged row
+                        for (int u = lane; u < rows; u += 32) {
+                            const unsigned e = (unsigned)__ldg(entries + start0 + k0 + u);
+                            src[u] = (int)div_m(e);
+                            woff[u] = (int)e;
+                        }
+                        __syncwarp();
+                    }
+                } else {
+                    rows = 8 * min(6, UC - 6 * s);
+                }
+                const int rows_pad = kIsFloat ? ((rows + 7) & ~7) : ((rows + 15) & ~15);
+                // ---- rows -> Xs
+#pragma unroll
+                for (int k = 0; k < kSR / kRowsPerPass; ++k) {
+                    const int r = pr + kRowsPerPass * k;
+                    if (r < rows_pad) {
+                        T* dst = xdst(r);
+                        if (r < rows) {
+                            const int row = kind == kTileRuns ? src[r] : (int)uniq[6 * s + (r >> 3)] * 8 + (r & 7);
+                            cp_async16_cg(dst, Xh + (long long)row * kC + pc * kPer);
+                        } else {
+                            *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+                }
+                // ---- weights -> Ws[row][target]
+                if (kind == kTileRuns) {
+                    constexpr int kPieces = kT / kPer;      // 16-byte pieces per row of 8 weights: 2 or 1
+                    for (int z = lane; z < rows_pad * kPieces; z += 32) {
+                        const int u = z / kPieces, piece = z % kPieces;
+                        T* dst = Ws + u * kT + piece * kPer;
+                        if (u < rows) cp_async16_ca(dst, Wh + woff[u] + piece * kPer);
+                        else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                } else {
+                    for (int z = lane; z < rows_pad * kT * (int)sizeof(T) / 16; z += 32)
+                        reinterpret_cast<float4*>(Ws)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    __syncwarp();
+                    const int xs = lane >> 3, r = lane & 7;
+                    for (int x = xs; x < L; x += 4) {
+                        const unsigned sq = slotq[x];
+                        const int rel = (int)(sq & 0xfffu) - 6 * s;
+                        if (rel >= 0 && rel < 6) {
+                            const T* wsrc = Wh + code[x] + r * m;
+                            T* dst = Ws + (rel * 8 + r) * kT + (sq >> 12);
+                            if (kIsFloat) cp_async4_ca(dst, wsrc);
+                            else *dst = *wsrc;
+                        }
+                    }
+                }
+                cp_async_commit();
+                cp_async_wait<0>();
+                __syncwarp();
+                if (kIsFloat) struct_steps<0>(sa, rows_pad >> 3, acc);
+                else struct_product16<T>(Xs, Ws, rows_pad >> 4, lane, acc);
+            }
+            // ---- D fragments -> output tile -> 16-byte stores
+            {
+                const int gg = lane >> 2, tt = lane & 3;
+                __syncwarp();
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    float* o = Ot + (2 * tt) * kOLD + 16 * mt + gg;
+                    o[0] = acc[mt][0];
+                    o[kOLD] = acc[mt][1];
+                    o[8] = acc[mt][2];
+                    o[kOLD + 8] = acc[mt][3];
+                }
+                __syncwarp();
+                const int qi = lane >> 3, ci = lane & 7;
+                T* Oh = Og + bh * n * kC;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    const int q = 2 * qi + a;
+                    st4(Oh + (long long)(t0 + q) * kC + ci * 4, *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4));
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+int scatter_struct_t(const char* label, StructParams p, cudaStream_t s) {
+    const size_t smem = size_t(kWarps) * StructSmem<T>::kTotal;
+    auto kernel = p.m == 48 ? scatter_struct_kernel<T, true> : scatter_struct_kernel<T, false>;
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kWarps, smem);
+    if (per_sm < 0) return per_sm;
+    long long grid = (long long)sm_count() * per_sm;
+    const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
+    if (grid > need) grid = need;
+    ScopedKernelTimer timer(label, s);
+    kernel<<<(int)grid, 32 * kWarps, smem, s>>>(p);
+    note_launch();
+    return check_launch();
+}
+
+}  // namespace
+
+// Structured tiles of d_key / d_value; the other tiles are scatter_tiles_kernel's (launch_tiled_scatter).
+int launch_struct_scatter(const char* label, int dtype, const void* W, const void* X, const InverseView& inv, void* out,
+                          int b, int h, int n, int m, cudaStream_t s) {
+    StructParams p{};
+    p.W = W;  p.X = X;  p.out = out;  p.inv = inv;
+    p.batch = b;  p.heads = h;  p.n = n;  p.m = m;  p.tiles = (n + kT - 1) / kT;
+    if ((long long)b * p.tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    {
+        unsigned l = 0;
+        while ((1ull << l) < (unsigned)m) ++l;
+        p.m_magic = (unsigned)(((1ull << 32) * ((1ull << l) - (unsigned)m)) / (unsigned)m + 1);
+        p.m_shift = l;
+    }
+    switch (dtype) {
+        case CLUSTEN_F32: return scatter_struct_t<float>(label, p, s);
+        case CLUSTEN_F16: return scatter_struct_t<__half>(label, p, s);
+        case CLUSTEN_BF16: return scatter_struct_t<__nv_bfloat16>(label, p, s);
+        default: return CLUSTEN_ERR_DTYPE;
+    }
+}
+
+}  // namespace clusten

@@ -19,6 +19,10 @@ bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void
 int launch_tiled_scatter(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
                          void* out, int b, int h, int n, int m, cudaStream_t s);
 
+// the structured tiles of the same reduction (scatter_struct.cu); launch_tiled_scatter calls it first
+int launch_struct_scatter(const char* label, int dtype, const void* W, const void* X, const InverseView& inv, void* out,
+                          int b, int h, int n, int m, cudaStream_t s);
+
 // scatter-sum for WF:  out[b,t,:] = sum_{idx[b,i,j]==t} sum_k W[b,i,j,k] * X[b,i,k,:]   (d_feat)
 bool tiled_wf_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n_out, int n, int m,
                                 int ic, int c);

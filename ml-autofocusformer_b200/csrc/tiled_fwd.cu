@@ -406,6 +406,7 @@ struct ScatterParams {
     const int64_t* idx;  int idx_rows;  int m;                   // nbhd_idx [batch][idx_rows][m]
     InverseView inv;  int n_tgt;
     int ic, heads, batch, tiles;
+    int skip_flagged;                                           // tiles the inverse build marked as structured are done elsewhere
     int w_pairs;                                                // W may be read in aligned 32-bit words
     unsigned m_magic, m_shift, ic_magic, ic_shift;              // x / d = (umulhi(magic, x) + x) >> shift
 };
@@ -490,6 +491,9 @@ scatter_tiles_kernel(const ScatterParams p) {
         const int* entries = p.inv.entries + (long long)b * p.idx_rows * m;
         const int len = next_len, start = next_start;
         load_segment(task + nwarps, next_len, next_start);      // in flight while this tile is worked on
+        if (p.skip_flagged &&
+            p.inv.tileflag[(long long)b * (1 + p.inv.ntiles) + 1 + (t0 >> 3)] != kTileGeneral)
+            continue;                                           // scatter_struct_kernel has this tile
         const int qlen = __shfl_sync(kFull, len, myq);          // entries of this lane's target
         const int* qent = entries + __shfl_sync(kFull, start, myq);
         int maxlen = len;
@@ -976,6 +980,13 @@ int launch_tiled_scatter(const char* label, int dtype, const void* W, const void
     p.out = out;  p.o_batch = p.x_batch;  p.o_head = p.x_head;  p.o_row = kC;
     p.idx = idx;  p.idx_rows = n;  p.m = m;  p.inv = inv;  p.n_tgt = n;
     p.ic = 1;  p.heads = h;  p.batch = b;
+    // tiles whose structure the inverse build recorded go to the lean kernel, the others to the general one
+    const bool lean = reinterpret_cast<uintptr_t>(W) % 16 == 0;
+    if (lean) {
+        const int st = launch_struct_scatter(label, dtype, W, X, inv, out, b, h, n, m, s);
+        if (st != CLUSTEN_OK) return st;
+    }
+    p.skip_flagged = lean ? 1 : 0;
     return scatter_dispatch(label, dtype, p, s);
 }
 

@@ -8,12 +8,14 @@ read-only checkout of apple/ml-autofocusformer, nothing of it is copied as sourc
   * the three extension modules `clustenqk_cuda`, `clustenav_cuda`, `clustenwf_cuda`:
     the reference's own kernels (clusten/src/*.cu, *.cpp) compiled for sm_100a.  They
     check the oracle and the parity tests and serve as a speed bar in the benchmark.
-  * Python bytecode (.pyc) of the modules that CALL the operators: models/aff_transformer.py
-    and models/point_utils.py (the AutoFocusFormer model, the caller of this repository's
-    `clusten` package in the model-level benchmark) and clusten/clusten.py + clusten/__init__.py
-    (the reference's autograd wrappers, so that the same model can also run on the
-    reference's kernels).  They land in oracle/_ref/aff_model/models/ and
-    oracle/_ref/ref_clusten/clusten/ and are imported as sourceless modules.
+  * Python bytecode of the modules that CALL the operators: models/aff_transformer.py and
+    models/point_utils.py (the AutoFocusFormer model, the caller of this repository's `clusten`
+    package in the model-level benchmark) and clusten/clusten.py (the reference's autograd
+    wrappers, so that the same model can also run on the reference's kernels).  They land in
+    oracle/_ref/aff_model/models/ and oracle/_ref/ref_clusten/clusten/ as `.bytecode` files
+    (the .pyc format under a name that file filters for Python caches leave alone) and are
+    loaded as sourceless modules.  The upstream models/__init__.py is left out: it imports the
+    training-side builder (models/__init__.py:8), which is not on the measured path.
 
 nvcc / g++ / py_compile read the sources where they lie and only objects, shared
 objects and bytecode are written (all below oracle/_ref/, which is git-ignored).  The
@@ -39,10 +41,9 @@ OUT = os.path.join(HERE, "_ref")
 MODULES = ("clustenqk_cuda", "clustenav_cuda", "clustenwf_cuda")
 # (source inside the checkout, bytecode below oracle/_ref/)
 BYTECODE = (
-    ("models/aff_transformer.py", "aff_model/models/aff_transformer.pyc"),
-    ("models/point_utils.py", "aff_model/models/point_utils.pyc"),
-    ("clusten/clusten.py", "ref_clusten/clusten/clusten.pyc"),
-    ("clusten/__init__.py", "ref_clusten/clusten/__init__.pyc"),
+    ("models/aff_transformer.py", "aff_model/models/aff_transformer.bytecode"),
+    ("models/point_utils.py", "aff_model/models/point_utils.bytecode"),
+    ("clusten/clusten.py", "ref_clusten/clusten/clusten.bytecode"),
 )
 
 
@@ -57,7 +58,7 @@ def reference_root(arg=None):
 
 
 def byte_compile(root, force=False):
-    """models/*.py and clusten/*.py of the checkout -> sourceless .pyc below oracle/_ref/."""
+    """models/*.py and clusten/clusten.py of the checkout -> sourceless bytecode below oracle/_ref/."""
     for src_rel, dst_rel in BYTECODE:
         src, dst = os.path.join(root, src_rel), os.path.join(OUT, dst_rel)
         if not os.path.exists(src):
@@ -66,11 +67,6 @@ def byte_compile(root, force=False):
             os.makedirs(os.path.dirname(dst), exist_ok=True)
             py_compile.compile(src, cfile=dst, dfile=src_rel, doraise=True)
             print("byte-compiled", src_rel, "->", dst, flush=True)
-    # the model package gets an empty __init__ of its own: the upstream one imports the
-    # training-side builder (models/__init__.py:8), which is not part of the measured path
-    init = os.path.join(OUT, "aff_model", "models", "__init__.py")
-    if os.path.isdir(os.path.dirname(init)) and not os.path.exists(init):
-        open(init, "w").close()
 
 
 def _run(cmd):
