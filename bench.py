@@ -766,7 +766,8 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
         return t, kb
 
     per_kernel, kb = kernel_table(kernel_ms, esize)
-    dominant = max(per_kernel, key=lambda k_: per_kernel[k_]["ms_per_step"]) if per_kernel else None
+    known = [k_ for k_ in per_kernel if k_ in kb]
+    dominant = max(known, key=lambda k_: per_kernel[k_]["ms_per_step"]) if known else None
     roof = None
     if dominant is not None:
         dom_bytes = kb[dominant]
@@ -783,7 +784,8 @@ def run_b200_arm(args, dtype, rank, local_rank, world):
                 "ms_per_step": dom_ms, "bytes_per_step": dom_bytes}
     o_table, o_kb = kernel_table(o_kernel_ms, o_esize)
     o_ms = statistics.median(o_series)
-    o_dom = max(o_table, key=lambda k_: o_table[k_]["ms_per_step"]) if o_table else None
+    o_known = [k_ for k_ in o_table if k_ in o_kb]
+    o_dom = max(o_known, key=lambda k_: o_table[k_]["ms_per_step"]) if o_known else None
     line = {
         "metric": "clusten_av_wf_fwd_bwd_algorithmic_bandwidth",
         "value": world * total_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,

@@ -188,6 +188,19 @@ CLUSTEN_API int clusten_wf_backward(const void* d_feat_new, const void* weights,
                         void* d_weights, void* d_feat,
                         int b, int n_out, int n, int m, int ic, int c, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Neighbourhood search on 2-D token positions: nn_idx[b,i,:] = the k database
+ * points nearest to query[b,i] by Euclidean distance, ascending, ties towards
+ * the lower index; nn_dist (may be NULL) receives the distances.
+ * replaces knn_keops (models/point_utils.py:27-58; callers
+ * models/aff_transformer.py:298 with k = 2 and :476 with k = 6), which the
+ * reference evaluates with a pykeops LazyTensor argKmin.  fp32 positions
+ * [b, n_query, 2] and [b, n, 2], int64 indices [b, n_query, k] like the
+ * reference's.  Limits: k <= 8, k <= n, b <= 65535 (CLUSTEN_ERR_UNSUPPORTED).
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API int clusten_knn2d(const float* query, const float* database, int b, int n_query, int n, int k,
+                              int64_t* nn_idx, float* nn_dist, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -11,8 +11,9 @@ things the file needs that are not in this environment:
     training, zeroes whole samples with probability p and rescales the rest by 1 / (1 - p);
     trunc_normal_ is torch.nn.init.trunc_normal_.
   * `knn_keops` (models/point_utils.py:27-58; pykeops is not installed): the k nearest
-    database points of every query by exact Euclidean distance, ascending, computed with
-    torch.cdist + topk.  Tie-breaking of the original is not pinned by any reference test.
+    database points of every query by exact Euclidean distance, ascending: on the GPU the
+    library's clusten_knn2d kernel, on the CPU torch.cdist + topk.  Tie-breaking of the
+    original is not pinned by any reference test.
   * the `clusten` package: this repository's operators ("b200"), the PyTorch gather
     formulation of the reference's kernel tests ("formula", the parity checker), or the
     reference's own wrappers on its own CUDA kernels ("reference", the speed bar).
@@ -110,6 +111,11 @@ def knn(query, database, k, return_dist=False, chunk_elems=1 << 28):
     with torch.no_grad():
         q = query.detach().float()
         d = database.detach().float()
+        if q.is_cuda and q.shape[2] == 2 and k <= 8 and k <= d.shape[1] and q.shape[0] <= 65535:
+            # on the GPU the search is the library's kernel (clusten_knn2d): same definition, ties towards the
+            # lower index
+            from clusten import ops
+            return ops.knn2d(q.contiguous(), d.contiguous(), k, return_dist)
         b, nq, _ = q.shape
         n = d.shape[1]
         step = max(1, min(b, chunk_elems // max(1, nq * n)))

@@ -154,6 +154,24 @@ def _order_ptr(row_order, nbhd_idx):
     return row_order, row_order.data_ptr()
 
 
+# ----------------------------------------------------------------------------- neighbourhood search
+def knn2d(query, database, k, return_dist=False):
+    """Indices [b, n_query, k] (int64) of the k database points nearest to every query, ascending distance,
+    ties towards the lower index; 2-D fp32 positions [b, n_query, 2] and [b, n, 2]."""
+    _chk("query", query, torch.float32, 3)
+    _chk("database", database, torch.float32, 3)
+    b, nq, d = query.shape
+    if d != 2 or database.shape[0] != b or database.shape[2] != 2:
+        raise RuntimeError("clusten: knn2d needs [b, n, 2] positions")
+    n = database.shape[1]
+    nn_idx = torch.empty((b, nq, k), dtype=torch.int64, device=query.device)
+    nn_dist = torch.empty((b, nq, k), dtype=torch.float32, device=query.device) if return_dist else None
+    with torch.cuda.device_of(query):
+        _lib.check(_lib.load().clusten_knn2d(query.data_ptr(), database.data_ptr(), b, nq, n, k, nn_idx.data_ptr(),
+                                             nn_dist.data_ptr() if return_dist else None, _stream(query)))
+    return (nn_idx, nn_dist) if return_dist else nn_idx
+
+
 # ----------------------------------------------------------------------------- QK
 def qk_forward(query, key, nbhd_idx):
     """attn[b,h,i,j] = <query[b,h,i], key[b,h,nbhd_idx[b,i,j]]>"""

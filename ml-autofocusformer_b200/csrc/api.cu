@@ -3,6 +3,7 @@
 // the reference interfaces they replace are in include/clusten_b200.h.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -46,6 +47,14 @@ ScopedKernelTimer::~ScopedKernelTimer() {
     if (slot < 0) return;
     std::lock_guard<std::mutex> lk(g_timing_mu);
     cudaEventRecord(g_timed[slot].stop, stream);
+}
+
+bool split_timing_labels() {
+    static const bool on = [] {
+        const char* v = getenv("CLUSTEN_SPLIT_TIMING");
+        return v != nullptr && v[0] == '1';
+    }();
+    return on;
 }
 
 int check_launch() { return cudaGetLastError() == cudaSuccess ? CLUSTEN_OK : CLUSTEN_ERR_CUDA; }
@@ -324,6 +333,17 @@ int clusten_av_backward(const void* d_feat, const void* attn, const void* value,
     if (tiled_scatter_supported(dtype, attn, d_feat, d_value, n, m, c))
         return launch_tiled_scatter("av_d_value", dtype, attn, d_feat, nbhd_idx, inv, d_value, b, h, n, m, s);
     return launch_scatter_sum("av_d_value", dtype, attn, d_feat, nbhd_idx, inv, d_value, b * h, h, n, n, m, 1, c, s);
+}
+
+int clusten_knn2d(const float* query, const float* database, int b, int n_query, int n, int k, int64_t* nn_idx,
+                  float* nn_dist, void* stream) {
+    if (b <= 0 || n_query <= 0 || n <= 0 || k <= 0) return CLUSTEN_ERR_SHAPE;
+    if (k > 8 || k > n || b > 65535) return CLUSTEN_ERR_UNSUPPORTED;
+    CLUSTEN_REQUIRE_PTR(query, 8);
+    CLUSTEN_REQUIRE_PTR(database, 8);
+    CLUSTEN_REQUIRE_PTR(nn_idx, 8);
+    if (nn_dist && !aligned(nn_dist, 4)) return CLUSTEN_ERR_ALIGN;
+    return launch_knn2d(query, database, b, n_query, n, k, nn_idx, nn_dist, (cudaStream_t)stream);
 }
 
 size_t clusten_wf_order_bytes(int b, int n_out) {

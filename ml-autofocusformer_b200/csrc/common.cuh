@@ -120,6 +120,9 @@ struct ScopedKernelTimer {
     cudaStream_t stream;
 };
 int check_launch();               // cudaGetLastError -> CLUSTEN_OK / CLUSTEN_ERR_CUDA
+// CLUSTEN_SPLIT_TIMING=1 in the environment: kernels that share an operator's timing label (the structured
+// and the general part of one reduction) are timed under names of their own
+bool split_timing_labels();
 int sm_count();                   // multiprocessors of the current device (cached per device)
 // One-time set-up of a kernel on the current device: raises its dynamic shared-memory limit to
 // smem bytes and returns how many CTAs of `threads` threads fit on one multiprocessor (>= 1), or a
@@ -159,6 +162,10 @@ int launch_scatter_sum(const char* label, int dtype, const void* W, const void* 
 int validate_av_backward(const void* d_feat, const void* attn, const void* value, const int64_t* nbhd_idx,
                          const void* inverse, const void* d_attn, const void* d_value, int b, int h, int n, int m,
                          int c, int dtype);
+
+// knn.cu
+int launch_knn2d(const float* query, const float* db, int b, int nq, int n, int k, int64_t* idx_out, float* dist_out,
+                 cudaStream_t s);
 
 // inverse.cu
 int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s);

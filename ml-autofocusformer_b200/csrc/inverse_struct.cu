@@ -248,36 +248,26 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
                         }
                         a[j + 1] = x;
                     }
-                    int prev_c = -1;
-                    for (int i = 0; i < L; ++i) {
-                        const int c = a[i] / m;
-                        plain = plain && c != prev_c;
-                        prev_c = c;
-                    }
+                    // one group of entries per distinct cluster: its 8 rows at the pair's slot, or, when the
+                    // cluster names t more than once, one flagged entry per row (the consumer rescans the row)
                     int* dst = ent + 8 * b0;
-                    if (plain) {
-                        for (int i = 0; i < L; ++i) {
-                            const int code = a[i];
-                            const int c = code / m, j = code - c * m;
-                            const int e0 = 8 * c * m + j;
-                            *reinterpret_cast<int4*>(dst + 8 * i) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
-                            *reinterpret_cast<int4*>(dst + 8 * i + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
+                    int d = 0;
+                    for (int i = 0; i < L;) {
+                        const int code = a[i];
+                        const int c = code / m, j = code - c * m;
+                        int i2 = i + 1;
+                        while (i2 < L && a[i2] / m == c) ++i2;
+                        int e0 = 8 * c * m + j, step = m;
+                        if (i2 - i > 1) {
+                            e0 = (int)(kDupFlag | (unsigned)(8 * c * m));
+                            plain = false;
                         }
-                        sl[t] = 8 * L;
-                    } else {
-                        // some cluster names t more than once: one flagged entry per row (the consumer rescans the row)
-                        int d = 0;
-                        prev_c = -1;
-                        for (int i = 0; i < L; ++i) {
-                            const int c = a[i] / m;
-                            if (c != prev_c) {
-                                for (int r = 0; r < 8; ++r) dst[8 * d + r] = (int)(kDupFlag | (unsigned)((8 * c + r) * m));
-                                ++d;
-                            }
-                            prev_c = c;
-                        }
-                        sl[t] = 8 * d;
+                        *reinterpret_cast<int4*>(dst + 8 * d) = make_int4(e0, e0 + step, e0 + 2 * step, e0 + 3 * step);
+                        *reinterpret_cast<int4*>(dst + 8 * d + 4) = make_int4(e0 + 4 * step, e0 + 5 * step, e0 + 6 * step, e0 + 7 * step);
+                        ++d;
+                        i = i2;
                     }
+                    sl[t] = 8 * d;
                 }
             }
             // tile of 8 targets = 8 neighbouring lanes
@@ -297,31 +287,21 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
             unsigned short* a = placed + b0;
             warp_sort_smem(a, L, lane);
             int* dst = ent + 8 * b0;
-            bool dup = false;
-            for (int i = lane + 1; i < L; i += 32) dup = dup || (a[i] / m == a[i - 1] / m);
-            dup = __any_sync(kFull, dup);
-            if (!dup) {
-                for (int i = lane; i < L; i += 32) {
-                    const int code = a[i];
-                    const int c = code / m, j = code - c * m;
-                    const int e0 = 8 * c * m + j;
-                    *reinterpret_cast<int4*>(dst + 8 * i) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
-                    *reinterpret_cast<int4*>(dst + 8 * i + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
-                }
-                if (lane == 0) sl[t] = 8 * L;
-                continue;
-            }
-            // some cluster names t more than once: one flagged entry per row, distinct clusters in order
             int d_base = 0;
             for (int i0 = 0; i0 < L; i0 += 32) {
                 const int i = i0 + lane;
-                const int c = i < L ? a[i] / m : -1;
+                const int code = i < L ? a[i] : 0;
+                const int c = i < L ? code / m : -1;
                 const int pc = (i > 0 && i < L) ? a[i - 1] / m : -1;
+                const int nc = i + 1 < L ? a[i + 1] / m : -2;
                 const bool first = i < L && c != pc;
                 const unsigned mk = __ballot_sync(kFull, first);
                 if (first) {
                     const int d = d_base + __popc(mk & ((1u << lane) - 1u));
-                    for (int r = 0; r < 8; ++r) dst[8 * d + r] = (int)(kDupFlag | (unsigned)((8 * c + r) * m));
+                    int e0 = 8 * c * m + (code - c * m);
+                    if (nc == c) e0 = (int)(kDupFlag | (unsigned)(8 * c * m));      // named more than once: flagged rows
+                    *reinterpret_cast<int4*>(dst + 8 * d) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
+                    *reinterpret_cast<int4*>(dst + 8 * d + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
                 }
                 d_base += __popc(mk);
             }
@@ -371,16 +351,21 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
                 }
             }
         } else {
+            // a row that names the run more than once gets one flagged entry per target
             int d_base = 0;
             for (int i0 = 0; i0 < L; i0 += 32) {
                 const int i = i0 + lane;
-                const int row = i < L ? a[i] / R : -1;
+                const int code = i < L ? a[i] : 0;
+                const int row = i < L ? code / R : -1;
                 const int prow = (i > 0 && i < L) ? a[i - 1] / R : -1;
+                const int nrow = i + 1 < L ? a[i + 1] / R : -2;
                 const bool first = i < L && row != prow;
                 const unsigned mk = __ballot_sync(kFull, first);
                 if (first) {
                     const int d = d_base + __popc(mk & ((1u << lane) - 1u));
-                    for (int q = 0; q < nq; ++q) ent[8 * b0 + q * L + d] = (int)(kDupFlag | (unsigned)(row * m));
+                    for (int q = 0; q < nq; ++q)
+                        ent[8 * b0 + q * L + d] = nrow == row ? (int)(kDupFlag | (unsigned)(row * m))
+                                                              : row * m + 8 * (code - row * R) + q;
                 }
                 d_base += __popc(mk);
             }
@@ -416,7 +401,7 @@ int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, 
     auto kernel = m <= 32 ? inverse_struct_kernel<1> : inverse_struct_kernel<2>;
     const int fit = resident_ctas(reinterpret_cast<const void*>(kernel), kThreads, smem);
     if (fit < 0) return fit;
-    ScopedKernelTimer timer("inverse_build", s);
+    ScopedKernelTimer timer(split_timing_labels() ? "inverse_struct" : "inverse_build", s);
     kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, ntiles, kStructMaxPairs, p, const_cast<int*>(v.rowptr),
                                      const_cast<int*>(v.seglen), const_cast<int*>(v.entries), tf);
     note_launch();

@@ -340,7 +340,7 @@ int scatter_struct_t(const char* label, StructParams p, cudaStream_t s) {
     long long grid = (long long)sm_count() * per_sm;
     const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
-    ScopedKernelTimer timer(label, s);
+    ScopedKernelTimer timer(split_timing_labels() ? "scatter_struct" : label, s);
     kernel<<<(int)grid, 32 * kWarps, smem, s>>>(p);
     note_launch();
     return check_launch();
