@@ -100,13 +100,15 @@ __device__ void warp_sort_smem(unsigned short* a, int L, int lane) {
 template <int P>
 __global__ void __launch_bounds__(kThreads)
 inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int ntiles, int max_tile_pairs,
-                      int* __restrict__ header, int* __restrict__ rowptr, int* __restrict__ seglen,
+                      unsigned m_magic, unsigned m_shift, int with_owner, int* __restrict__ header, int* __restrict__ rowptr, int* __restrict__ seglen,
                       int* __restrict__ entries, int* __restrict__ tileflag) {
     extern __shared__ __align__(16) int sm[];
     int* cntS = sm;                                   // [nt]      pairs per target (clusters)
     int* cntM = cntS + nt;                            // [ntiles]  pairs per target run (runs)
     int* cur = cntM + ntiles;                         // [nt]      write cursor of the chosen kind
     unsigned short* placed = reinterpret_cast<unsigned short*>(cur + nt);    // [n_rows * m / 8] the pairs, by target
+    // clusters: the target of every placed pair, when shared memory has room for it (a search in cur otherwise)
+    unsigned short* owner = with_owner ? placed + ((n_rows * m / 8 + 1) & ~1) : nullptr;
     __shared__ int warp_tot[kWarps + 1];
     __shared__ int ok_clusters, ok_runs, q_len;
     __shared__ int queue[kQueue];
@@ -119,6 +121,7 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
     int* ent = entries + (long long)b * E;
     int* tf = tileflag + (long long)b * (1 + ntiles);
     const int R = m >> 3;                             // run slots per row
+    auto div_m = [&](unsigned x) { return (__umulhi(m_magic, x) + x) >> m_shift; };      // x / m for x < 2^31
 
     if (b == 0 && tid == 0) {
         header[0] = (int)kInvMagic;
@@ -147,9 +150,9 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
                     const int j = lane + 32 * p, row = 8 * k + r;
-                    long long tk = -1;
-                    if (row < n_rows && j < m) tk = __ldg(ib + (long long)row * m + j);
-                    v[r][p] = (tk >= 0 && tk < nt) ? (int)tk : -1;
+                    unsigned long long tk = ~0ull;
+                    if (row < n_rows && j < m) tk = (unsigned long long)__ldg(ib + (long long)row * m + j);
+                    v[r][p] = tk < (unsigned long long)nt ? (int)tk : -1;          // negative or too large: -1
                 }
             bool same = true, inrange = true;
 #pragma unroll
@@ -176,19 +179,24 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
                 for (int p = 0; p < P; ++p)
                     if (lane + 32 * p < m) atomicAdd(&cntS[v[0][p]], 1);
             }
-            if (inrange && (m & 7) == 0) {
+            if (inrange && (m & 7) == 0 && runs) {
+                // is every aligned group of 8 slots one whole cluster 8T .. 8T+7?  Identical rows are checked once.
 #pragma unroll
-                for (int r = 0; r < 8; ++r)
+                for (int r = 0; r < 8; ++r) {
+                    if (r == 0 || !same) {
 #pragma unroll
-                    for (int p = 0; p < P; ++p) {
-                        const int j = lane + 32 * p;
-                        const int v0 = __shfl_sync(kFull, v[r][p], lane & ~7);     // slot j & ~7 of the same pass
-                        if (j < m && 8 * k + r < n_rows) {
-                            const bool good = (v0 & 7) == 0 && v[r][p] == v0 + (lane & 7) && v0 + 7 < nt;
-                            runs = runs && good;
-                            if (good && (lane & 7) == 0) atomicAdd(&cntM[v0 >> 3], 1);
+                        for (int p = 0; p < P; ++p) {
+                            const int j = lane + 32 * p;
+                            const int v0 = __shfl_sync(kFull, v[r][p], lane & ~7);     // slot j & ~7 of the same pass
+                            if (j < m && 8 * k + r < n_rows) {
+                                const bool good = (v0 & 7) == 0 && v[r][p] == v0 + (lane & 7) && v0 + 7 < nt;
+                                runs = runs && good;
+                                if (good && (lane & 7) == 0) atomicAdd(&cntM[v0 >> 3], same ? 8 : 1);
+                            }
                         }
                     }
+                }
+                runs = __all_sync(kFull, runs);
             }
         }
         if (!__all_sync(kFull, clusters) && lane == 0) ok_clusters = 0;
@@ -207,105 +215,148 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
         // ---- clusters: cur = exclusive scan of cntS (in pairs; a pair is 8 entries)
         const int total = block_exclusive_scan(cntS, cur, nt, warp_tot);
         if (tid == 0) rp[nt] = 8 * total;
-        // ---- place the (cluster, slot) pairs: row 8k stands for its cluster
-        for (int k = warp; k < (n_rows >> 3); k += kWarps) {
+        // ---- place the (cluster, slot) pairs: row 8k stands for its cluster; two clusters per warp in flight
+        {
+            const int nblocks = n_rows >> 3;
+            for (int k = warp; k < nblocks; k += 2 * kWarps) {
+                int t0[P], t1[P];
+                const int k1 = k + kWarps;
 #pragma unroll
-            for (int p = 0; p < P; ++p) {
-                const int j = lane + 32 * p;
-                if (j < m) {
-                    const int t = (int)__ldg(ib + (long long)(8 * k) * m + j);
-                    const int pos = atomicAdd(&cur[t], 1);
-                    placed[pos] = (unsigned short)(k * m + j);
+                for (int p = 0; p < P; ++p) {
+                    const int j = lane + 32 * p;
+                    t0[p] = j < m ? (int)__ldg(ib + (long long)(8 * k) * m + j) : -1;
+                    t1[p] = (j < m && k1 < nblocks) ? (int)__ldg(ib + (long long)(8 * k1) * m + j) : -1;
+                }
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                    const int j = lane + 32 * p;
+                    if (t0[p] >= 0) {
+                        const int pos = atomicAdd(&cur[t0[p]], 1);
+                        placed[pos] = (unsigned short)(k * m + j);
+                        if (owner) owner[pos] = (unsigned short)t0[p];
+                    }
+                    if (t1[p] >= 0) {
+                        const int pos = atomicAdd(&cur[t1[p]], 1);
+                        placed[pos] = (unsigned short)(k1 * m + j);
+                        if (owner) owner[pos] = (unsigned short)t1[p];
+                    }
                 }
             }
         }
         __syncthreads();
-        // ---- per target: sort its pairs, expand them into 8 entries each, flag its tile
-        const int nt32 = (nt + 31) & ~31;
-        for (int tb = warp * 32; tb < nt32; tb += kThreads) {
-            const int t = tb + lane;
-            const bool live = t < nt;
-            const int L = live ? cntS[t] : 0;
-            const int b0 = live ? cur[t] - L : 0;
-            bool plain = true;                        // no cluster names t twice, and the list was short
-            if (live) {
-                rp[t] = 8 * b0;
-                if (L > kShortList) {
-                    const int slot = atomicAdd(&q_len, 1);
-                    if (slot < kQueue) {
-                        queue[slot] = t;
-                        plain = false;
-                    }
+        // cur[t] is now the END of target t's pairs; cntS[t] their number.  Bit 30 of cntS[t] will say that the
+        // segment needs the slow path: a cluster names t more than once, or the list is long.
+        constexpr int kSlow = 1 << 30;
+        constexpr int kLong = 64;
+        // ---- one thread per pair: its rank among the target's pairs is where its 8 entries go (the rows of
+        //      its cluster at its slot, 32 contiguous bytes), so the segment comes out ordered by row whatever
+        //      order the atomics ran in
+        for (int p = tid; p < total; p += kThreads) {
+            int t;
+            if (owner) {
+                t = owner[p];
+            } else {
+                int lo = 0, hi = nt - 1;              // the first target whose pairs end behind p
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (cur[mid] > p) hi = mid;
+                    else lo = mid + 1;
                 }
-                if (plain) {
-                    unsigned short* a = placed + b0;
-                    for (int i = 1; i < L; ++i) {     // insertion sort
-                        const unsigned short x = a[i];
-                        int j = i - 1;
-                        while (j >= 0 && a[j] > x) {
-                            a[j + 1] = a[j];
-                            --j;
-                        }
-                        a[j + 1] = x;
-                    }
-                    // one group of entries per distinct cluster: its 8 rows at the pair's slot, or, when the
-                    // cluster names t more than once, one flagged entry per row (the consumer rescans the row)
-                    int* dst = ent + 8 * b0;
-                    int d = 0;
-                    for (int i = 0; i < L;) {
-                        const int code = a[i];
-                        const int c = code / m, j = code - c * m;
-                        int i2 = i + 1;
-                        while (i2 < L && a[i2] / m == c) ++i2;
-                        int e0 = 8 * c * m + j, step = m;
-                        if (i2 - i > 1) {
-                            e0 = (int)(kDupFlag | (unsigned)(8 * c * m));
-                            plain = false;
-                        }
-                        *reinterpret_cast<int4*>(dst + 8 * d) = make_int4(e0, e0 + step, e0 + 2 * step, e0 + 3 * step);
-                        *reinterpret_cast<int4*>(dst + 8 * d + 4) = make_int4(e0 + 4 * step, e0 + 5 * step, e0 + 6 * step, e0 + 7 * step);
-                        ++d;
-                        i = i2;
-                    }
-                    sl[t] = 8 * d;
-                }
+                t = lo;
             }
-            // tile of 8 targets = 8 neighbouring lanes
-            int pairs = L;
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) pairs += __shfl_xor_sync(kFull, pairs, o);
-            const unsigned good = __ballot_sync(kFull, plain && live);
-            const bool tile_ok = ((good >> (lane & ~7)) & 0xffu) == 0xffu && pairs <= max_tile_pairs;
-            if ((lane & 7) == 0 && t < nt) tf[1 + (t >> 3)] = tile_ok ? kTileClusters : kTileGeneral;
+            const int L = cntS[t] & ~kSlow, b0 = cur[t] - L;
+            if (L > kLong) {
+                if (p == b0) atomicOr(&cntS[t], kSlow);
+                continue;
+            }
+            const unsigned code = placed[p];
+            const unsigned c = div_m(code), j = code - c * (unsigned)m;
+            int rank = 0;
+            bool repeat = false;
+            for (int i = 0; i < L; ++i) {
+                const unsigned other = placed[b0 + i];
+                rank += other < code ? 1 : 0;
+                repeat = repeat || (other != code && div_m(other) == c);
+            }
+            if (repeat) atomicOr(&cntS[t], kSlow);
+            const int e0 = (int)(8u * c * (unsigned)m + j);
+            int* dst = ent + 8 * (long long)(b0 + rank);
+            *reinterpret_cast<int4*>(dst) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
+            *reinterpret_cast<int4*>(dst + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
         }
         __syncthreads();
-        // ---- long lists, one warp each
-        const int nq = min(q_len, kQueue);
-        for (int qi = warp; qi < nq; qi += kWarps) {
-            const int t = queue[qi];
-            const int L = cntS[t], b0 = cur[t] - L;
+        // ---- segment starts and lengths; the slow targets go to a queue
+        for (int t = tid; t < nt; t += kThreads) {
+            const int Lr = cntS[t], L = Lr & ~kSlow;
+            rp[t] = 8 * (cur[t] - L);
+            if (!(Lr & kSlow)) {
+                sl[t] = 8 * L;
+            } else {
+                const int slot = atomicAdd(&q_len, 1);
+                if (slot < kQueue) queue[slot] = t;
+                else cntS[t] = Lr | (1 << 29);                      // no room: this thread does it itself below
+            }
+        }
+        __syncthreads();
+        // ---- slow targets, one warp each: sort, then one group of entries per distinct cluster -- its 8 rows
+        //      at the pair's slot, or flagged rows when the cluster names the target more than once
+        auto slow_target = [&](int t, int sub, int nsub) {            // nsub = 32: a warp; nsub = 1: one thread
+            const int L = cntS[t] & ((1 << 29) - 1), b0 = cur[t] - L;
             unsigned short* a = placed + b0;
-            warp_sort_smem(a, L, lane);
-            int* dst = ent + 8 * b0;
+            if (nsub == 32) {
+                warp_sort_smem(a, L, sub);
+            } else {
+                for (int i = 1; i < L; ++i) {
+                    const unsigned short x = a[i];
+                    int j = i - 1;
+                    while (j >= 0 && a[j] > x) {
+                        a[j + 1] = a[j];
+                        --j;
+                    }
+                    a[j + 1] = x;
+                }
+            }
+            int* dst = ent + 8 * (long long)b0;
             int d_base = 0;
-            for (int i0 = 0; i0 < L; i0 += 32) {
-                const int i = i0 + lane;
-                const int code = i < L ? a[i] : 0;
-                const int c = i < L ? code / m : -1;
-                const int pc = (i > 0 && i < L) ? a[i - 1] / m : -1;
-                const int nc = i + 1 < L ? a[i + 1] / m : -2;
+            for (int i0 = 0; i0 < L; i0 += nsub) {
+                const int i = i0 + sub;
+                const unsigned code = i < L ? a[i] : 0u;
+                const int c = i < L ? (int)div_m(code) : -1;
+                const int pc = (i > 0 && i < L) ? (int)div_m(a[i - 1]) : -1;
+                const int nc = i + 1 < L ? (int)div_m(a[i + 1]) : -2;
                 const bool first = i < L && c != pc;
-                const unsigned mk = __ballot_sync(kFull, first);
+                const unsigned mk = nsub == 32 ? __ballot_sync(kFull, first) : (first ? 1u : 0u);
                 if (first) {
-                    const int d = d_base + __popc(mk & ((1u << lane) - 1u));
-                    int e0 = 8 * c * m + (code - c * m);
-                    if (nc == c) e0 = (int)(kDupFlag | (unsigned)(8 * c * m));      // named more than once: flagged rows
+                    const int d = d_base + __popc(mk & ((1u << sub) - 1u));
+                    int e0 = (int)(8u * (unsigned)c * (unsigned)m + (code - (unsigned)c * (unsigned)m));
+                    if (nc == c) e0 = (int)(kDupFlag | (8u * (unsigned)c * (unsigned)m));
                     *reinterpret_cast<int4*>(dst + 8 * d) = make_int4(e0, e0 + m, e0 + 2 * m, e0 + 3 * m);
                     *reinterpret_cast<int4*>(dst + 8 * d + 4) = make_int4(e0 + 4 * m, e0 + 5 * m, e0 + 6 * m, e0 + 7 * m);
                 }
                 d_base += __popc(mk);
             }
-            if (lane == 0) sl[t] = 8 * d_base;
+            if (sub == 0) sl[t] = 8 * d_base;
+        };
+        {
+            const int nq = min(q_len, kQueue);
+            for (int qi = warp; qi < nq; qi += kWarps) slow_target(queue[qi], lane, 32);
+            if (q_len > kQueue)
+                for (int t = tid; t < nt; t += kThreads)
+                    if (cntS[t] & (1 << 29)) slow_target(t, 0, 1);
+        }
+        // ---- tiles: structured when complete, without slow targets and small enough for the lean kernel
+        for (int T = tid; T < ntiles; T += kThreads) {
+            bool ok = 8 * T + 8 <= nt;
+            int pairs = 0;
+            if (ok) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int Lr = cntS[8 * T + q];
+                    ok = ok && !(Lr & kSlow);
+                    pairs += Lr & ((1 << 29) - 1);
+                }
+            }
+            tf[1 + T] = (ok && pairs <= max_tile_pairs) ? kTileClusters : kTileGeneral;
         }
         if (tid == 0) tf[0] = kBuildClusters;
         return;
@@ -387,7 +438,10 @@ int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, 
     InverseView v = inverse_view(buf, b, n_rows, m, nt);
     const int ntiles = inverse_tiles(nt);
     int* tf = const_cast<int*>(v.tileflag);
-    const size_t smem = size_t(2 * nt + ntiles) * sizeof(int) + ((size_t(n_rows) * m / 8 + 1) & ~size_t(1)) * sizeof(unsigned short);
+    const size_t units2 = ((size_t(n_rows) * m / 8 + 1) & ~size_t(1)) * sizeof(unsigned short);
+    size_t smem = size_t(2 * nt + ntiles) * sizeof(int) + units2;
+    const int with_owner = (nt <= 65535 && smem + units2 <= 200 * 1024) ? 1 : 0;
+    if (with_owner) smem += units2;
     const bool possible = m <= 64 && smem <= 200 * 1024 && (long long)n_rows * m / 8 <= 65535 &&
                           (m % 8 == 0 || n_rows % 8 == 0);
     if (!possible) {
@@ -402,7 +456,10 @@ int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, 
     const int fit = resident_ctas(reinterpret_cast<const void*>(kernel), kThreads, smem);
     if (fit < 0) return fit;
     ScopedKernelTimer timer(split_timing_labels() ? "inverse_struct" : "inverse_build", s);
-    kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, ntiles, kStructMaxPairs, p, const_cast<int*>(v.rowptr),
+    unsigned m_magic, m_shift = 0;
+    while ((1ull << m_shift) < (unsigned)m) ++m_shift;
+    m_magic = (unsigned)(((1ull << 32) * ((1ull << m_shift) - (unsigned)m)) / (unsigned)m + 1);
+    kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, ntiles, kStructMaxPairs, m_magic, m_shift, with_owner, p, const_cast<int*>(v.rowptr),
                                      const_cast<int*>(v.seglen), const_cast<int*>(v.entries), tf);
     note_launch();
     return check_launch();

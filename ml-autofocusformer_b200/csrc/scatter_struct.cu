@@ -24,23 +24,24 @@
 namespace clusten {
 namespace {
 
-constexpr int kSR = 48;                  // staged rows per stage
-constexpr int kPairs = kStructMaxPairs;  // (cluster, slot) pairs of a clusters tile
+constexpr int kSR = 32;                  // staged rows per stage (4 clusters)
+constexpr int kPairs = kStructMaxPairs;  // (cluster, slot) pairs of a clusters tile; entries kept of a runs tile
 
+// Per-warp shared memory.  Rows and weights are double-buffered: while one stage is multiplied the next
+// one (the next 32 rows, or the next head) is on its way.
 template <typename T> struct StructSmem {
     static constexpr bool kIsFloat = std::is_same<T, float>::value;
-    static constexpr int kX = kSR * kC * (int)sizeof(T);      // staged rows; de-duplication scratch before that
-    static constexpr int kW = kSR * kT * (int)sizeof(T);      // dense weights [staged row][target]
+    static constexpr int kX = kSR * kC * (int)sizeof(T);      // staged rows, one buffer; de-duplication scratch before that
+    static constexpr int kW = kSR * kT * (int)sizeof(T);      // dense weights [staged row][target], one buffer
     static constexpr int kOut = kT * kOLD * 4;                // output tile
-    static constexpr int kSrc = kSR * 4;                      // runs: source row of each staged row
-    static constexpr int kWoff = kSR * 4;                     // runs: offset of the row's 8 weights
-    static constexpr int kCode = kPairs * 4;                  // clusters: offset of a pair's first weight
+    static constexpr int kCode = kPairs * 4;                  // clusters: offset of a pair's first weight;  runs: the entries
     static constexpr int kSlotq = kPairs * 2;                 // clusters: slot of the pair's cluster | target << 12
     static constexpr int kUniq = kPairs * 2;                  // clusters: slot -> cluster
-    static constexpr int kTotal = kX + kW + kOut + kSrc + kWoff + kCode + kSlotq + kUniq;
+    static constexpr int kJmap = kPairs * kT;                 // clusters: [slot][target] -> neighbour slot j, 0xff = not named
+    static constexpr int kTotal = 2 * kX + 2 * kW + kOut + kCode + kSlotq + kUniq + kJmap;
 };
-// scratch of dedup_tokens (tok, bm, pre, rowbm) lives in the row buffer while a tile is analysed
-static_assert(kPairs * 2 + kBMW * 4 + kBMW * 2 + 64 <= kSR * kC * 2, "de-duplication scratch must fit in the row buffer");
+static_assert(kPairs * 2 + kBMW * 4 + kBMW * 2 + 64 <= 2 * kSR * kC * 2, "de-duplication scratch must fit in the row buffers");
+static_assert(StructSmem<float>::kTotal % 128 == 0 && StructSmem<__half>::kTotal % 128 == 0, "warps stay 128-byte aligned");
 
 struct StructParams {
     const void* W;      // [batch][heads][n][m]
@@ -134,16 +135,16 @@ scatter_struct_kernel(const StructParams p) {
     constexpr int kPer = 16 / (int)sizeof(T);           // elements per 16-byte piece
     constexpr int kLanesPerRow = kC / kPer;             // 8 (fp32) or 4 (16-bit)
     constexpr int kRowsPerPass = 32 / kLanesPerRow;     // 4 or 8
+    constexpr int kXe = kSR * kC, kWe = kSR * kT;       // elements per buffer
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
-    T* Xs = reinterpret_cast<T*>(base);
-    T* Ws = reinterpret_cast<T*>(base + WS::kX);
-    float* Ot = reinterpret_cast<float*>(base + WS::kX + WS::kW);
-    int* src = reinterpret_cast<int*>(base + WS::kX + WS::kW + WS::kOut);
-    int* woff = src + kSR;
-    unsigned* code = reinterpret_cast<unsigned*>(woff + kSR);
+    T* Xs = reinterpret_cast<T*>(base);                                         // [2][kSR][32]
+    T* Ws = reinterpret_cast<T*>(base + 2 * WS::kX);                            // [2][kSR][8]
+    float* Ot = reinterpret_cast<float*>(base + 2 * WS::kX + 2 * WS::kW);
+    unsigned* code = reinterpret_cast<unsigned*>(Ot + kT * kOLD);
     unsigned short* slotq = reinterpret_cast<unsigned short*>(code + kPairs);
     unsigned short* uniq = slotq + kPairs;
+    unsigned char* jmap = reinterpret_cast<unsigned char*>(uniq + kPairs);
     DedupScratch ds;
     ds.tok = reinterpret_cast<unsigned short*>(base);
     ds.bm = reinterpret_cast<unsigned*>(base + kPairs * 2);
@@ -157,35 +158,47 @@ scatter_struct_kernel(const StructParams p) {
     const T* Xg = static_cast<const T*>(p.X);
     T* Og = static_cast<T*>(p.out);
     const int pr = lane / kLanesPerRow, pc = lane % kLanesPerRow;       // staging: row within a pass, 16-byte piece
-    // chunk swizzle of staged row r (see the product routines)
-    auto xdst = [&](int r) {
-        if (kIsFloat) return Xs + r * kC + ((pc ^ ((r & 3) << 1)) << 2);
-        return Xs + swz16(r, pc);
-    };
-    StructAddr sa{};
-    if (kIsFloat) sa = make_struct_addr(reinterpret_cast<const float*>(Ws), reinterpret_cast<const float*>(Xs), lane);
+    // element offset of this lane's piece of staged row r inside a row buffer (chunk swizzle of the products)
+    auto xoff = [&](int r) { return kIsFloat ? r * kC + ((pc ^ ((r & 3) << 1)) << 2) : swz16(r, pc); };
+    StructAddr sa0{};
+    if (kIsFloat) sa0 = make_struct_addr(reinterpret_cast<const float*>(Ws), reinterpret_cast<const float*>(Xs), lane);
 
     const unsigned total = (unsigned)p.batch * (unsigned)p.tiles;
     const unsigned nwarps = gridDim.x * kWarps;
-    for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
-        const int b = (int)(task / (unsigned)p.tiles);
-        const int tile = (int)(task - (unsigned)b * (unsigned)p.tiles);
-        const int kind = p.inv.tileflag[(long long)b * (1 + p.inv.ntiles) + 1 + tile];
-        if (kind == kTileGeneral) continue;
-        const int t0 = tile * kT;
-        const int* entries = p.inv.entries + (long long)b * n * m;
-        int len = 0, start = 0;
-        if (lane < kT) {
-            len = p.inv.seglen[(long long)b * n + t0 + lane];
-            start = p.inv.rowptr[(long long)b * (n + 1) + t0 + lane];
+    // kind, and (lanes 0..7) segment length and start of the targets of a task's tile
+    auto load_meta = [&](unsigned task, int& kind, int& len, int& start) {
+        kind = kTileGeneral;
+        len = 0;
+        start = 0;
+        if (task < total) {
+            const int b = (int)(task / (unsigned)p.tiles);
+            const int tile = (int)(task - (unsigned)b * (unsigned)p.tiles);
+            kind = __ldg(p.inv.tileflag + (long long)b * (1 + p.inv.ntiles) + 1 + tile);
+            const int t = tile * kT + lane;
+            if (lane < kT && t < n) {
+                len = __ldg(p.inv.seglen + (long long)b * n + t);
+                start = __ldg(p.inv.rowptr + (long long)b * (n + 1) + t);
+            }
         }
+    };
+    int next_kind, next_len, next_start;
+    load_meta(blockIdx.x * kWarps + warp, next_kind, next_len, next_start);
+    for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
+        const int kind = next_kind, len = next_len, start = next_start;
+        load_meta(task + nwarps, next_kind, next_len, next_start);      // in flight while this tile is worked on
+        if (kind == kTileGeneral) continue;
+        const int b = (int)(task / (unsigned)p.tiles);
+        const int t0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
+        const int* entries = p.inv.entries + (long long)b * n * m;
         __syncwarp();
 
-        int L = 0, UC = 0;                 // runs: rows of the tile;  clusters: distinct clusters
+        int L = 0, UC = 0;                 // runs: rows of the tile;  clusters: pairs and distinct clusters
         int start0 = 0;
         if (kind == kTileRuns) {
             L = __shfl_sync(kFull, len, 0);
             start0 = __shfl_sync(kFull, start, 0);
+            for (int x = lane; x < min(L, kPairs); x += 32) code[x] = (unsigned)__ldg(entries + start0 + x);
+            __syncwarp();
         } else {
             // ---- the tile's (cluster, slot) pairs: first entry of every group of 8
             const int pairs = len >> 3;
@@ -196,25 +209,30 @@ scatter_struct_kernel(const StructParams p) {
                 if (lane >= o) incl += y;
             }
             const int CE = __shfl_sync(kFull, incl, kT - 1);
+            int off[kT], st[kT];
+#pragma unroll
+            for (int j = 0; j < kT; ++j) {
+                off[j] = __shfl_sync(kFull, incl - pairs, j);
+                st[j] = __shfl_sync(kFull, start, j);
+            }
             int lo = INT_MAX, hi = -1;
             unsigned myq[(kPairs + 31) / 32];
 #pragma unroll
             for (int i = 0; i < (kPairs + 31) / 32; ++i) {
                 const int x = lane + 32 * i;
-                int q = 0, off = 0, st = __shfl_sync(kFull, start, 0);
+                int q = 0;
 #pragma unroll
-                for (int j = 1; j < kT; ++j) {
-                    const int oj = __shfl_sync(kFull, incl - pairs, j);
-                    const int sj = __shfl_sync(kFull, start, j);
-                    if (x >= oj) {
-                        q = j;
-                        off = oj;
-                        st = sj;
+                for (int j = 1; j < kT; ++j) q += x >= off[j] ? 1 : 0;
+                int o = off[0], s0 = st[0];
+#pragma unroll
+                for (int j = 1; j < kT; ++j)
+                    if (q == j) {
+                        o = off[j];
+                        s0 = st[j];
                     }
-                }
                 myq[i] = (unsigned)q;
                 if (x < CE) {
-                    const unsigned e = (unsigned)__ldg(entries + st + 8 * (x - off));
+                    const unsigned e = (unsigned)__ldg(entries + s0 + 8 * (x - o));
                     const int c = (int)(div_m(e) >> 3);
                     code[x] = e;
                     ds.tok[x] = (unsigned short)c;
@@ -223,93 +241,154 @@ scatter_struct_kernel(const StructParams p) {
                 }
             }
             bool unused = false;
-            unsigned short* slots = slotq;                // slot first, the target is merged in below
-            UC = CE > 0 ? dedup_tokens(ds, slots, CE, m, false, &unused, lane, lo, hi) : 0;
+            UC = CE > 0 ? dedup_tokens(ds, slotq, CE, m, false, &unused, lane, lo, hi) : 0;
+            // per distinct cluster: the slot at which it names each of the 8 targets (a flagged tile has at
+            // most one), 0xff where it does not
+            for (int z = lane; z < UC * kT / 4; z += 32) reinterpret_cast<unsigned*>(jmap)[z] = 0xffffffffu;
+            __syncwarp();
 #pragma unroll
             for (int i = 0; i < (kPairs + 31) / 32; ++i) {
                 const int x = lane + 32 * i;
-                if (x < CE) slotq[x] = (unsigned short)(slotq[x] | (myq[i] << 12));
+                if (x < CE) {
+                    const unsigned e = code[x];
+                    jmap[(int)slotq[x] * kT + (int)myq[i]] = (unsigned char)(e - div_m(e) * (unsigned)m);
+                }
             }
             L = CE;
             __syncwarp();
         }
 
-        const int nstages = kind == kTileRuns ? (L + kSR - 1) / kSR : (UC + 5) / 6;
-        for (int g = 0; g < heads; ++g) {
+        const int nstages = kind == kTileRuns ? (L + kSR - 1) / kSR : (UC + 3) / 4;
+        const int units = heads * nstages;
+        // rows of stage s, and rounded up to what the product consumes
+        auto stage_rows = [&](int s) { return kind == kTileRuns ? min(kSR, L - s * kSR) : 8 * min(4, UC - 4 * s); };
+        auto padded = [&](int rows) { return kIsFloat ? ((rows + 7) & ~7) : ((rows + 15) & ~15); };
+        // clusters tiles: lane l copies piece l of a cluster's 8 contiguous rows (fp32: two pieces, rows l / 8 and
+        // 4 + l / 8; 16-bit: row l / 4) and fills weight (row l % 8, targets l / 8 and 4 + l / 8)
+        const int wr = lane & 7, wq = lane >> 3;
+        const int xrow = kIsFloat ? (lane >> 3) : (lane >> 2);
+
+        // ---- loads of unit (head g, stage s) into buffer `buf`; 16-bit weights of a clusters tile come back in
+        //      wv and are stored by the caller once the previous product is done with the buffer
+        auto issue = [&](int g, int s, int buf, T (&wv)[8]) {
             const long long bh = (long long)b * heads + g;
             const T* Wh = Wg + bh * n * m;
             const T* Xh = Xg + bh * n * kC;
-            float acc[2][4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
-            for (int s = 0; s < nstages; ++s) {
-                int rows;                                  // staged rows of this stage
-                __syncwarp();
-                if (kind == kTileRuns) {
-                    const int k0 = s * kSR;
-                    rows = min(kSR, L - k0);
-                    if (g == 0 || nstages > 1) {
-                        // source row and weight offset of every staged row
-                        for (int u = lane; u < rows; u += 32) {
-                            const unsigned e = (unsigned)__ldg(entries + start0 + k0 + u);
-                            src[u] = (int)div_m(e);
-                            woff[u] = (int)e;
-                        }
-                        __syncwarp();
-                    }
-                } else {
-                    rows = 8 * min(6, UC - 6 * s);
-                }
-                const int rows_pad = kIsFloat ? ((rows + 7) & ~7) : ((rows + 15) & ~15);
-                // ---- rows -> Xs
+            T* Xb = Xs + buf * kXe;
+            T* Wb = Ws + buf * kWe;
+            const int rows = stage_rows(s), rows_pad = padded(rows);
+            if (kind == kTileRuns) {
+                const int k0 = s * kSR;
+                auto entry = [&](int r) {
+                    return k0 + r < kPairs ? code[k0 + r] : (unsigned)__ldg(entries + start0 + k0 + r);
+                };
 #pragma unroll
                 for (int k = 0; k < kSR / kRowsPerPass; ++k) {
                     const int r = pr + kRowsPerPass * k;
                     if (r < rows_pad) {
-                        T* dst = xdst(r);
-                        if (r < rows) {
-                            const int row = kind == kTileRuns ? src[r] : (int)uniq[6 * s + (r >> 3)] * 8 + (r & 7);
-                            cp_async16_cg(dst, Xh + (long long)row * kC + pc * kPer);
-                        } else {
-                            *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                    }
-                }
-                // ---- weights -> Ws[row][target]
-                if (kind == kTileRuns) {
-                    constexpr int kPieces = kT / kPer;      // 16-byte pieces per row of 8 weights: 2 or 1
-                    for (int z = lane; z < rows_pad * kPieces; z += 32) {
-                        const int u = z / kPieces, piece = z % kPieces;
-                        T* dst = Ws + u * kT + piece * kPer;
-                        if (u < rows) cp_async16_ca(dst, Wh + woff[u] + piece * kPer);
+                        T* dst = Xb + xoff(r);
+                        if (r < rows) cp_async16_cg(dst, Xh + (long long)div_m(entry(r)) * kC + pc * kPer);
                         else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                     }
-                } else {
-                    for (int z = lane; z < rows_pad * kT * (int)sizeof(T) / 16; z += 32)
-                        reinterpret_cast<float4*>(Ws)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    __syncwarp();
-                    const int xs = lane >> 3, r = lane & 7;
-                    for (int x = xs; x < L; x += 4) {
-                        const unsigned sq = slotq[x];
-                        const int rel = (int)(sq & 0xfffu) - 6 * s;
-                        if (rel >= 0 && rel < 6) {
-                            const T* wsrc = Wh + code[x] + r * m;
-                            T* dst = Ws + (rel * 8 + r) * kT + (sq >> 12);
-                            if (kIsFloat) cp_async4_ca(dst, wsrc);
-                            else *dst = *wsrc;
-                        }
+                }
+                constexpr int kPieces = kT / kPer;      // 16-byte pieces per row of 8 weights: 2 or 1
+#pragma unroll
+                for (int k = 0; k < kSR * kPieces / 32; ++k) {
+                    const int z = lane + 32 * k;
+                    const int r = z / kPieces, piece = z % kPieces;
+                    if (r < rows_pad) {
+                        T* dst = Wb + r * kT + piece * kPer;
+                        if (r < rows) cp_async16_ca(dst, Wh + entry(r) + piece * kPer);
+                        else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                 }
-                cp_async_commit();
-                cp_async_wait<0>();
-                __syncwarp();
-                if (kIsFloat) struct_steps<0>(sa, rows_pad >> 3, acc);
-                else struct_product16<T>(Xs, Ws, rows_pad >> 4, lane, acc);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int u = 4 * s + i;
+                    if (u < UC) {
+                        const int c8 = (int)uniq[u] * 8;                    // first row of the cluster
+                        const T* xsrc = Xh + (long long)c8 * kC + lane * kPer;
+                        if (kIsFloat) {
+                            cp_async16_cg(Xb + xoff(8 * i + xrow), xsrc);
+                            cp_async16_cg(Xb + xoff(8 * i + 4 + xrow), xsrc + 4 * kC);
+                        } else {
+                            cp_async16_cg(Xb + xoff(8 * i + xrow), xsrc);
+                        }
+                        const T* wsrc = Wh + (long long)(c8 + wr) * m;
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2) {
+                            const int q = wq + 4 * h2;
+                            const unsigned j = jmap[u * kT + q];
+                            if (kIsFloat) {
+                                T* dst = Wb + (8 * i + wr) * kT + q;
+                                if (j != 0xffu) cp_async4_ca(dst, wsrc + j);
+                                else *dst = Elem<T>::down(0.f);
+                            } else {
+                                wv[2 * i + h2] = j != 0xffu ? wsrc[j] : Elem<T>::down(0.f);
+                            }
+                        }
+                    } else if (8 * i < rows_pad) {
+                        // 16-bit products run over multiples of 16 rows: an empty cluster slot is zero
+                        *reinterpret_cast<float4*>(Xb + xoff(8 * i + xrow)) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        wv[2 * i] = wv[2 * i + 1] = Elem<T>::down(0.f);
+                    }
+                }
             }
-            // ---- D fragments -> output tile -> 16-byte stores
-            {
+            cp_async_commit();
+        };
+
+        float acc[2][4];
+        T wnext[8];
+        if (units > 0) issue(0, 0, 0, wnext);
+        int g = 0, st = 0;
+        for (int u = 0; u < units; ++u) {
+            const int buf = u & 1;
+            int ng = g, ns = st + 1;
+            if (ns == nstages) {
+                ns = 0;
+                ++ng;
+            }
+            T wcur[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wcur[i] = wnext[i];
+            if (u + 1 < units) {
+                issue(ng, ns, buf ^ 1, wnext);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            const int rows_pad = padded(stage_rows(st));
+            if (!kIsFloat && kind == kTileClusters) {
+                T* Wb = Ws + buf * kWe;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (8 * i < rows_pad) {
+                        Wb[(8 * i + wr) * kT + wq] = wcur[2 * i];
+                        Wb[(8 * i + wr) * kT + wq + 4] = wcur[2 * i + 1];
+                    }
+            }
+            __syncwarp();
+            if (st == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
+            }
+            if (kIsFloat) {
+                StructAddr sa = sa0;
+                sa.w += buf * kWe * 4;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    sa.x[mt][0] += buf * kXe * 4;
+                    sa.x[mt][1] += buf * kXe * 4;
+                }
+                struct_steps<0>(sa, rows_pad >> 3, acc);
+            } else {
+                struct_product16<T>(Xs + buf * kXe, Ws + buf * kWe, rows_pad >> 4, lane, acc);
+            }
+            __syncwarp();                                  // this buffer may be refilled by the next issue
+            if (st == nstages - 1) {
+                // ---- D fragments -> output tile -> 16-byte stores
                 const int gg = lane >> 2, tt = lane & 3;
-                __syncwarp();
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
                     float* o = Ot + (2 * tt) * kOLD + 16 * mt + gg;
@@ -320,12 +399,24 @@ scatter_struct_kernel(const StructParams p) {
                 }
                 __syncwarp();
                 const int qi = lane >> 3, ci = lane & 7;
-                T* Oh = Og + bh * n * kC;
+                T* Oh = Og + ((long long)b * heads + g) * n * kC;
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
                     const int q = 2 * qi + a;
                     st4(Oh + (long long)(t0 + q) * kC + ci * 4, *reinterpret_cast<const float4*>(Ot + q * kOLD + ci * 4));
                 }
+                __syncwarp();
+            }
+            g = ng;
+            st = ns;
+        }
+        if (units == 0 || nstages == 0) {
+            // a tile nobody names: zeros
+            for (int g = 0; g < heads; ++g) {
+                T* Oh = Og + ((long long)b * heads + g) * n * kC;
+                const int qi = lane >> 3, ci = lane & 7;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) st4(Oh + (long long)(t0 + 2 * qi + a) * kC + ci * 4, make_float4(0.f, 0.f, 0.f, 0.f));
             }
         }
     }
