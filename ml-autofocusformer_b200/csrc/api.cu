@@ -95,13 +95,16 @@ int resident_ctas(const void* kernel, int threads, size_t smem) {
     std::lock_guard<std::mutex> lk(mu);
     // the limit is one number per kernel and device: it is only ever raised, so that a launch with a
     // smaller request does not take it away from a later launch with a larger one
+    // (a kernel's static shared memory counts towards the 48 KB that need no opt-in, so the limit is raised well
+    // before the dynamic part alone gets there)
     size_t& cur = limit[{kernel, dev}];
-    if (smem > 48 * 1024 && smem > cur) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (smem > 32 * 1024 && smem > cur) {
+        const size_t want = smem < 64 * 1024 ? 64 * 1024 : smem;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) != cudaSuccess) {
             cudaGetLastError();
             return CLUSTEN_ERR_CUDA;
         }
-        cur = smem;
+        cur = want;
     }
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;

@@ -100,15 +100,19 @@ __device__ void warp_sort_smem(unsigned short* a, int L, int lane) {
 template <int P>
 __global__ void __launch_bounds__(kThreads)
 inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt, int ntiles, int max_tile_pairs,
-                      unsigned m_magic, unsigned m_shift, int with_owner, int* __restrict__ header, int* __restrict__ rowptr, int* __restrict__ seglen,
+                      unsigned m_magic, unsigned m_shift, int with_owner, int warp_counts, int* __restrict__ header, int* __restrict__ rowptr, int* __restrict__ seglen,
                       int* __restrict__ entries, int* __restrict__ tileflag) {
     extern __shared__ __align__(16) int sm[];
     int* cntS = sm;                                   // [nt]      pairs per target (clusters)
     int* cntM = cntS + nt;                            // [ntiles]  pairs per target run (runs)
     int* cur = cntM + ntiles;                         // [nt]      write cursor of the chosen kind
     unsigned short* placed = reinterpret_cast<unsigned short*>(cur + nt);    // [n_rows * m / 8] the pairs, by target
-    // clusters: the target of every placed pair, when shared memory has room for it (a search in cur otherwise)
+    // the target (clusters) or target run (runs) of every placed pair, when shared memory has room for it (a
+    // search in cur otherwise)
     unsigned short* owner = with_owner ? placed + ((n_rows * m / 8 + 1) & ~1) : nullptr;
+    // runs: pairs per (warp, target run), each warp counting the rows it will later place (in order, so that
+    // the run's pairs come out sorted without a sort); behind placed / owner when there is room
+    int* cntW = warp_counts ? reinterpret_cast<int*>(placed + (with_owner ? 2 : 1) * ((n_rows * m / 8 + 1) & ~1)) : nullptr;
     __shared__ int warp_tot[kWarps + 1];
     __shared__ int ok_clusters, ok_runs, q_len;
     __shared__ int queue[kQueue];
@@ -132,6 +136,8 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
     }
     for (int t = tid; t < nt; t += kThreads) cntS[t] = 0;
     for (int t = tid; t < ntiles; t += kThreads) cntM[t] = 0;
+    if (cntW)
+        for (int t = tid; t < kWarps * ntiles; t += kThreads) cntW[t] = 0;
     if (tid == 0) {
         ok_clusters = (n_rows % 8 == 0) ? 1 : 0;
         ok_runs = (m % 8 == 0) ? 1 : 0;
@@ -143,7 +149,12 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
     {
         bool clusters = true, runs = true;
         const int blocks = (n_rows + 7) >> 3;
-        for (int k = warp; k < blocks; k += kWarps) {
+        const int per_warp = (blocks + kWarps - 1) / kWarps;           // a contiguous range of row blocks per warp
+        int* cnt_runs = cntW ? cntW + warp * ntiles : cntM;
+        for (int k = warp * per_warp; k < min(blocks, (warp + 1) * per_warp); ++k) {
+            // nothing left to find out once both structures are ruled out (by this warp or another one)
+            if (!clusters && !runs) break;
+            if (*reinterpret_cast<volatile int*>(&ok_clusters) == 0 && *reinterpret_cast<volatile int*>(&ok_runs) == 0) break;
             int v[8][P];
 #pragma unroll
             for (int r = 0; r < 8; ++r)
@@ -191,13 +202,15 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
                             if (j < m && 8 * k + r < n_rows) {
                                 const bool good = (v0 & 7) == 0 && v[r][p] == v0 + (lane & 7) && v0 + 7 < nt;
                                 runs = runs && good;
-                                if (good && (lane & 7) == 0) atomicAdd(&cntM[v0 >> 3], same ? 8 : 1);
+                                if (good && (lane & 7) == 0) atomicAdd(&cnt_runs[v0 >> 3], same ? 8 : 1);
                             }
                         }
                     }
                 }
                 runs = __all_sync(kFull, runs);
             }
+            if (!clusters && lane == 0) ok_clusters = 0;
+            if (!runs && lane == 0) ok_runs = 0;
         }
         if (!__all_sync(kFull, clusters) && lane == 0) ok_clusters = 0;
         if (!__all_sync(kFull, runs) && lane == 0) ok_runs = 0;
@@ -362,9 +375,85 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
         return;
     }
 
-    // ---- runs: cur = exclusive scan of cntM (in pairs; a pair is one entry for each of the run's 8 targets)
-    const int total = block_exclusive_scan(cntM, cur, ntiles, warp_tot);
+    // ---- runs (a pair is one entry for each of the run's 8 targets)
+    constexpr int kSlowRun = 1 << 30;
+    unsigned r_shift = 0;                             // x / R for x < 2^31 (R <= 8)
+    while ((1u << r_shift) < (unsigned)R) ++r_shift;
+    const unsigned r_magic = (unsigned)(((1ull << 32) * ((1ull << r_shift) - (unsigned)R)) / (unsigned)R + 1);
+    auto div_R = [&](unsigned x) { return (__umulhi(r_magic, x) + x) >> r_shift; };
+    if (cntW) {
+        for (int T = tid; T < ntiles; T += kThreads) {
+            int tot = 0;
+            for (int w = 0; w < kWarps; ++w) tot += cntW[w * ntiles + T];
+            cntM[T] = tot;
+        }
+        __syncthreads();
+    }
+    const int total = block_exclusive_scan(cntM, cur, ntiles, warp_tot);     // cur[T]: start of run T's pairs
     if (tid == 0) rp[nt] = 8 * total;
+    if (cntW) {
+        // start of every warp's share of every run
+        for (int T = tid; T < ntiles; T += kThreads) {
+            int running = cur[T];
+            for (int w = 0; w < kWarps; ++w) {
+                const int c = cntW[w * ntiles + T];
+                cntW[w * ntiles + T] = running;
+                running += c;
+            }
+            cur[T] = running;                          // end of the run's pairs, as after an atomic placement
+        }
+        __syncthreads();
+        // ---- ordered placement: every warp walks its rows in ascending order, a few rows per trip; pairs of one
+        //      trip that name the same run are ranked by lane (= by row, then slot)
+        const int rows_per = 32 / R;
+        const int sub = lane / R, jr = lane - sub * R;
+        const int blocks = (n_rows + 7) >> 3;
+        const int per_warp = (blocks + kWarps - 1) / kWarps;
+        const int row_lo = min(n_rows, 8 * warp * per_warp), row_hi = min(n_rows, 8 * (warp + 1) * per_warp);
+        int* mine = cntW + warp * ntiles;
+        for (int r0 = row_lo; r0 < row_hi; r0 += rows_per) {
+            const int row = r0 + sub;
+            const bool act = sub < rows_per && row < row_hi;
+            const int T = act ? (int)(__ldg(ib + (long long)row * m + 8 * jr) >> 3) : -1 - lane;
+            const unsigned peers = __match_any_sync(kFull, T);
+            const int before = __popc(peers & ((1u << lane) - 1u));
+            int pos = 0;
+            if (act) pos = mine[T] + before;
+            __syncwarp();
+            if (act) {
+                if (before == 0) mine[T] += __popc(peers);
+                placed[pos] = (unsigned short)(row * R + jr);
+                if (owner) owner[pos] = (unsigned short)T;
+                // a row that names the run twice: two peers inside the row's own lanes
+                const unsigned rowmask = ((R == 32 ? 0xffffffffu : ((1u << R) - 1u)) << (sub * R));
+                if (__popc(peers & rowmask) > 1) atomicOr(&cntM[T], kSlowRun);
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        // ---- one thread per pair: the pairs are in order, pair k of a run is entry k of its 8 segments
+        for (int p = tid; p < total; p += kThreads) {
+            int T;
+            if (owner) {
+                T = owner[p];
+            } else {
+                int lo = 0, hi = ntiles - 1;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (cur[mid] > p) hi = mid;
+                    else lo = mid + 1;
+                }
+                T = lo;
+            }
+            const int L = cntM[T] & ~kSlowRun, b0 = cur[T] - L;
+            const unsigned code = placed[p];
+            const unsigned row = div_R(code), jr2 = code - row * (unsigned)R;
+            const int nq = min(8, nt - 8 * T);
+            const int e0 = (int)(row * (unsigned)m + 8u * jr2);
+            int* dst = ent + 8 * (long long)b0 + (p - b0);
+            for (int q = 0; q < nq; ++q) dst[q * L] = e0 + q;
+        }
+    } else {
     {
         const int rows_per = 32 / R;                  // rows per warp and trip, R lanes each
         const int sub = lane / R, jr = lane - sub * R;
@@ -375,58 +464,87 @@ inverse_struct_kernel(const int64_t* __restrict__ idx, int n_rows, int m, int nt
                 const int T = (int)(__ldg(ib + (long long)row * m + 8 * jr) >> 3);
                 const int pos = atomicAdd(&cur[T], 1);
                 placed[pos] = (unsigned short)(row * R + jr);
+                if (owner) owner[pos] = (unsigned short)T;
             }
         }
     }
     __syncthreads();
-    for (int T = warp; T < ntiles; T += kWarps) {
-        const int L = cntM[T], b0 = cur[T] - L;
-        unsigned short* a = placed + b0;
-        if (L > 1) warp_sort_smem(a, L, lane);
-        // does a row name the run twice?
-        bool dup = false;
-        for (int i = lane + 1; i < L; i += 32) dup = dup || (a[i] / R == a[i - 1] / R);
-        dup = __any_sync(kFull, dup);
-        const int nq = min(8, nt - 8 * T);            // targets of this run that exist
-        if (!dup) {
-            for (int q = 0; q < nq; ++q) {
-                int* dst = ent + 8 * b0 + q * L;
-                for (int i = lane; i < L; i += 32) {
-                    const int code = a[i];
-                    const int row = code / R, r = code - row * R;
-                    dst[i] = row * m + 8 * r + q;
-                }
-                if (lane == 0) {
-                    rp[8 * T + q] = 8 * b0 + q * L;
-                    sl[8 * T + q] = L;
-                }
-            }
+    // ---- one thread per pair: its rank among the run's pairs is its place in each of the 8 segments
+    for (int p = tid; p < total; p += kThreads) {
+        int T;
+        if (owner) {
+            T = owner[p];
         } else {
-            // a row that names the run more than once gets one flagged entry per target
-            int d_base = 0;
-            for (int i0 = 0; i0 < L; i0 += 32) {
-                const int i = i0 + lane;
-                const int code = i < L ? a[i] : 0;
-                const int row = i < L ? code / R : -1;
-                const int prow = (i > 0 && i < L) ? a[i - 1] / R : -1;
-                const int nrow = i + 1 < L ? a[i + 1] / R : -2;
-                const bool first = i < L && row != prow;
-                const unsigned mk = __ballot_sync(kFull, first);
-                if (first) {
-                    const int d = d_base + __popc(mk & ((1u << lane) - 1u));
-                    for (int q = 0; q < nq; ++q)
-                        ent[8 * b0 + q * L + d] = nrow == row ? (int)(kDupFlag | (unsigned)(row * m))
-                                                              : row * m + 8 * (code - row * R) + q;
-                }
-                d_base += __popc(mk);
+            int lo = 0, hi = ntiles - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (cur[mid] > p) hi = mid;
+                else lo = mid + 1;
             }
-            if (lane == 0)
-                for (int q = 0; q < nq; ++q) {
-                    rp[8 * T + q] = 8 * b0 + q * L;
-                    sl[8 * T + q] = d_base;
-                }
+            T = lo;
         }
-        if (lane == 0) tf[1 + T] = (!dup && nq == 8) ? kTileRuns : kTileGeneral;
+        const int L = cntM[T] & ~kSlowRun, b0 = cur[T] - L;
+        const unsigned code = placed[p];
+        const unsigned row = div_R(code), jr = code - row * (unsigned)R;
+        int rank = 0;
+        bool repeat = false;
+        for (int i = 0; i < L; ++i) {
+            const unsigned other = placed[b0 + i];
+            rank += other < code ? 1 : 0;
+            repeat = repeat || (other != code && div_R(other) == row);
+        }
+        if (repeat) atomicOr(&cntM[T], kSlowRun);
+        const int nq = min(8, nt - 8 * T);            // targets of this run that exist
+        const int e0 = (int)(row * (unsigned)m + 8u * jr);
+        int* dst = ent + 8 * (long long)b0 + rank;
+        for (int q = 0; q < nq; ++q) dst[q * L] = e0 + q;
+    }
+    }
+    __syncthreads();
+    // ---- per run: segment starts and lengths, the tile's flag; runs that some row names twice are redone
+    //      by a warp: sorted, with one flagged entry per such row and target
+    for (int T = tid; T < ntiles; T += kThreads) {
+        const int Lr = cntM[T], L = Lr & ~kSlowRun, b0 = cur[T] - L;
+        const int nq = min(8, nt - 8 * T);
+        for (int q = 0; q < nq; ++q) {
+            rp[8 * T + q] = 8 * b0 + q * L;
+            sl[8 * T + q] = L;
+        }
+        tf[1 + T] = (!(Lr & kSlowRun) && nq == 8) ? kTileRuns : kTileGeneral;
+        if (Lr & kSlowRun) {
+            const int slot = atomicAdd(&q_len, 1);
+            if (slot < kQueue) queue[slot] = T;
+        }
+    }
+    __syncthreads();
+    // (a table with more than kQueue such runs in one batch element is handled run by run)
+    const int nslow = q_len;
+    for (int qi = warp; qi < (nslow <= kQueue ? nslow : ntiles); qi += kWarps) {
+        const int T = nslow <= kQueue ? queue[qi] : qi;
+        if (!(cntM[T] & kSlowRun)) continue;
+        const int L = cntM[T] & ~kSlowRun, b0 = cur[T] - L;
+        unsigned short* a = placed + b0;
+        warp_sort_smem(a, L, lane);
+        const int nq = min(8, nt - 8 * T);
+        int d_base = 0;
+        for (int i0 = 0; i0 < L; i0 += 32) {
+            const int i = i0 + lane;
+            const unsigned code = i < L ? a[i] : 0u;
+            const int row = i < L ? (int)div_R(code) : -1;
+            const int prow = (i > 0 && i < L) ? (int)div_R(a[i - 1]) : -1;
+            const int nrow = i + 1 < L ? (int)div_R(a[i + 1]) : -2;
+            const bool first = i < L && row != prow;
+            const unsigned mk = __ballot_sync(kFull, first);
+            if (first) {
+                const int d = d_base + __popc(mk & ((1u << lane) - 1u));
+                for (int q = 0; q < nq; ++q)
+                    ent[8 * (long long)b0 + q * L + d] = nrow == row ? (int)(kDupFlag | (unsigned)(row * m))
+                                                                     : row * m + 8 * (int)(code - (unsigned)row * (unsigned)R) + q;
+            }
+            d_base += __popc(mk);
+        }
+        if (lane == 0)
+            for (int q = 0; q < nq; ++q) sl[8 * T + q] = d_base;
     }
     if (tid == 0) tf[0] = kBuildRuns;
 }
@@ -442,6 +560,9 @@ int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, 
     size_t smem = size_t(2 * nt + ntiles) * sizeof(int) + units2;
     const int with_owner = (nt <= 65535 && smem + units2 <= 200 * 1024) ? 1 : 0;
     if (with_owner) smem += units2;
+    const size_t per_warp_counts = size_t(kWarps) * ntiles * sizeof(int);
+    const int warp_counts = (m % 8 == 0 && smem + per_warp_counts <= 200 * 1024) ? 1 : 0;
+    if (warp_counts) smem += per_warp_counts;
     const bool possible = m <= 64 && smem <= 200 * 1024 && (long long)n_rows * m / 8 <= 65535 &&
                           (m % 8 == 0 || n_rows % 8 == 0);
     if (!possible) {
@@ -459,7 +580,7 @@ int launch_inverse_struct(const int64_t* idx, int b, int n_rows, int m, int nt, 
     unsigned m_magic, m_shift = 0;
     while ((1ull << m_shift) < (unsigned)m) ++m_shift;
     m_magic = (unsigned)(((1ull << 32) * ((1ull << m_shift) - (unsigned)m)) / (unsigned)m + 1);
-    kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, ntiles, kStructMaxPairs, m_magic, m_shift, with_owner, p, const_cast<int*>(v.rowptr),
+    kernel<<<b, kThreads, smem, s>>>(idx, n_rows, m, nt, ntiles, kStructMaxPairs, m_magic, m_shift, with_owner, warp_counts, p, const_cast<int*>(v.rowptr),
                                      const_cast<int*>(v.seglen), const_cast<int*>(v.entries), tf);
     note_launch();
     return check_launch();

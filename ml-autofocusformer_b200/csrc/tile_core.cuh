@@ -21,6 +21,7 @@ constexpr int kWLD = 52;           // row stride (floats) of the score tile
 constexpr int kOLD = 36;           // row stride (floats) of the output tile
 constexpr int kYLD = 36;           // row stride (floats) of the fp32 Y tile
 constexpr int kBMW = 256;          // bitmap words: token ids of a tile may span 8192
+constexpr int kDirectU = 144;      // more distinct neighbour rows than this in a tile: gather them unstaged
 constexpr int kWarps = 4;          // warps per CTA (independent of each other)
 constexpr int kEPL = kE / 32;      // edges per lane
 constexpr unsigned kFull = 0xffffffffu;

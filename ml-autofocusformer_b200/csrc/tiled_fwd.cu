@@ -27,6 +27,62 @@ namespace clusten {
 
 namespace {
 
+// Rows that share next to nothing (random tables): staging U rows in rounds of 48 costs more than it
+// saves.  Every lane takes one channel and walks the 8 x m edges of the tile directly: the neighbour rows
+// come from global memory (contiguous across the warp), the indices are still in the landing area, the
+// weights go through shared memory.  Kept out of line so that it does not weigh on the registers of the
+// staged path.
+template <typename T>
+__device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* Wd, const T* __restrict__ A,
+                                                 const T* __restrict__ X, T* __restrict__ out, int b, int heads,
+                                                 int n, int m, int i0, int lane) {
+    const int E = kT * m;
+    const int4* ring4 = reinterpret_cast<const int4*>(ring);
+    for (int g = 0; g < heads; ++g) {
+        const long long bb = (long long)b * heads + g;
+        const T* Xh = X + (bb * n) * kC + lane;
+        const T* Wt = A + (bb * n + i0) * m;
+        __syncwarp();
+        for (int x = lane; x < E; x += 32) {
+            const int q = x / m;
+            Wd[x] = i0 + q < n ? Elem<T>::up(Wt[x]) : 0.f;          // [8][m], row stride m
+        }
+        __syncwarp();
+        float accq[kT];
+#pragma unroll
+        for (int q = 0; q < kT; ++q) accq[q] = 0.f;
+        if ((m & 3) == 0) {
+#pragma unroll
+            for (int q = 0; q < kT; ++q) {
+                for (int j = 0; j < m; j += 4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(Wd + q * m + j);
+                    const int4 ta = ring4[(q * m + j) >> 1], tb = ring4[((q * m + j) >> 1) + 1];
+                    const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                    const int tl[4] = {ta.x, ta.z, tb.x, tb.z}, th[4] = {ta.y, ta.w, tb.y, tb.w};
+                    T xv[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const bool ok = th[e] == 0 && (unsigned)tl[e] < (unsigned)n;
+                        xv[e] = ok ? Xh[(long long)tl[e] * kC] : Elem<T>::down(0.f);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) accq[q] += wv[e] * Elem<T>::up(xv[e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < kT; ++q)
+                for (int j = 0; j < m; ++j) {
+                    const long long t = ring[q * m + j];
+                    if (t >= 0 && t < n) accq[q] += Wd[q * m + j] * Elem<T>::up(Xh[t * kC]);
+                }
+        }
+#pragma unroll
+        for (int q = 0; q < kT; ++q)
+            if (i0 + q < n) out[(bb * n + i0 + q) * kC + lane] = Elem<T>::down(accq[q]);
+    }
+}
+
 // ----------------------------------------------------------------------------- the kernel
 // MODE 0: tiled_sum (A = W [bb, n, m]),  MODE 1: tiled_dot (A = Y [bb, n, 32]); X = [bb, n, 32]
 // M48: m = 48 (every AutoFocusFormer stage but the last) is known at compile time
@@ -144,6 +200,20 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         // 16-bit inputs stay 16-bit (m16n8k16 products) unless a row repeats a neighbour: then the weights
         // of one slot are summed in fp32 and the fp32 path below is taken
         const bool native16 = !kIsFloat && !rowdup;
+
+        if (MODE == 0 && !identical && U > kDirectU) {
+            gather_sum_unstaged<T>(ring, Wd, A, X, out, b, heads, n, m, i0, lane);
+            // advance to this warp's next (batch, tile)
+            b = nb;
+            tile = ntile;
+            nb += step_b;
+            ntile += step_t;
+            if (ntile >= tiles) {
+                ntile -= tiles;
+                ++nb;
+            }
+            continue;
+        }
 
         for (int g = 0; g < heads; ++g) {
             const long long bb = (long long)b * heads + g;
@@ -474,8 +544,11 @@ scatter_tiles_kernel(const ScatterParams p) {
         start = 0;
         if (task < total) {
             const int b = (int)(task / (unsigned)p.tiles);
-            const int t = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT + lane;
-            if (lane < kT && t < n_tgt) {
+            const int tile = (int)(task - (unsigned)b * (unsigned)p.tiles);
+            const int t = tile * kT + lane;
+            if (p.skip_flagged && p.inv.tileflag[(long long)b * (1 + p.inv.ntiles) + 1 + tile] != kTileGeneral) {
+                len = -1;                                       // scatter_struct_kernel has this tile
+            } else if (lane < kT && t < n_tgt) {
                 len = p.inv.seglen[(long long)b * n_tgt + t];
                 start = p.inv.rowptr[(long long)b * (n_tgt + 1) + t];
             }
@@ -491,9 +564,7 @@ scatter_tiles_kernel(const ScatterParams p) {
         const int* entries = p.inv.entries + (long long)b * p.idx_rows * m;
         const int len = next_len, start = next_start;
         load_segment(task + nwarps, next_len, next_start);      // in flight while this tile is worked on
-        if (p.skip_flagged &&
-            p.inv.tileflag[(long long)b * (1 + p.inv.ntiles) + 1 + (t0 >> 3)] != kTileGeneral)
-            continue;                                           // scatter_struct_kernel has this tile
+        if (len < 0) continue;                                  // a structured tile (uniform over the warp)
         const int qlen = __shfl_sync(kFull, len, myq);          // entries of this lane's target
         const int* qent = entries + __shfl_sync(kFull, start, myq);
         int maxlen = len;
