@@ -90,7 +90,10 @@ CLUSTEN_API int clusten_timing_collect(char* buf, size_t buf_bytes);
  * reference's atomicAdd scatter (clusten/src/clustenqk_cuda_kernel.cu:125,
  * clustenav_cuda_kernel.cu:121, clustenwf_cuda_kernel.cu:129) and makes the
  * gradients bit-reproducible.  One inverse serves every backward call that
- * uses the same nbhd_idx tensor.
+ * uses the same nbhd_idx tensor.  The buffer also records, per tile of 8
+ * targets, whether the tile has one of the two shapes AutoFocusFormer's tables
+ * produce (the 8 tokens of a cluster share a row; or every row is made of whole
+ * clusters); the backward entry points use a leaner kernel on such tiles.
  *
  *   n_rows    rows of nbhd_idx per batch element (n for QK/AV, n_ for WF)
  *   n_targets number of tokens the indices point into (n)
@@ -145,8 +148,12 @@ CLUSTEN_API int clusten_av_backward(const void* d_feat, const void* attn, const 
  * makes no cudaMalloc / cudaFree and no allocating library call.  It is meant for
  * hosts that own all device memory themselves or run inside an engine's enqueue
  * callback and so have no buffer to pass and may not ask for one.
- * Limit: 64 + 2 * roundup64(b * (n + 1)) + roundup64(b * n * m) <= CLUSTEN_NOALLOC_MAX_INTS,
- * e.g. b = 16, n = 3136, m = 48; larger calls return CLUSTEN_ERR_NOALLOC_CAPACITY.
+ * Limit: clusten_inverse_bytes(b, n, m, n) <= 4 * CLUSTEN_NOALLOC_MAX_INTS, i.e.
+ * 64 + roundup64(b * (n + 1)) + roundup64(b * n) + roundup64(b * n * m) + roundup64(b * (1 + ceil(n / 8)))
+ * ints, e.g. b = 21, n = 3136, m = 48; larger calls return CLUSTEN_ERR_NOALLOC_CAPACITY.
+ * Every argument is checked before anything is launched, so a rejected call leaves the array and the
+ * outputs untouched.  The array's address is looked up once per device ordinal and kept for the life of the
+ * process: do not use this entry point after cudaDeviceReset.
  * The first call on a device looks up the array's device address (a little set-up
  * work: make that call before any stream capture).  All calls share the array, so
  * calls that overlap on the GPU race; serialise them on one stream.
