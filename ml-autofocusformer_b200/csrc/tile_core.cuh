@@ -461,9 +461,12 @@ struct DedupScratch {
 __device__ int dedup_tokens(const DedupScratch ps_, unsigned short* lut, int E, int m, bool want_rowdup,
                             bool* rowdup, int lane, int lo, int hi);
 
+// as_runs (optional): when the tile is made of aligned runs of 8 tokens, *as_runs is set and lut holds ONE slot
+// per run edge y = row * (m / 8) + run (the run's 8 tokens have slots 8 s .. 8 s + 7) instead of one per edge.
 __device__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigned short* lut, int E, int m, int i0,
-                          int n, bool want_rowdup, bool* rowdup, int lane, int n_src = -1) {
+                          int n, bool want_rowdup, bool* rowdup, int lane, int n_src = -1, bool* as_runs = nullptr) {
     if (n_src < 0) n_src = n;
+    if (as_runs) *as_runs = false;
     const DedupScratch* ps = &ps_;
     int lo = INT_MAX, hi = -1;
     // Tiles whose rows are made of aligned runs of 8 consecutive tokens (neighbourhoods built from whole
@@ -499,7 +502,12 @@ __device__ int dedup_tile(const DedupScratch ps_, const long long* ring, unsigne
 #pragma unroll
                     for (int r = 0; r < 8; ++r) ps->uniq[(lane + 32 * k) * 8 + r] = (unsigned short)(rid[k] * 8 + r);
                 }
-            for (int x = lane; x < E; x += 32) lut[x] = (unsigned short)(slot_r[x >> 3] * 8 + (x & 7));
+            if (as_runs) {
+                *as_runs = true;
+                for (int y = lane; y < R; y += 32) lut[y] = slot_r[y];
+            } else {
+                for (int x = lane; x < E; x += 32) lut[x] = (unsigned short)(slot_r[x >> 3] * 8 + (x & 7));
+            }
             __syncwarp();
             return UR * 8;
         }

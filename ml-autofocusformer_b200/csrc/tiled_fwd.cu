@@ -189,13 +189,28 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         __syncwarp();
         const bool identical = rows_identical(ring, E, m, n, complete, lane, col0, col_step);
         int U = m;
-        bool rowdup = false;
+        bool rowdup = false, runs = false;               // runs: lut holds one slot per run of 8 neighbours
         if (identical) {
             const int* ring32 = reinterpret_cast<const int*>(ring);
             for (int r = lane; r < m; r += 32) tok_s[r] = ring32[2 * r];
         } else {
-            U = dedup_tile(ds, ring, lut, E, m, i0, n, MODE == 0, &rowdup, lane);
+            U = dedup_tile(ds, ring, lut, E, m, i0, n, MODE == 0, &rowdup, lane, -1, &runs);
+            if (runs && rowdup) {
+                // a row names a run twice: its weights have to be added up, which the per-edge path does
+                unsigned short s[kEPL];
+#pragma unroll
+                for (int k = 0; k < kEPL; ++k) {
+                    const int x = lane + 32 * k;
+                    s[k] = x < E ? (unsigned short)(lut[x >> 3] * 8 + (x & 7)) : kSkip;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < kEPL; ++k)
+                    if (lane + 32 * k < E) lut[lane + 32 * k] = s[k];
+                runs = false;
+            }
         }
+        const int rpr = m >> 3;                          // runs per row (runs tiles have m % 8 == 0)
         __syncwarp();                                    // the landing area is free again
         // 16-bit inputs stay 16-bit (m16n8k16 products) unless a row repeats a neighbour: then the weights
         // of one slot are summed in fp32 and the fp32 path below is taken
@@ -293,6 +308,16 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                 Wd16[(z >> 3) * kWLD16 + m + (z & 7)] = Elem<T>::down(0.f);
                             }
                         }
+                    } else if (native16 && runs) {
+                        // a run's 8 weights of a row are 16 contiguous bytes, and so are its 8 slots
+                        for (int z = lane; z < kT * kWLD16 * 2 / 16; z += 32)
+                            reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        __syncwarp();
+                        for (int y = lane; y < kT * rpr; y += 32) {
+                            const int q = y / rpr, jr = y - q * rpr;
+                            const int rel = (int)lut[y] * 8 - u0;
+                            if (rel >= 0 && rel < Uc) cp_async16_ca(Wd16 + q * kWLD16 + rel, Wt + q * m + jr * 8);
+                        }
                     } else if (native16) {
                         for (int z = lane; z < kT * kWLD16 * 2 / 16; z += 32)
                             reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -317,6 +342,18 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                 if (kIsFloat) cp_async16_ca(dd, Wt + wq[k] * m + wc[k] * 4);
                                 else *reinterpret_cast<float4*>(dd) = ld4(Wt + wq[k] * m + wc[k] * 4);
                             }
+                    } else if (runs && kIsFloat) {
+                        for (int z = lane; z < kT * kWLD / 4; z += 32)
+                            reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        __syncwarp();
+                        for (int y = lane; y < kT * rpr; y += 32) {
+                            const int q = y / rpr, jr = y - q * rpr;
+                            const int rel = (int)lut[y] * 8 - u0;
+                            if (rel >= 0 && rel < Uc) {
+                                cp_async16_ca(Wd + q * kWLD + rel, Wt + q * m + jr * 8);
+                                cp_async16_ca(Wd + q * kWLD + rel + 4, Wt + q * m + jr * 8 + 4);
+                            }
+                        }
                     } else {
                         for (int z = lane; z < kT * kWLD / 4; z += 32)
                             reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -400,6 +437,16 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         for (int k = 0; k < 3; ++k)
                             if (lane + 32 * k < kT * m4)
                                 st4(Ot + wq[k] * m + wc[k] * 4, ld4(Sb + wq[k] * kWLD + wc[k] * 4));
+                    } else if (runs) {
+                        // the 8 scores of a run of neighbours are neighbours in the score tile and in the output
+                        for (int y = lane; y < kT * rpr; y += 32) {
+                            const int q = y / rpr, jr = y - q * rpr;
+                            const int rel = (int)lut[y] * 8 - u0;
+                            if (rel >= 0 && rel < Uc) {
+                                st4(Ot + q * m + jr * 8, ld4(Sb + q * kWLD + rel));
+                                st4(Ot + q * m + jr * 8 + 4, ld4(Sb + q * kWLD + rel + 4));
+                            }
+                        }
                     } else {
 #pragma unroll
                         for (int k = 0; k < kEPL; ++k) {

@@ -239,6 +239,52 @@ template <typename T, int ICT> __device__ __forceinline__ void store_w(T* p, con
     }
 }
 
+// Merge rows that share next to nothing (random tables): staging their distinct feature rows 32 at a time
+// costs more than it saves.  Every lane takes two channels of a 64-channel group and walks the 8 x m edges
+// directly: feature rows from global memory (contiguous across the warp), indices from the landing area,
+// weights as warp-wide broadcast loads.  Out of line, so that it does not weigh on the staged path's registers.
+// more distinct feature rows than this in a tile (of at most 384): gather them unstaged.  Measured break-even:
+// the staged path at about 170 distinct rows costs half of the unstaged one in fp32, less still for 16-bit
+// inputs (whose staged products are cheap)
+constexpr int kDirectUW = 288, kDirectUW16 = 352;
+template <typename T, int ICT>
+__device__ __noinline__ void wf_sum_unstaged(const long long* ring, const int* rowsS, const T* __restrict__ Wb,
+                                             const T* __restrict__ Fb, T* __restrict__ Ob, int n, int m, int c,
+                                             int lane) {
+    for (int q = 0; q < kT; ++q) {
+        const int rq = rowsS[q];
+        if (rq < 0) continue;
+        const T* wrow = Wb + (long long)rq * m * ICT;
+        for (int c0 = 0; c0 < c; c0 += kCG) {
+            const int ch = c0 + 2 * lane;
+            float acc[ICT][2];
+#pragma unroll
+            for (int k = 0; k < ICT; ++k) acc[k][0] = acc[k][1] = 0.f;
+#pragma unroll 4
+            for (int j = 0; j < m; ++j) {
+                const long long t = ring[q * m + j];
+                if (t >= 0 && t < n) {
+                    const T* fp = Fb + t * c + ch;
+                    const float x0 = Elem<T>::up(fp[0]), x1 = Elem<T>::up(fp[1]);
+                    float w[ICT];
+                    load_w<T, ICT>(wrow + j * ICT, w);
+#pragma unroll
+                    for (int k = 0; k < ICT; ++k) {
+                        acc[k][0] += w[k] * x0;
+                        acc[k][1] += w[k] * x1;
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < ICT; ++k) {
+                T* op = Ob + ((long long)rq * ICT + k) * c + ch;
+                op[0] = Elem<T>::down(acc[k][0]);
+                op[1] = Elem<T>::down(acc[k][1]);
+            }
+        }
+    }
+}
+
 // MODE 0: wf_sum, MODE 1: wf_dot.  ICT = ic (1, 2 or 4).  c must be a multiple of 64.
 // M48: m = 48 is known at compile time (every AutoFocusFormer merge table); C64: c = 64 (the first merge)
 template <typename T, int MODE, int ICT, bool M48, bool C64>
@@ -324,6 +370,11 @@ wf_tiles_kernel(const WfParams p) {
         __syncwarp();
         bool rowdup = false;
         const int U = dedup_tile(ds, ring, lut, E, m, 0, kT, MODE == 0, &rowdup, lane, n);
+        if (MODE == 0 && U > (kSplit ? kDirectUW : kDirectUW16)) {
+            wf_sum_unstaged<T, ICT>(ring, rowsS, static_cast<const T*>(p.W) + brow * m * ICT, Fg + (long long)b * n * c,
+                                    static_cast<T*>(p.out) + brow * ICT * c, n, m, c, lane);
+            continue;
+        }
         // ---- per edge of this lane: offset of its weights; tile row into lut
         int woff[kEPL];
         {
