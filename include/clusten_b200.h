@@ -116,6 +116,21 @@ CLUSTEN_API int clusten_inverse_build(const int64_t* nbhd_idx, int b, int n_rows
 CLUSTEN_API int clusten_qk_forward(const void* query, const void* key, const int64_t* nbhd_idx, void* attn,
                        int b, int h, int n, int m, int c, int dtype, void* stream);
 
+/* QK / AV forward on VIEWS.  The model hands query, key and value as permuted views of its Linear outputs
+ * (models/aff_transformer.py:117-119: element strides (n C, c, C, 1) and (n 2C, 2c, 2C, 1) with C = h c), and
+ * the reference copies each of them first (clusten/clusten.py:23-24,50).  These two entry points read them
+ * in place: *_strides = element strides of (batch, head, row); the c elements of a row are contiguous.
+ * attn (input of AV) and all outputs stay contiguous.  Requirements: the shapes of the tiled kernels
+ * (c = 32, m <= 48), every pointer and every stride a multiple of 16 bytes; otherwise
+ * CLUSTEN_ERR_UNSUPPORTED, and the caller copies and uses the contiguous entry point. */
+CLUSTEN_API int clusten_qk_forward_strided(const void* query, const long long* query_strides,
+                                           const void* key, const long long* key_strides,
+                                           const int64_t* nbhd_idx, void* attn,
+                                           int b, int h, int n, int m, int c, int dtype, void* stream);
+CLUSTEN_API int clusten_av_forward_strided(const void* attn, const void* value, const long long* value_strides,
+                                           const int64_t* nbhd_idx, void* feat,
+                                           int b, int h, int n, int m, int c, int dtype, void* stream);
+
 /* d_query[b,h,i,c] = sum_j key[b,h,idx,c] * d_attn[b,h,i,j]
  * d_key[b,h,t,c]   = sum_{(i,j): idx[b,i,j]==t} query[b,h,i,c] * d_attn[b,h,i,j]
  * replaces clusten_qk_backward (clustenqk_cuda.cpp:35-45, kernel :91-132).

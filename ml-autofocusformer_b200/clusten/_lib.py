@@ -24,6 +24,8 @@ SIGNATURES = {
     "clusten_inverse_bytes": (_sz, [_i, _i, _i, _i]),
     "clusten_inverse_build": (_i, [_p, _i, _i, _i, _i, _p, _sz, _p]),
     "clusten_qk_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "clusten_qk_forward_strided": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "clusten_av_forward_strided": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_qk_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),

@@ -5,9 +5,11 @@ clusten/clusten.py of apple/ml-autofocusformer (`CLUSTENQKFunction` :17-40,
 `CLUSTENAVFunction` :43-66, `CLUSTENWFFunction` :69-92), so that
 models/aff_transformer.py (:11, :120, :154, :361) imports this package
 unchanged.  As there, the second tensor is converted to the first tensor's
-dtype, inputs are made contiguous, and the index receives no gradient.
-Differences: bf16 is accepted, key is not transposed, and the scatter-side
-gradients are deterministic.
+dtype and the index receives no gradient.  Differences: bf16 is accepted, key
+is not transposed, the scatter-side gradients are deterministic, and the
+forward passes read query / key / value in place when they arrive as views with
+contiguous rows (the reference copies them, clusten/clusten.py:23-24,50); the
+backward passes copy such views, as the reference does.
 """
 from torch.autograd import Function
 
@@ -29,6 +31,13 @@ class CLUSTENQKFunction(Function):
 
     @staticmethod
     def forward(ctx, query, key, nbhd_idx):
+        nbhd_idx = nbhd_idx.contiguous()
+        if key.dtype == query.dtype:
+            # the model's query / key are permuted views of Linear outputs: read them where they are
+            attn = ops.qk_forward_views(query, key, nbhd_idx)
+            if attn is not None:
+                ctx.save_for_backward(query, key, nbhd_idx)
+                return attn
         query, key, nbhd_idx = _normalise(query, key, nbhd_idx)
         ctx.save_for_backward(query, key, nbhd_idx)
         return ops.qk_forward(query, key, nbhd_idx)
@@ -36,6 +45,7 @@ class CLUSTENQKFunction(Function):
     @staticmethod
     def backward(ctx, grad_attn):
         query, key, nbhd_idx = ctx.saved_tensors
+        query, key = query.contiguous(), key.contiguous()
         d_query, d_key = ops.qk_backward(grad_attn.contiguous().to(query.dtype), query, key, nbhd_idx)
         return d_query, d_key, None
 
@@ -45,6 +55,13 @@ class CLUSTENAVFunction(Function):
 
     @staticmethod
     def forward(ctx, attn, v, nbhd_idx):
+        nbhd_idx = nbhd_idx.contiguous()
+        attn = attn.contiguous()          # the [..., :-1] slice of the softmax output: rows of m + 1, copied
+        if v.dtype == attn.dtype:
+            feat = ops.av_forward_views(attn, v, nbhd_idx)     # v: a view of the kv Linear output, read in place
+            if feat is not None:
+                ctx.save_for_backward(attn, v, nbhd_idx)
+                return feat
         attn, v, nbhd_idx = _normalise(attn, v, nbhd_idx)
         ctx.save_for_backward(attn, v, nbhd_idx)
         return ops.av_forward(attn, v, nbhd_idx)
@@ -52,7 +69,7 @@ class CLUSTENAVFunction(Function):
     @staticmethod
     def backward(ctx, grad_feat):
         attn, v, nbhd_idx = ctx.saved_tensors
-        d_attn, d_v = ops.av_backward(grad_feat.contiguous().to(attn.dtype), attn, v, nbhd_idx)
+        d_attn, d_v = ops.av_backward(grad_feat.contiguous().to(attn.dtype), attn, v.contiguous(), nbhd_idx)
         return d_attn, d_v, None
 
 

@@ -189,6 +189,64 @@ def qk_forward(query, key, nbhd_idx):
     return attn
 
 
+def _row_view(t):
+    """Can the kernels read this [b, h, n, 32] tensor in place?  Rows contiguous, every other stride and the
+    base address a multiple of 16 bytes."""
+    es = t.element_size()
+    return (t.is_cuda and t.dim() == 4 and t.shape[3] == 32 and t.stride(3) == 1 and t.data_ptr() % 16 == 0
+            and all(s > 0 and (s * es) % 16 == 0 for s in t.stride()[:3]))
+
+
+def _strides3(t):
+    import ctypes
+    return (ctypes.c_longlong * 3)(*t.stride()[:3])
+
+
+def strided_forward_ok(a, b_, nbhd_idx):
+    """QK: both operands; AV: the value operand (attn must be contiguous) -- see qk/av_forward_views."""
+    return (a.dtype == b_.dtype and a.dtype in (torch.float32, torch.float16, torch.bfloat16)
+            and 1 <= nbhd_idx.shape[2] <= 48 and nbhd_idx.is_contiguous())
+
+
+def qk_forward_views(query, key, nbhd_idx):
+    """qk_forward on views of query and key (permuted Linear outputs): no copies.  None when the views do not
+    qualify (the caller then makes them contiguous)."""
+    if not (_row_view(query) and _row_view(key) and strided_forward_ok(query, key, nbhd_idx)):
+        return None
+    b, h, n, c = query.shape
+    m = nbhd_idx.shape[2]
+    if key.shape != query.shape or nbhd_idx.shape[:2] != (b, n) or nbhd_idx.dtype != torch.int64:
+        raise RuntimeError("clusten: QK shape mismatch")
+    attn = torch.empty((b, h, n, m), dtype=query.dtype, device=query.device)
+    with torch.cuda.device_of(query):
+        st = _lib.load().clusten_qk_forward_strided(query.data_ptr(), _strides3(query), key.data_ptr(), _strides3(key),
+                                                    nbhd_idx.data_ptr(), attn.data_ptr(), b, h, n, m, c, _dt(query),
+                                                    _stream(query))
+    if st == -6:
+        return None
+    _lib.check(st)
+    return attn
+
+
+def av_forward_views(attn, value, nbhd_idx):
+    """av_forward with value read in place through a view; attn must be contiguous.  None when not possible."""
+    if not (attn.is_contiguous() and _row_view(value) and strided_forward_ok(attn, value, nbhd_idx)):
+        return None
+    b, h, n, m = attn.shape
+    c = value.shape[3]
+    if value.shape[:3] != (b, h, n) or nbhd_idx.shape != (b, n, m) or nbhd_idx.dtype != torch.int64:
+        raise RuntimeError("clusten: AV shape mismatch")
+    feat = torch.empty((b, h, n, c), dtype=attn.dtype, device=attn.device)
+    with torch.cuda.device_of(attn):
+        st = _lib.load().clusten_av_forward_strided(attn.data_ptr(), value.data_ptr(), _strides3(value),
+                                                    nbhd_idx.data_ptr(), feat.data_ptr(), b, h, n, m, c, _dt(attn),
+                                                    _stream(attn))
+    if st == -6:
+        return None
+    _lib.check(st)
+    return feat
+
+
 def qk_backward(d_attn, query, key, nbhd_idx, inverse=None):
     _chk("d_attn", d_attn, query.dtype, 4)
     _chk("query", query, dim=4)

@@ -275,6 +275,52 @@ int clusten_qk_forward(const void* query, const void* key, const int64_t* nbhd_i
     return launch_gather_dot("qk_forward", dtype, key, query, nbhd_idx, attn, b * h, h, n, n, m, 1, c, s);
 }
 
+// element strides (batch, head, row) of a [b, h, n, c] view with contiguous rows -> usable by the tiled kernels?
+static bool view_ok(const void* p, const long long* st, int esize) {
+    if (!aligned(p, 16)) return false;
+    for (int i = 0; i < 3; ++i)
+        if (st[i] < 0 || (st[i] * esize) % 16 != 0) return false;
+    return st[2] > 0;
+}
+
+int clusten_qk_forward_strided(const void* query, const long long* query_strides, const void* key,
+                               const long long* key_strides, const int64_t* nbhd_idx, void* attn, int b, int h, int n,
+                               int m, int c, int dtype, void* stream) {
+    const int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(query, es);
+    CLUSTEN_REQUIRE_PTR(key, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(attn, es);
+    if (query_strides == nullptr || key_strides == nullptr) return CLUSTEN_ERR_NULL;
+    if (!tiled_dot_supported(dtype, query, key, attn, n, m, c) || !view_ok(query, query_strides, (int)es) ||
+        !view_ok(key, key_strides, (int)es))
+        return CLUSTEN_ERR_UNSUPPORTED;
+    GatherStrides gs{};
+    gs.x_batch = key_strides[0];  gs.x_head = key_strides[1];  gs.x_row = key_strides[2];
+    gs.y_batch = query_strides[0];  gs.y_head = query_strides[1];  gs.y_row = query_strides[2];
+    return launch_tiled_dot("qk_forward", dtype, key, query, nbhd_idx, attn, b, h, n, m, (cudaStream_t)stream, gs);
+}
+
+int clusten_av_forward_strided(const void* attn, const void* value, const long long* value_strides,
+                               const int64_t* nbhd_idx, void* feat, int b, int h, int n, int m, int c, int dtype,
+                               void* stream) {
+    const int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(attn, es);
+    CLUSTEN_REQUIRE_PTR(value, es);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(feat, es);
+    if (value_strides == nullptr) return CLUSTEN_ERR_NULL;
+    if (!tiled_sum_supported(dtype, attn, value, feat, n, m, c) || !view_ok(value, value_strides, (int)es))
+        return CLUSTEN_ERR_UNSUPPORTED;
+    GatherStrides gs{};
+    gs.x_batch = value_strides[0];  gs.x_head = value_strides[1];  gs.x_row = value_strides[2];
+    return launch_tiled_sum("av_forward", dtype, attn, value, nbhd_idx, feat, b, h, n, m, (cudaStream_t)stream, gs);
+}
+
 int clusten_qk_backward(const void* d_attn, const void* query, const void* key, const int64_t* nbhd_idx,
                         const void* inverse, void* d_query, void* d_key, int b, int h, int n, int m, int c,
                         int dtype, void* stream) {

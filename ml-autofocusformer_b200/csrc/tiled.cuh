@@ -4,15 +4,23 @@
 
 namespace clusten {
 
+// Element strides of the operands the gather kernels read through views: X (the gathered rows: key / value)
+// and, for the dot product, Y (the tile's own rows: query / d_feat).  Rows themselves are contiguous (32
+// elements).  Zero-initialised = the contiguous [b, h, n, 32] layout.
+struct GatherStrides {
+    long long x_batch, x_head, x_row;
+    long long y_batch, y_head, y_row;
+};
+
 // gather-sum:  out[b,h,i,:] = sum_j W[b,h,i,j] * X[b,h,idx[b,i,j],:]      (AV forward, d_query)
 bool tiled_sum_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c);
 int launch_tiled_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out, int b, int h, int n,
-                     int m, cudaStream_t s);
+                     int m, cudaStream_t s, const GatherStrides& gs = GatherStrides{});
 
 // gather-dot:  out[b,h,i,j] = <X[b,h,idx[b,i,j],:], Y[b,h,i,:]>           (QK forward, d_attn)
 bool tiled_dot_supported(int dtype, const void* Y, const void* X, const void* out, int n, int m, int c);
 int launch_tiled_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out, int b, int h, int n,
-                     int m, cudaStream_t s);
+                     int m, cudaStream_t s, const GatherStrides& gs = GatherStrides{});
 
 // scatter-sum: out[b,h,t,:] = sum_{idx[b,i,j]==t} W[b,h,i,j] * X[b,h,i,:]   (d_key, d_value)
 bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c);

@@ -35,12 +35,12 @@ namespace {
 template <typename T>
 __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* Wd, const T* __restrict__ A,
                                                  const T* __restrict__ X, T* __restrict__ out, int b, int heads,
-                                                 int n, int m, int i0, int lane) {
+                                                 int n, int m, int i0, int lane, const GatherStrides gs) {
     const int E = kT * m;
     const int4* ring4 = reinterpret_cast<const int4*>(ring);
     for (int g = 0; g < heads; ++g) {
         const long long bb = (long long)b * heads + g;
-        const T* Xh = X + (bb * n) * kC + lane;
+        const T* Xh = X + (long long)b * gs.x_batch + (long long)g * gs.x_head + lane;
         const T* Wt = A + (bb * n + i0) * m;
         __syncwarp();
         for (int x = lane; x < E; x += 32) {
@@ -63,7 +63,7 @@ __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* W
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const bool ok = th[e] == 0 && (unsigned)tl[e] < (unsigned)n;
-                        xv[e] = ok ? Xh[(long long)tl[e] * kC] : Elem<T>::down(0.f);
+                        xv[e] = ok ? Xh[(long long)tl[e] * gs.x_row] : Elem<T>::down(0.f);
                     }
 #pragma unroll
                     for (int e = 0; e < 4; ++e) accq[q] += wv[e] * Elem<T>::up(xv[e]);
@@ -74,7 +74,7 @@ __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* W
             for (int q = 0; q < kT; ++q)
                 for (int j = 0; j < m; ++j) {
                     const long long t = ring[q * m + j];
-                    if (t >= 0 && t < n) accq[q] += Wd[q * m + j] * Elem<T>::up(Xh[t * kC]);
+                    if (t >= 0 && t < n) accq[q] += Wd[q * m + j] * Elem<T>::up(Xh[t * gs.x_row]);
                 }
         }
 #pragma unroll
@@ -89,7 +89,7 @@ __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* W
 template <typename T, int MODE, bool M48>
 __global__ void __launch_bounds__(32 * kWarps, MODE == 0 ? 5 : 4)
 gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int64_t* __restrict__ idx,
-                    T* __restrict__ out, int batch, int heads, int n, int m_arg, int tiles) {
+                    T* __restrict__ out, int batch, int heads, int n, int m_arg, int tiles, const GatherStrides gs) {
     const int m = M48 ? kMmax : m_arg;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using WS = WarpSmem<T, MODE>;
@@ -167,9 +167,12 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                 if (lane * 16 < E) prefetch_l2(idx + ((long long)nb * n + ni0) * m + lane * 16);
                 const int arow = MODE == 0 ? m : kC;               // elements per row of A
                 const int abytes = kT * arow * (int)sizeof(T);
-                for (int g = 0; g < heads; ++g)
+                const bool a_contig = MODE == 0 || gs.y_row == kC;
+                for (int g = 0; g < heads && a_contig; ++g)
                     if (lane * 128 < abytes)
-                        prefetch_l2(reinterpret_cast<const char*>(A + (((long long)nb * heads + g) * n + ni0) * arow) +
+                        prefetch_l2(reinterpret_cast<const char*>(
+                                        MODE == 0 ? A + (((long long)nb * heads + g) * n + ni0) * arow
+                                                  : A + (long long)nb * gs.y_batch + (long long)g * gs.y_head + (long long)ni0 * gs.y_row) +
                                     lane * 128);
             }
         }
@@ -217,7 +220,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         const bool native16 = !kIsFloat && !rowdup;
 
         if (MODE == 0 && !identical && U > kDirectU) {
-            gather_sum_unstaged<T>(ring, Wd, A, X, out, b, heads, n, m, i0, lane);
+            gather_sum_unstaged<T>(ring, Wd, A, X, out, b, heads, n, m, i0, lane, gs);
             // advance to this warp's next (batch, tile)
             b = nb;
             tile = ntile;
@@ -232,7 +235,8 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
 
         for (int g = 0; g < heads; ++g) {
             const long long bb = (long long)b * heads + g;
-            const T* Xh = X + (bb * n) * kC;
+            const T* Xh = X + (long long)b * gs.x_batch + (long long)g * gs.x_head;
+            const int x_row = (int)gs.x_row;
             float acc[2][4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
@@ -252,7 +256,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
 #pragma unroll
                     for (int k = 0; k < kUC / 4; ++k)
                         if (qi + 4 * k < m)
-                            cp_async16_cg(dst + 4 * k * kC + ((k & 1) ? sw_odd : sw_even), Xl + (long long)tok_s[qi + 4 * k] * kC);
+                            cp_async16_cg(dst + 4 * k * kC + ((k & 1) ? sw_odd : sw_even), Xl + (long long)tok_s[qi + 4 * k] * x_row);
                 } else if (kIsFloat) {
 #pragma unroll
                     for (int k = 0; k < kUC / 4; ++k) {
@@ -267,7 +271,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                 }
                             }
                             float* dst = Xs + r * kC + ((k & 1) ? sw_odd : sw_even);
-                            if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * kC + ci * 4);
+                            if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * x_row + ci * 4);
                             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
@@ -287,7 +291,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                                 }
                             }
                             T* dst = Xraw + swz16(r, pc);
-                            if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * kC + pc * kPer);
+                            if (t >= 0) cp_async16_cg(dst, Xh + (long long)t * x_row + pc * kPer);
                             else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                     }
@@ -388,12 +392,12 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                     // ---- Y tile: the B fragments come straight from global memory (below)
                 } else if (ch == 0) {
                     // ---- Y tile -> Ys (fp32, row stride kYLD)
-                    const T* Yt = A + (bb * n + i0) * kC;
+                    const T* Yt = A + (long long)b * gs.y_batch + (long long)g * gs.y_head + (long long)i0 * gs.y_row;
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const int z = lane + 32 * k;
                         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (i0 + (z >> 3) < n) v = ld4(Yt + z * 4);
+                        if (i0 + (z >> 3) < n) v = ld4(Yt + (long long)(z >> 3) * gs.y_row + (z & 7) * 4);
                         *reinterpret_cast<float4*>(Ys + (z >> 3) * kYLD + (z & 7) * 4) = v;
                     }
                 }
@@ -419,7 +423,8 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         const int yg = lane >> 2, yt = lane & 3;
                         unsigned yb[2][2] = {{0u, 0u}, {0u, 0u}};
                         if (i0 + yg < n) {
-                            const unsigned* yrow = reinterpret_cast<const unsigned*>(A + (bb * n + i0 + yg) * kC);
+                            const unsigned* yrow = reinterpret_cast<const unsigned*>(
+                                A + (long long)b * gs.y_batch + (long long)g * gs.y_head + (long long)(i0 + yg) * gs.y_row);
 #pragma unroll
                             for (int ks = 0; ks < 2; ++ks) {
                                 yb[ks][0] = yrow[8 * ks + yt];
@@ -999,7 +1004,13 @@ bool gather_supported(int dtype, std::initializer_list<const void*> ptrs, int n,
 
 template <typename T, int MODE>
 int gather_tiles_t(const char* label, const void* A, const void* X, const int64_t* idx, void* out, int b, int h,
-                   int n, int m, cudaStream_t s) {
+                   int n, int m, cudaStream_t s, GatherStrides gs) {
+    if (gs.x_row == 0) {                       // contiguous [b, h, n, 32]
+        gs.x_batch = (long long)h * n * kC;  gs.x_head = (long long)n * kC;  gs.x_row = kC;
+    }
+    if (gs.y_row == 0) {
+        gs.y_batch = (long long)h * n * kC;  gs.y_head = (long long)n * kC;  gs.y_row = kC;
+    }
     const int tiles = (n + kT - 1) / kT;
     if ((long long)b * tiles > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
     const size_t smem = size_t(kWarps) * WarpSmem<T, MODE>::kTotal;
@@ -1011,7 +1022,7 @@ int gather_tiles_t(const char* label, const void* A, const void* X, const int64_
     const long long need = ((long long)b * tiles + kWarps - 1) / kWarps;
     if (grid > need) grid = need;
     ScopedKernelTimer timer(label, s);
-    kernel<<<(int)grid, 32 * kWarps, smem, s>>>((const T*)A, (const T*)X, idx, (T*)out, b, h, n, m, tiles);
+    kernel<<<(int)grid, 32 * kWarps, smem, s>>>((const T*)A, (const T*)X, idx, (T*)out, b, h, n, m, tiles, gs);
     note_launch();
     return check_launch();
 }
@@ -1061,11 +1072,11 @@ bool tiled_sum_supported(int dtype, const void* W, const void* X, const void* ou
     return gather_supported(dtype, {W, X, out}, n, m, c);
 }
 int launch_tiled_sum(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, void* out,
-                     int b, int h, int n, int m, cudaStream_t s) {
+                     int b, int h, int n, int m, cudaStream_t s, const GatherStrides& gs) {
     switch (dtype) {
-        case CLUSTEN_F32: return gather_tiles_t<float, 0>(label, W, X, idx, out, b, h, n, m, s);
-        case CLUSTEN_F16: return gather_tiles_t<__half, 0>(label, W, X, idx, out, b, h, n, m, s);
-        case CLUSTEN_BF16: return gather_tiles_t<__nv_bfloat16, 0>(label, W, X, idx, out, b, h, n, m, s);
+        case CLUSTEN_F32: return gather_tiles_t<float, 0>(label, W, X, idx, out, b, h, n, m, s, gs);
+        case CLUSTEN_F16: return gather_tiles_t<__half, 0>(label, W, X, idx, out, b, h, n, m, s, gs);
+        case CLUSTEN_BF16: return gather_tiles_t<__nv_bfloat16, 0>(label, W, X, idx, out, b, h, n, m, s, gs);
         default: return CLUSTEN_ERR_DTYPE;
     }
 }
@@ -1074,11 +1085,11 @@ bool tiled_dot_supported(int dtype, const void* Y, const void* X, const void* ou
     return gather_supported(dtype, {Y, X, out}, n, m, c);
 }
 int launch_tiled_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out,
-                     int b, int h, int n, int m, cudaStream_t s) {
+                     int b, int h, int n, int m, cudaStream_t s, const GatherStrides& gs) {
     switch (dtype) {
-        case CLUSTEN_F32: return gather_tiles_t<float, 1>(label, Y, X, idx, out, b, h, n, m, s);
-        case CLUSTEN_F16: return gather_tiles_t<__half, 1>(label, Y, X, idx, out, b, h, n, m, s);
-        case CLUSTEN_BF16: return gather_tiles_t<__nv_bfloat16, 1>(label, Y, X, idx, out, b, h, n, m, s);
+        case CLUSTEN_F32: return gather_tiles_t<float, 1>(label, Y, X, idx, out, b, h, n, m, s, gs);
+        case CLUSTEN_F16: return gather_tiles_t<__half, 1>(label, Y, X, idx, out, b, h, n, m, s, gs);
+        case CLUSTEN_BF16: return gather_tiles_t<__nv_bfloat16, 1>(label, Y, X, idx, out, b, h, n, m, s, gs);
         default: return CLUSTEN_ERR_DTYPE;
     }
 }

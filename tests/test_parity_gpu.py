@@ -531,3 +531,37 @@ def test_structured_tiles_with_irregularities(ops, case, dtype):
     ops.clear_inverse_cache()
     again = ops.av_backward(g_feat, attn, v, idx)[1]
     assert torch.equal(dv, again), "the summation order is fixed: same bits on a rebuilt inverse"
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=lambda d: str(d).split(".")[-1])
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+def test_forward_reads_model_style_views_in_place(ops, regime, dtype):
+    """query / key / value as the model hands them over (models/aff_transformer.py:117-119 of the reference:
+    permuted views of the q and kv Linear outputs) are read where they are: same bits as on contiguous copies,
+    and no copy is made (the strided entry points accept them)."""
+    b, h, n, m, c = 2, 4, 200, 48, 32
+    idx = workloads.make_index(regime, b, n, m, 370).to(DEV)
+    g = torch.Generator(device=DEV).manual_seed(371)
+    qlin = torch.randn(b, n, h * c, generator=g, device=DEV).to(dtype)
+    kvlin = torch.randn(b, n, 2 * h * c, generator=g, device=DEV).to(dtype)
+    q = qlin.reshape(b, n, h, c).permute(0, 2, 1, 3)
+    kv = kvlin.view(b, n, h, 2, c).permute(3, 0, 2, 1, 4)
+    key, v = kv[0], kv[1]
+    assert not q.is_contiguous() and not key.is_contiguous() and not v.is_contiguous()
+    attn = ops.qk_forward_views(q, key, idx)
+    assert attn is not None, "the views qualify: rows contiguous, strides multiples of 16 bytes"
+    assert torch.equal(attn, ops.qk_forward(q.contiguous(), key.contiguous(), idx))
+    assert_close(attn, exact("qk", "forward", q, key, idx), dtype, "qk forward on views")
+    probs = attn.float().softmax(-1).to(dtype)
+    feat = ops.av_forward_views(probs, v, idx)
+    assert feat is not None
+    assert torch.equal(feat, ops.av_forward(probs, v.contiguous(), idx))
+    assert_close(feat, exact("av", "forward", probs, v, idx), dtype, "av forward on a view")
+    # views that do not qualify are declined (the autograd operators then copy, like the reference)
+    assert ops.qk_forward_views(q[..., :16], key[..., :16], idx) is None
+    odd = torch.randn(b, h, n, c + 1, device=DEV).to(dtype)[..., 1:]          # rows start off a 16-byte boundary
+    assert ops.av_forward_views(probs, odd, idx) is None
+    # and the autograd operators give the same results either way
+    from clusten import CLUSTENAVFunction, CLUSTENQKFunction
+    assert torch.equal(CLUSTENQKFunction.apply(q, key, idx), attn)
+    assert torch.equal(CLUSTENAVFunction.apply(probs, v, idx), feat)
