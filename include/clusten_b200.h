@@ -131,6 +131,29 @@ CLUSTEN_API int clusten_av_forward_strided(const void* attn, const void* value, 
                                            const int64_t* nbhd_idx, void* feat,
                                            int b, int h, int n, int m, int c, int dtype, void* stream);
 
+/* Fused local attention, forward only (opt-in; the separate operators above remain the contract):
+ *   logits[b,h,i,j] = <query[b,h,i], key[b,h,idx[b,i,j]]> + pos_bias[b,h,i,j]            (pos_bias != NULL)
+ *                                                        + pe_table[pe_idx[b,i,j], h]     (pe_table != NULL)
+ *                                                        + (1 - mask[b,i,j]) * -100       (mask != NULL)
+ *   blank[b,h,i]    = <query[b,h,i], blank_k[h]>                                          (blank_k != NULL)
+ *   p = softmax over the m neighbours and the blank token
+ *   out[b,h,i,:]    = sum_j p[j] * value[b,h,idx[b,i,j],:] + p[blank] * blank_v[h,:]
+ * i.e. the chain of models/aff_transformer.py:120-155 (QK :120, position embedding :129-134, mask :136-137,
+ * blank token :140-141, softmax :142, AV :154, blank value :147,155) with the query already scaled (:104); the
+ * [b,h,n,m] attention tensor is never written.  query_strides / kv_strides: element strides (batch, head, row)
+ * of views with contiguous rows, or NULL for contiguous [b,h,n,c]; key and value share kv_strides (they are
+ * the two halves of the model's kv Linear output).  pe_table is [table_rows, h]; mask and pe_idx are int64
+ * [b,n,m]; blank_k / blank_v are [h, c].  Shapes of the tiled kernels only (c = 32, m <= 48), pointers of
+ * query / key / value / out / blank_* on 16-byte boundaries; otherwise CLUSTEN_ERR_UNSUPPORTED.
+ * The reference has no fused counterpart. */
+CLUSTEN_API int clusten_local_attention_forward(const void* query, const long long* query_strides,
+                                                const void* key, const void* value, const long long* kv_strides,
+                                                const int64_t* nbhd_idx,
+                                                const void* pos_bias, const void* pe_table, const int64_t* pe_idx,
+                                                int table_rows, const int64_t* mask,
+                                                const void* blank_k, const void* blank_v, void* out,
+                                                int b, int h, int n, int m, int c, int dtype, void* stream);
+
 /* d_query[b,h,i,c] = sum_j key[b,h,idx,c] * d_attn[b,h,i,j]
  * d_key[b,h,t,c]   = sum_{(i,j): idx[b,i,j]==t} query[b,h,i,c] * d_attn[b,h,i,j]
  * replaces clusten_qk_backward (clustenqk_cuda.cpp:35-45, kernel :91-132).

@@ -26,6 +26,8 @@ SIGNATURES = {
     "clusten_qk_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_qk_forward_strided": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_forward_strided": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "clusten_local_attention_forward": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p,
+                                            _i, _i, _i, _i, _i, _i, _p]),
     "clusten_qk_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_forward": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),

@@ -247,6 +247,51 @@ def av_forward_views(attn, value, nbhd_idx):
     return feat
 
 
+def local_attention_forward(query, key, value, nbhd_idx, pos_bias=None, pe_table=None, pe_idx=None, mask=None,
+                            blank_k=None, blank_v=None):
+    """Fused forward of the local attention chain (scores + position bias + mask + blank token + softmax +
+    output); see clusten_local_attention_forward in the header.  query must already be scaled.  query / key /
+    value may be views with contiguous rows (key and value with equal strides).  Inference only: no autograd."""
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        if not t.is_cuda or t.dim() != 4 or t.dtype != query.dtype:
+            raise RuntimeError(f"clusten: {name} must be a 4-d CUDA tensor of query's dtype")
+    _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+    b, h, n, c = query.shape
+    m = nbhd_idx.shape[2]
+    if key.shape != query.shape or value.shape != query.shape or nbhd_idx.shape[:2] != (b, n):
+        raise RuntimeError("clusten: local attention shape mismatch")
+    if not _row_view(query):
+        query = query.contiguous()
+    if not (_row_view(key) and _row_view(value) and key.stride() == value.stride()):
+        key, value = key.contiguous(), value.contiguous()
+    def opt(name, t, dtype, shape):
+        if t is None:
+            return None
+        _chk(name, t, dtype)
+        if tuple(t.shape) != shape:
+            raise RuntimeError(f"clusten: {name} must have shape {shape}, got {tuple(t.shape)}")
+        return t
+    pos_bias = opt("pos_bias", pos_bias, query.dtype, (b, h, n, m))
+    pe_idx = opt("pe_idx", pe_idx, torch.int64, (b, n, m))
+    mask = opt("mask", mask, torch.int64, (b, n, m))
+    blank_k = opt("blank_k", blank_k, query.dtype, (h, c))
+    blank_v = opt("blank_v", blank_v, query.dtype, (h, c))
+    rows = 0
+    if pe_table is not None:
+        _chk("pe_table", pe_table, query.dtype, 2)
+        if pe_table.shape[1] != h or pe_idx is None:
+            raise RuntimeError("clusten: pe_table must be [rows, heads] and come with pe_idx")
+        rows = pe_table.shape[0]
+    out = torch.empty((b, h, n, c), dtype=query.dtype, device=query.device)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device_of(query):
+        _lib.check(_lib.load().clusten_local_attention_forward(
+            query.data_ptr(), _strides3(query), key.data_ptr(), value.data_ptr(), _strides3(key), nbhd_idx.data_ptr(),
+            ptr(pos_bias), ptr(pe_table), ptr(pe_idx), rows, ptr(mask), ptr(blank_k), ptr(blank_v), out.data_ptr(),
+            b, h, n, m, c, _dt(query), _stream(query)))
+    return out
+
+
 def qk_backward(d_attn, query, key, nbhd_idx, inverse=None):
     _chk("d_attn", d_attn, query.dtype, 4)
     _chk("query", query, dim=4)

@@ -321,6 +321,39 @@ int clusten_av_forward_strided(const void* attn, const void* value, const long l
     return launch_tiled_sum("av_forward", dtype, attn, value, nbhd_idx, feat, b, h, n, m, (cudaStream_t)stream, gs);
 }
 
+int clusten_local_attention_forward(const void* query, const long long* query_strides, const void* key,
+                                    const void* value, const long long* kv_strides, const int64_t* nbhd_idx,
+                                    const void* pos_bias, const void* pe_table, const int64_t* pe_idx, int table_rows,
+                                    const int64_t* mask, const void* blank_k, const void* blank_v, void* out, int b,
+                                    int h, int n, int m, int c, int dtype, void* stream) {
+    const int st = check_attn_args(b, h, n, m, c, dtype);
+    if (st != CLUSTEN_OK) return st;
+    const int es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(query, 16);
+    CLUSTEN_REQUIRE_PTR(key, 16);
+    CLUSTEN_REQUIRE_PTR(value, 16);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(out, 16);
+    if (pos_bias && !aligned(pos_bias, es)) return CLUSTEN_ERR_ALIGN;
+    if ((pe_table == nullptr) != (pe_idx == nullptr)) return CLUSTEN_ERR_NULL;
+    if (pe_table && (!aligned(pe_table, es) || !aligned(pe_idx, 8) || table_rows <= 0)) return CLUSTEN_ERR_ALIGN;
+    if (mask && !aligned(mask, 8)) return CLUSTEN_ERR_ALIGN;
+    if ((blank_k == nullptr) != (blank_v == nullptr)) return CLUSTEN_ERR_NULL;
+    if (blank_k && (!aligned(blank_k, 16) || !aligned(blank_v, 16))) return CLUSTEN_ERR_ALIGN;
+    if (!fused_attention_supported(dtype, n, m, c)) return CLUSTEN_ERR_UNSUPPORTED;
+    GatherStrides gs{};
+    if (query_strides) {
+        if (!view_ok(query, query_strides, es)) return CLUSTEN_ERR_UNSUPPORTED;
+        gs.y_batch = query_strides[0];  gs.y_head = query_strides[1];  gs.y_row = query_strides[2];
+    }
+    if (kv_strides) {
+        if (!view_ok(key, kv_strides, es) || !view_ok(value, kv_strides, es)) return CLUSTEN_ERR_UNSUPPORTED;
+        gs.x_batch = kv_strides[0];  gs.x_head = kv_strides[1];  gs.x_row = kv_strides[2];
+    }
+    return launch_fused_attention(dtype, query, key, value, nbhd_idx, pos_bias, pe_table, pe_idx, table_rows, mask,
+                                  blank_k, blank_v, out, b, h, n, m, gs, (cudaStream_t)stream);
+}
+
 int clusten_qk_backward(const void* d_attn, const void* query, const void* key, const int64_t* nbhd_idx,
                         const void* inverse, void* d_query, void* d_key, int b, int h, int n, int m, int c,
                         int dtype, void* stream) {

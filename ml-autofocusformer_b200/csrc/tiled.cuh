@@ -22,6 +22,13 @@ bool tiled_dot_supported(int dtype, const void* Y, const void* X, const void* ou
 int launch_tiled_dot(const char* label, int dtype, const void* X, const void* Y, const int64_t* idx, void* out, int b, int h, int n,
                      int m, cudaStream_t s, const GatherStrides& gs = GatherStrides{});
 
+// fused local attention forward (fused_attn.cu): scores + bias + mask + blank token + softmax + output
+bool fused_attention_supported(int dtype, int n, int m, int c);
+int launch_fused_attention(int dtype, const void* q, const void* k, const void* v, const int64_t* idx, const void* bias,
+                           const void* table, const int64_t* pe_idx, int table_rows, const int64_t* mask,
+                           const void* blank_k, const void* blank_v, void* out, int b, int h, int n, int m,
+                           GatherStrides gs, cudaStream_t s);
+
 // scatter-sum: out[b,h,t,:] = sum_{idx[b,i,j]==t} W[b,h,i,j] * X[b,h,i,:]   (d_key, d_value)
 bool tiled_scatter_supported(int dtype, const void* W, const void* X, const void* out, int n, int m, int c);
 int launch_tiled_scatter(const char* label, int dtype, const void* W, const void* X, const int64_t* idx, const InverseView& inv,
