@@ -538,6 +538,23 @@ def config2_records(device, batch=256, dtype=torch.bfloat16, reps=12):
         t1.record()
         torch.cuda.synchronize()
         rec["chain_ms"] = round(t0.elapsed_time(t1) / reps, 4)
+        if m <= 48:
+            # the same chain in the fused kernel (scores + bias + softmax + output, attn never written)
+            def fused(i):
+                idx, q, k, v, bias = bufs[i % sets]
+                return ops.local_attention_forward(q, k, v, idx, pos_bias=bias)
+            for i in range(3):
+                fused(i)
+            torch.cuda.synchronize()
+            t0.record()
+            for i in range(reps):
+                fused(i)
+            t1.record()
+            torch.cuda.synchronize()
+            rec["fused_chain_ms"] = round(t0.elapsed_time(t1) / reps, 4)
+            chain_bytes = batch * (3 * h * n * 32 * s + h * n * m * s + n * m * 8 + h * n * 32 * s)
+            rec["fused_chain_MB"] = round(chain_bytes / 1e6, 1)
+            rec["fused_frac_of_hbm_peak"] = round(chain_bytes / rec["fused_chain_ms"] / 1e6 / peak, 3)
         for name, evs in timers.items():
             rec[name] = round(statistics.median(a.elapsed_time(b_) for a, b_ in evs), 4)
         ab = workloads.algorithmic_bytes("qk", "fwd", b=batch, h=h, n=n, m=m, c=32, s=s)
@@ -638,6 +655,27 @@ def model_records(device, world, barrier, reduce_max, warmup=50, steps=30, legs=
             rec["e2e_images_per_sec"] = world * e_steps * batch / (ms * 1e-3)
             rec["e2e_h2d_bytes_per_step"] = host.numel() * 4
             rec["e2e_d2h_bytes_per_step"] = out_host.numel() * 4
+            # the same model with ClusterAttention's local-attention chain done by the fused kernel (one method of
+            # the model replaced: reported beside the unmodified model's figure)
+            try:
+                aff_harness.use_fused_attention(True)
+                fused = aff_harness.forward(model, images[:2], dtype)
+                aff_harness.use_fused_attention(False)
+                plain = aff_harness.forward(model, images[:2], dtype)
+                rec["fused_logits_rel_err_vs_separate"] = ((fused.double() - plain.double()).abs().max()
+                                                           / plain.double().abs().max()).item()
+                aff_harness.use_fused_attention(True)
+                for _ in range(5):
+                    aff_harness.forward(model, images, dtype)
+                barrier()
+                t0.record()
+                for _ in range(steps):
+                    aff_harness.forward(model, images, dtype)
+                t1.record()
+                barrier()
+                rec["fused_attention_images_per_sec"] = world * steps * batch / (reduce_max(t0.elapsed_time(t1)) * 1e-3)
+            finally:
+                aff_harness.use_fused_attention(False)
             if with_reference and world == 1 and dname == "fp32" and aff_harness.reference_kernels_available():
                 # the same model on the reference's own kernels (compiled unmodified into oracle/_ref), same GPU
                 aff_harness.use_implementation("reference")

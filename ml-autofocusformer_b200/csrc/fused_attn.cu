@@ -42,7 +42,7 @@ struct FusedParams {
     void* out;                                       // [b, h, n, 32]
     int batch, heads, n, m, tiles;
     GatherStrides gs;                                // x: keys AND values (same strides), y: queries
-    long long v_offset_unused;
+    int bias_aligned;                                // bias starts on a 16-byte boundary and so does every [n, m] slab
 };
 
 template <typename T, bool M48>
@@ -75,7 +75,9 @@ fused_attention_kernel(const FusedParams p) {
     int* tok_s = reinterpret_cast<int*>(uniq);                // identical rows: source row of slot r
 
     const SumAddr sa = make_sum_addr(Wd, Xs, lane);
+    const SumAddr sa_p = make_sum_addr(P, Xs, lane);            // identical rows: the probability tile is the weight matrix
     const DotAddr da = make_dot_addr(Ys, Xs, Sb, lane);
+    const DotAddr da_p = make_dot_addr(Ys, Xs, P, lane);        // identical rows: slot = neighbour, scores land in P
     const int E = kT * m;
     const int col0 = (2 * lane) % m, col_step = 64 % m;
     unsigned long long qpack = 0ull;                          // 3 bits per edge of this lane: its row
@@ -165,12 +167,49 @@ fused_attention_kernel(const FusedParams p) {
         }
         __syncwarp();
         const int nchunks = U > 0 ? (U + kUC - 1) / kUC : 1;
+        // position-table index (bits 0..30; all ones = none) and mask bit (bit 31 = masked out) of every edge of
+        // this lane: the same for all heads, requested now so that they arrive while head 0 stages its rows
+        const int valid = min(kT, n - i0) * m;
+        unsigned pm[kEPL];
+        {
+            const int64_t* pe_t = p.table ? p.pe_idx + ((long long)b * n + i0) * m : nullptr;
+            const int64_t* mask_t = p.mask ? p.mask + ((long long)b * n + i0) * m : nullptr;
+#pragma unroll
+            for (int k = 0; k < kEPL; ++k) {
+                const int x = lane + 32 * k;
+                unsigned v = 0x7fffffffu;
+                if (x < valid) {
+                    if (pe_t) {
+                        const long long pi = pe_t[x];
+                        if (pi >= 0 && pi < p.table_rows) v = (unsigned)pi;
+                    }
+                    if (mask_t && mask_t[x] == 0) v |= 0x80000000u;
+                }
+                pm[k] = v;
+            }
+        }
+        // the tile's [8][m] rows of a dense bias are contiguous: they can travel as 16-byte pieces
+        const bool bias_async = p.bias != nullptr && complete && ((m * (int)sizeof(T)) & 15) == 0 && p.bias_aligned;
 
         for (int g = 0; g < heads; ++g) {
             const long long bh = (long long)b * heads + g;
             const T* Kh = Kg + (long long)b * p.gs.x_batch + (long long)g * p.gs.x_head;
             const T* Vh = Vg + (long long)b * p.gs.x_batch + (long long)g * p.gs.x_head;
             const T* Qt = Qg + (long long)b * p.gs.y_batch + (long long)g * p.gs.y_head + (long long)i0 * p.gs.y_row;
+            // 16-bit inputs: the query fragments of the score product come straight from global memory; requested
+            // here, they arrive while the key rows are staged
+            unsigned yb[2][2] = {{0u, 0u}, {0u, 0u}};
+            if (!kIsFloat) {
+                const int yg = lane >> 2, yt = lane & 3;
+                if (i0 + yg < n) {
+                    const unsigned* yrow = reinterpret_cast<const unsigned*>(Qt + (long long)yg * p.gs.y_row);
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks) {
+                        yb[ks][0] = yrow[8 * ks + yt];
+                        yb[ks][1] = yrow[8 * ks + 4 + yt];
+                    }
+                }
+            }
             // ================= scores =================
             float oreg[kEPL];
 #pragma unroll
@@ -179,6 +218,11 @@ fused_attention_kernel(const FusedParams p) {
                 const int u0 = ch * kUC;
                 const int Uc = max(0, min(kUC, U - u0));
                 __syncwarp();
+                if (ch == 0 && bias_async) {
+                    const T* bias_t = static_cast<const T*>(p.bias) + (bh * n + i0) * m;
+                    T* Bt = reinterpret_cast<T*>(Wd);           // [8 m] in edge order; the weight tile is free until the output phase
+                    for (int z = lane; z < E / kPer; z += 32) cp_async16_ca(Bt + z * kPer, bias_t + z * kPer);
+                }
                 stage(Kh, u0, Uc, identical, true);
                 if (kIsFloat && ch == 0) {
                     // the tile's query rows -> Ys (fp32, row stride kYLD)
@@ -192,31 +236,20 @@ fused_attention_kernel(const FusedParams p) {
                 }
                 cp_async_wait<0>();
                 __syncwarp();
+                float* Sdst = identical ? P : Sb;
                 if (kIsFloat) {
-                    dot_product_mma<true>(da, (Uc + 15) >> 4);
+                    dot_product_mma<true>(identical ? da_p : da, (Uc + 15) >> 4);
                 } else {
-                    const int yg = lane >> 2, yt = lane & 3;
-                    unsigned yb[2][2] = {{0u, 0u}, {0u, 0u}};
-                    if (i0 + yg < n) {
-                        const unsigned* yrow = reinterpret_cast<const unsigned*>(Qt + (long long)yg * p.gs.y_row);
-#pragma unroll
-                        for (int ks = 0; ks < 2; ++ks) {
-                            yb[ks][0] = yrow[8 * ks + yt];
-                            yb[ks][1] = yrow[8 * ks + 4 + yt];
-                        }
-                    }
-                    dot_product16<T>(Xraw, yb, Sb, (Uc + 15) >> 4, lane);
+                    dot_product16<T>(Xraw, yb, Sdst, (Uc + 15) >> 4, lane);
                 }
                 __syncwarp();
-                // every edge whose neighbour is in this round picks its score
+                // every edge whose neighbour is in this round picks its score (identical rows: already in place)
+                if (!identical) {
 #pragma unroll
-                for (int k = 0; k < kEPL; ++k) {
-                    const int x = lane + 32 * k;
-                    if (x < E) {
-                        const int q = (int)((qpack >> (3 * k)) & 7ull);
-                        if (identical) {
-                            if (ch == 0) oreg[k] = Sb[q * kWLD + (x - q * m)];
-                        } else {
+                    for (int k = 0; k < kEPL; ++k) {
+                        const int x = lane + 32 * k;
+                        if (x < E) {
+                            const int q = (int)((qpack >> (3 * k)) & 7ull);
                             const unsigned short sl = lut[x];
                             const int rel = (int)sl - u0;
                             if (sl != kSkip && rel >= 0 && rel < Uc) oreg[k] = Sb[q * kWLD + rel];
@@ -224,25 +257,32 @@ fused_attention_kernel(const FusedParams p) {
                     }
                 }
             }
-            // ================= logits: + bias, + mask; -> P[row][neighbour] =================
+            // the row buffer is free again: the first round of VALUE rows travels while the logits are finished
+            // and the softmax runs
             __syncwarp();
+            stage(Vh, 0, max(0, min(kUC, U)), identical, false);
+            // ================= logits: + bias, + mask; -> P[row][neighbour] =================
+            {
+                // the tile's rows of the bias are contiguous: element (row q, neighbour j) is x = q m + j
+                const T* bias_t = (p.bias && !bias_async) ? static_cast<const T*>(p.bias) + (bh * n + i0) * m : nullptr;
+                const T* Bt = reinterpret_cast<const T*>(Wd);
+                const T* table_g = static_cast<const T*>(p.table) + g;
 #pragma unroll
-            for (int k = 0; k < kEPL; ++k) {
-                const int x = lane + 32 * k;
-                if (x < E) {
-                    const int q = (int)((qpack >> (3 * k)) & 7ull);
-                    const int j = x - q * m;
-                    float lg = oreg[k];
-                    if (i0 + q < n) {
-                        const long long e = ((long long)b * n + i0 + q) * m + j;
-                        if (p.bias) lg += Elem<T>::up(static_cast<const T*>(p.bias)[(bh * n + i0 + q) * m + j]);
-                        if (p.table) {
-                            const long long pi = p.pe_idx[e];
-                            if (pi >= 0 && pi < p.table_rows) lg += Elem<T>::up(static_cast<const T*>(p.table)[pi * heads + g]);
+                for (int k = 0; k < kEPL; ++k) {
+                    const int x = lane + 32 * k;
+                    if (x < E) {
+                        const int q = (int)((qpack >> (3 * k)) & 7ull);
+                        const int j = x - q * m;
+                        float lg = identical ? P[q * kWLD + j] : oreg[k];
+                        if (x < valid) {
+                            if (bias_async) lg += Elem<T>::up(Bt[x]);
+                            else if (bias_t) lg += Elem<T>::up(bias_t[x]);
+                            const unsigned pi = pm[k] & 0x7fffffffu;
+                            if (p.table && pi != 0x7fffffffu) lg += Elem<T>::up(table_g[(long long)pi * heads]);
+                            if (pm[k] & 0x80000000u) lg -= 100.f;
                         }
-                        if (p.mask) lg += (1.f - (float)p.mask[e]) * -100.f;
+                        P[q * kWLD + j] = lg;
                     }
-                    P[q * kWLD + j] = lg;
                 }
             }
             // blank-token logit of row srow: <query, blank_k>, 8 channels per lane
@@ -291,9 +331,14 @@ fused_attention_kernel(const FusedParams p) {
                 const int Uc = max(0, min(kUC, U - u0));
                 const int rows8 = (Uc + 7) & ~7;
                 __syncwarp();
-                stage(Vh, u0, Uc, identical, false);
-                // ---- dense probabilities of this round, by slot
-                if (kIsFloat) {
+                if (ch > 0) stage(Vh, u0, Uc, identical, false);
+                // ---- dense probabilities of this round, by slot (identical rows in fp32: the probability tile
+                //      itself is that matrix, slot = neighbour)
+                const bool p_is_wd = kIsFloat && identical;
+                if (p_is_wd) {
+                    // columns m .. 47 of P are never written by the softmax: the product must not see stale values
+                    for (int z = lane; z < kT * (kUC - m); z += 32) P[(z / (kUC - m)) * kWLD + m + z % (kUC - m)] = 0.f;
+                } else if (kIsFloat) {
                     for (int z = lane; z < kT * kWLD / 4; z += 32)
                         reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                 } else {
@@ -301,7 +346,8 @@ fused_attention_kernel(const FusedParams p) {
                         reinterpret_cast<float4*>(Wd16)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
                 __syncwarp();
-                if (identical || !rowdup) {
+                if (p_is_wd) {
+                } else if (identical || !rowdup) {
 #pragma unroll
                     for (int k = 0; k < kEPL; ++k) {
                         const int x = lane + 32 * k;
@@ -339,7 +385,7 @@ fused_attention_kernel(const FusedParams p) {
                 }
                 cp_async_wait<0>();
                 __syncwarp();
-                if (kIsFloat) sum_product_mma<true>(sa, rows8, acc);
+                if (kIsFloat) sum_product_mma<true>(p_is_wd ? sa_p : sa, rows8, acc);
                 else sum_product16<T>(Xraw, Wd16, (Uc + 15) >> 4, lane, acc);
             }
             // D fragments -> output tile in the score tile -> + blank probability x blank value -> 16-byte stores
@@ -414,6 +460,8 @@ int launch_fused_attention(int dtype, const void* q, const void* k, const void* 
     p.q = q;  p.k = k;  p.v = v;  p.idx = idx;  p.bias = bias;  p.table = table;  p.pe_idx = pe_idx;
     p.table_rows = table_rows;  p.mask = mask;  p.blank_k = blank_k;  p.blank_v = blank_v;  p.out = out;
     p.batch = b;  p.heads = h;  p.n = n;  p.m = m;  p.gs = gs;
+    p.bias_aligned = bias != nullptr && reinterpret_cast<uintptr_t>(bias) % 16 == 0 &&
+                     ((long long)n * m * dtype_size(dtype)) % 16 == 0;
     switch (dtype) {
         case CLUSTEN_F32: return fused_t<float>(p, s);
         case CLUSTEN_F16: return fused_t<__half>(p, s);

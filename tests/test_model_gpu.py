@@ -65,3 +65,27 @@ def test_logits_match_the_reference_kernels(lib, capsys):
     with capsys.disabled():
         print(f"\ntiny224 fp32 vs the reference's kernels: logits rel err {err:.2e}")
     assert err <= 1e-4, err
+
+
+@pytest.mark.parametrize("config,batch,dtype,tol", [("tiny224", 4, torch.float32, 1e-4), ("base384", 2, torch.bfloat16, 5e-2)],
+                         ids=["tiny224-fp32", "base384-bf16"])
+def test_fused_attention_variant_of_the_model(lib, config, batch, dtype, tol, capsys):
+    """ClusterAttention routed through the fused local-attention kernel (an opt-in that replaces one method of
+    the reference's model): same logits as the unmodified model on the gather formulation."""
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    aff_harness.use_implementation("b200")
+    model = aff_harness.build_model(config, DEV, seed=0)
+    x = aff_harness.synthetic_images(config, batch, DEV, seed=1)
+    try:
+        aff_harness.use_fused_attention(True)
+        got = aff_harness.forward(model, x, dtype)
+    finally:
+        aff_harness.use_fused_attention(False)
+    aff_harness.use_implementation("formula", formula_chunk=1)
+    want = aff_harness.forward(model, x, dtype)
+    aff_harness.use_implementation("b200")
+    err = _rel(got, want)
+    with capsys.disabled():
+        print(f"\n{config} {dtype} fused attention: logits rel err {err:.2e}")
+    assert err <= tol, err
