@@ -243,6 +243,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
             float oreg[kEPL];
 #pragma unroll
             for (int k = 0; k < kEPL; ++k) oreg[k] = 0.f;
+            unsigned yb16[2][2] = {{0u, 0u}, {0u, 0u}};     // MODE 1, 16-bit inputs: B fragments of the tile's Y rows
             const int nchunks = U > 0 ? (U + kUC - 1) / kUC : 1;
             for (int ch = 0; ch < nchunks; ++ch) {
                 const int u0 = ch * kUC;
@@ -389,7 +390,21 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                         }
                     }
                 } else if (native16) {
-                    // ---- Y tile: the B fragments come straight from global memory (below)
+                    // ---- Y tile: the B fragments come straight from global memory, requested here so that they
+                    //      arrive together with the staged rows
+                    if (ch == 0) {
+                        const int yg = lane >> 2, yt = lane & 3;
+                        yb16[0][0] = yb16[0][1] = yb16[1][0] = yb16[1][1] = 0u;
+                        if (i0 + yg < n) {
+                            const unsigned* yrow = reinterpret_cast<const unsigned*>(
+                                A + (long long)b * gs.y_batch + (long long)g * gs.y_head + (long long)(i0 + yg) * gs.y_row);
+#pragma unroll
+                            for (int ks = 0; ks < 2; ++ks) {
+                                yb16[ks][0] = yrow[8 * ks + yt];
+                                yb16[ks][1] = yrow[8 * ks + 4 + yt];
+                            }
+                        }
+                    }
                 } else if (ch == 0) {
                     // ---- Y tile -> Ys (fp32, row stride kYLD)
                     const T* Yt = A + (long long)b * gs.y_batch + (long long)g * gs.y_head + (long long)i0 * gs.y_row;
@@ -420,18 +435,7 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
                     else sum_product_mma<kIsFloat>(sa, rows8, acc);
                 } else {
                     if (native16) {
-                        const int yg = lane >> 2, yt = lane & 3;
-                        unsigned yb[2][2] = {{0u, 0u}, {0u, 0u}};
-                        if (i0 + yg < n) {
-                            const unsigned* yrow = reinterpret_cast<const unsigned*>(
-                                A + (long long)b * gs.y_batch + (long long)g * gs.y_head + (long long)(i0 + yg) * gs.y_row);
-#pragma unroll
-                            for (int ks = 0; ks < 2; ++ks) {
-                                yb[ks][0] = yrow[8 * ks + yt];
-                                yb[ks][1] = yrow[8 * ks + 4 + yt];
-                            }
-                        }
-                        dot_product16<T>(Xraw, yb, Sb, (Uc + 15) >> 4, lane);
+                        dot_product16<T>(Xraw, yb16, Sb, (Uc + 15) >> 4, lane);
                     } else {
                         dot_product_mma<kIsFloat>(da, (Uc + 15) >> 4);
                     }
