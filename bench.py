@@ -674,8 +674,25 @@ def model_records(device, world, barrier, reduce_max, warmup=50, steps=30, legs=
                 t1.record()
                 barrier()
                 rec["fused_attention_images_per_sec"] = world * steps * batch / (reduce_max(t0.elapsed_time(t1)) * 1e-3)
+                # ... and every stage's neighbourhood tables and merge weights built by one kernel each (two more
+                # methods replaced)
+                aff_harness.use_fused_neighbourhood(True)
+                aff_harness.use_fused_merging(True)
+                both = aff_harness.forward(model, images[:2], dtype)
+                rec["fused_tables_logits_rel_err_vs_separate"] = ((both.double() - plain.double()).abs().max()
+                                                                  / plain.double().abs().max()).item()
+                for _ in range(5):
+                    aff_harness.forward(model, images, dtype)
+                barrier()
+                t0.record()
+                for _ in range(steps):
+                    aff_harness.forward(model, images, dtype)
+                t1.record()
+                barrier()
+                rec["fused_attention_tables_merging_images_per_sec"] = (world * steps * batch
+                                                                        / (reduce_max(t0.elapsed_time(t1)) * 1e-3))
             finally:
-                aff_harness.use_fused_attention(False)
+                aff_harness.use_fused(False)
             if with_reference and world == 1 and dname == "fp32" and aff_harness.reference_kernels_available():
                 # the same model on the reference's own kernels (compiled unmodified into oracle/_ref), same GPU
                 aff_harness.use_implementation("reference")

@@ -246,6 +246,41 @@ CLUSTEN_API int clusten_wf_backward(const void* d_feat_new, const void* weights,
 CLUSTEN_API int clusten_knn2d(const float* query, const float* database, int b, int n_query, int n, int k,
                               int64_t* nn_idx, float* nn_dist, void* stream);
 
+/* ------------------------------------------------------------------------
+ * Neighbourhood tables of a stage in one pass: for token i, nearest cluster
+ * r < nnc and member s < cs (slot j = r * cs + s), with
+ * c = nearest_cluster[b,i,r] and t = member_idx[b,c,s]:
+ *   nbhd_idx[b,i,j]  = t
+ *   nbhd_mask[b,i,j] = cluster_mask[b,c,s]      (cluster_mask and nbhd_mask both given or both NULL)
+ *   pe_idx[b,i,j]    = (int64)(rel.y * table_width + rel.x),
+ *                      rel = pos[b,t] - (pos[b,i] - rel_pos_width), evaluated in fp32 in this order
+ * replaces the three gathers and the elementwise arithmetic of BasicLayer.forward
+ * (models/aff_transformer.py:476-487).  pos fp32 [b,n,2]; member_idx, cluster_mask
+ * int64 [b,k,cs]; nearest_cluster int64 [b,n,nnc]; outputs int64 [b,n,nnc*cs].
+ * A cluster id outside [0,k) gives nbhd_idx -1, mask 0 and pe_idx 0 for its cs
+ * slots; a member outside [0,n) is passed through with pe_idx 0 (the reference's
+ * gather is undefined for both).
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API int clusten_nbhd_build(const float* pos, const int64_t* member_idx, const int64_t* cluster_mask,
+                                   const int64_t* nearest_cluster, int64_t* nbhd_idx, int64_t* nbhd_mask,
+                                   int64_t* pe_idx, int b, int n, int k, int cs, int nnc, int rel_pos_width,
+                                   int table_width, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Merge weights of ClusterMerging in one pass:
+ *   weights[b,i,j,:] = weights_table[pe_idx[b,i,j],:] * (learned_prob[b, nbhd_idx[b,i,j]] * nbhd_mask[b,i,j])
+ * replaces the table gather, the score gather and the elementwise products of
+ * models/aff_transformer.py:340-358; the result is CLUSTENWF's first argument.
+ * weights_table [table_rows, ic], learned_prob [b, n] (NULL = 1) and weights
+ * [b, n_out, m, ic] share `dtype` (fp32 / fp16 / bf16); pe_idx, nbhd_idx and
+ * nbhd_mask (NULL = 1) are int64 [b, n_out, m]; nbhd_idx is only read when
+ * learned_prob is given.  A table row or a token out of range gives zero
+ * weights (the reference's gathers are undefined there).
+ * ---------------------------------------------------------------------- */
+CLUSTEN_API int clusten_merge_weights(const void* weights_table, const int64_t* pe_idx, const void* learned_prob,
+                                      const int64_t* nbhd_idx, const int64_t* nbhd_mask, void* weights, int b,
+                                      int n_out, int n, int m, int ic, int table_rows, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

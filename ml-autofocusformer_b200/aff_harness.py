@@ -30,6 +30,7 @@ Configurations (BASELINE configs 3 and 4):
 import importlib
 import importlib.machinery
 import importlib.util
+import math
 import os
 import sys
 import types
@@ -252,6 +253,125 @@ def use_fused_attention(on=True):
     if _original_attention_forward is None:
         _original_attention_forward = aff.ClusterAttention.forward
     aff.ClusterAttention.forward = _fused_cluster_attention_forward if on else _original_attention_forward
+
+
+_original_layer_forward = None
+
+
+def _fused_basic_layer_forward(self, pos, feat, h, w, on_grid, stride):
+    """BasicLayer.forward (models/aff_transformer.py:428-505 of the reference) with the stage's neighbourhood
+    tables -- members of the nearest clusters :479, their mask :481-482, offsets and position-table rows
+    :483-487 -- built by one call of the library instead of three gathers and the arithmetic between them.
+    Clustering, the nearest-cluster search, the blocks and the merge are the reference's; stages with global
+    attention or one-token clusters keep the original code."""
+    b, n, d = pos.shape
+    cs = self.cluster_size
+    k = int(math.ceil(n / float(cs)))
+    if self.nbhd_size >= n or k == n or d != 2 or pos.dtype != torch.float32:
+        return _original_layer_forward(self, pos, feat, h, w, on_grid, stride)
+    from clusten import ops
+    aff = model_module()
+    c = feat.shape[2]
+    nnc = min(int(round(self.nbhd_size / float(cs))), k)
+    self.nbhd_size = cs * nnc
+    if on_grid:
+        # the first feature map is the same grid for every image: clustered once, kept on the layer
+        if self.cluster_mean_pos is None:
+            (self.pos, self.cluster_mean_pos, self.member_idx, self.cluster_mask,
+             self.reorder) = aff.space_filling_cluster(pos, cs, h, w, no_reorder=False)
+        pos, means, members, reorder = self.pos[:b], self.cluster_mean_pos[:b], self.member_idx[:b], self.reorder[:b]
+        cmask = None if self.cluster_mask is None else self.cluster_mask[:b]
+    else:
+        pos, means, members, cmask, reorder = aff.space_filling_cluster(pos, cs, h, w, no_reorder=False)
+    feat = feat.gather(1, reorder.reshape(b, n, 1).expand(-1, -1, c))     # the tokens of a cluster side by side
+    nearest = aff.knn_keops(pos, means, nnc)
+    member_idx, cluster_mask, pe_idx = ops.nbhd_build(
+        pos.contiguous(), members.contiguous(), None if cmask is None else cmask.contiguous(), nearest.contiguous(),
+        aff.rel_pos_width, aff.table_width)
+    for blk in self.blocks:
+        feat = blk(feat=feat, member_idx=member_idx, cluster_mask=cluster_mask, pe_idx=pe_idx, global_attn=False)
+    if self.downsample is not None:
+        learned_prob = self.prob_net(feat).sigmoid()
+        reserve_num = math.ceil(h / (stride * 2)) * math.ceil(w / (stride * 2))
+        pos, feat = self.downsample(pos=pos, feat=feat, member_idx=member_idx, cluster_mask=cluster_mask,
+                                    learned_prob=learned_prob, stride=stride, pe_idx=pe_idx, reserve_num=reserve_num)
+    return pos, feat
+
+
+def use_fused_neighbourhood(on=True):
+    """Opt-in: build every stage's neighbourhood tables with clusten_nbhd_build.  Like use_fused_attention this
+    replaces one method of the reference's model; its figures are reported beside the unmodified model's."""
+    global _original_layer_forward
+    aff = model_module()
+    if _original_layer_forward is None:
+        _original_layer_forward = aff.BasicLayer.forward
+    aff.BasicLayer.forward = _fused_basic_layer_forward if on else _original_layer_forward
+
+
+_original_merging_forward = None
+
+
+def _fused_cluster_merging_forward(self, pos, feat, member_idx, cluster_mask, learned_prob, stride, pe_idx,
+                                   reserve_num):
+    """ClusterMerging.forward (models/aff_transformer.py:276-365 of the reference) with the merge weights --
+    table rows by pe_idx :347-350, importance scores of the neighbours :340, mask and products :352-358 --
+    formed by one call of the library.  Choosing the merge centres (:294-331) and everything after CLUSTENWF
+    are the reference's computation, restated."""
+    from clusten import ops
+    aff = model_module()
+    b, n, c = feat.shape
+    d = pos.shape[2]
+    keep = int(n * self.ds_rate)
+    # ---- merge centres: tokens on the (adaptive) coarse lattice first, then by importance score
+    if stride == 2:
+        on_lattice = ((pos % stride).sum(-1) == 0).float()
+    else:
+        _, spacing = aff.knn_keops(pos, pos, 2, return_dist=True)
+        spacing = 2 ** (spacing[:, :, 1].log2().ceil() + 1)
+        on_lattice = ((pos.long() % spacing.unsqueeze(2).long()).sum(-1) == 0).float()
+    score = on_lattice
+    if learned_prob is not None:
+        score = score + learned_prob.detach().view(b, n) * self.alpha
+    if self.reserve_on:
+        reserved = ((pos % (stride * 2)).sum(-1) == 0).float()
+        score = score + reserved * (-100)
+        picked = score.topk(keep - reserve_num, dim=1, sorted=False)[1]
+        centres = torch.cat([picked, reserved.nonzero(as_tuple=True)[1].reshape(b, reserve_num)], dim=-1)
+    else:
+        centres = score.topk(keep, dim=1, sorted=False)[1]
+    if centres.shape[1] != keep:
+        raise RuntimeError("the number of merge centres differs from the number of tokens to keep")
+    # ---- the centres' rows of the stage's tables
+    row = centres.unsqueeze(2)
+    m = member_idx.shape[-1]
+    pos = pos.gather(1, row.expand(-1, -1, d))
+    member_idx = member_idx.gather(1, row.expand(-1, -1, m))
+    pe_idx = pe_idx.gather(1, row.expand(-1, -1, m))
+    if cluster_mask is not None:
+        cluster_mask = cluster_mask.gather(1, row.expand(-1, -1, m))
+    # ---- merge weights, merge, projection
+    if not aff.pre_table.is_cuda:
+        aff.pre_table = aff.pre_table.to(pe_idx.device)
+    weights = ops.merge_weights(self.weight_net(aff.pre_table), pe_idx, learned_prob, member_idx, cluster_mask)
+    feat = aff.CLUSTENWFFunction.apply(weights, feat, member_idx).reshape(b, keep, -1)
+    return pos, self.linear(self.norm(feat))
+
+
+def use_fused_merging(on=True):
+    """Opt-in: form ClusterMerging's weights with clusten_merge_weights (one method of the reference's model
+    replaced; figures reported beside the unmodified model's)."""
+    global _original_merging_forward
+    aff = model_module()
+    if _original_merging_forward is None:
+        _original_merging_forward = aff.ClusterMerging.forward
+    aff.ClusterMerging.forward = _fused_cluster_merging_forward if on else _original_merging_forward
+
+
+def use_fused(on=True):
+    """All three opt-ins together: fused attention, neighbourhood tables and merge weights from the library."""
+    use_fused_attention(on)
+    use_fused_neighbourhood(on)
+    use_fused_merging(on)
 
 
 def build_model(config, device, seed=0):

@@ -33,6 +33,8 @@ SIGNATURES = {
     "clusten_av_backward": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_av_backward_noalloc": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_knn2d": (_i, [_p, _p, _i, _i, _i, _i, _p, _p, _p]),
+    "clusten_nbhd_build": (_i, [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
+    "clusten_merge_weights": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),
     "clusten_wf_order_bytes": (_sz, [_i, _i]),
     "clusten_wf_order_build": (_i, [_p, _i, _i, _i, _p, _sz, _p]),
     "clusten_wf_forward": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p]),

@@ -172,6 +172,70 @@ def knn2d(query, database, k, return_dist=False):
     return (nn_idx, nn_dist) if return_dist else nn_idx
 
 
+def nbhd_build(pos, member_idx, cluster_mask, nearest_cluster, rel_pos_width, table_width):
+    """(nbhd_idx, nbhd_mask or None, pe_idx), each int64 [b, n, nnc * cs]: the members of every token's
+    nearest clusters, their mask bits, and their offsets' rows in the position-embedding table
+    (models/aff_transformer.py:476-487 of the reference in one kernel).  pos fp32 [b, n, 2];
+    member_idx / cluster_mask int64 [b, k, cs]; nearest_cluster int64 [b, n, nnc]."""
+    _chk("pos", pos, torch.float32, 3)
+    _chk("member_idx", member_idx, torch.int64, 3)
+    _chk("nearest_cluster", nearest_cluster, torch.int64, 3)
+    b, n, d = pos.shape
+    _, k, cs = member_idx.shape
+    nnc = nearest_cluster.shape[2]
+    if d != 2 or member_idx.shape[0] != b or nearest_cluster.shape[:2] != (b, n):
+        raise RuntimeError("clusten: nbhd_build shape mismatch")
+    if cluster_mask is not None:
+        _chk("cluster_mask", cluster_mask, torch.int64, 3)
+        if cluster_mask.shape != member_idx.shape:
+            raise RuntimeError("clusten: cluster_mask must have member_idx's shape")
+    m = nnc * cs
+    nbhd_idx = torch.empty((b, n, m), dtype=torch.int64, device=pos.device)
+    pe_idx = torch.empty((b, n, m), dtype=torch.int64, device=pos.device)
+    nbhd_mask = torch.empty((b, n, m), dtype=torch.int64, device=pos.device) if cluster_mask is not None else None
+    with torch.cuda.device_of(pos):
+        _lib.check(_lib.load().clusten_nbhd_build(
+            pos.data_ptr(), member_idx.data_ptr(), cluster_mask.data_ptr() if cluster_mask is not None else None,
+            nearest_cluster.data_ptr(), nbhd_idx.data_ptr(), nbhd_mask.data_ptr() if nbhd_mask is not None else None,
+            pe_idx.data_ptr(), b, n, k, cs, nnc, int(rel_pos_width), int(table_width), _stream(pos)))
+    return nbhd_idx, nbhd_mask, pe_idx
+
+
+def merge_weights(weights_table, pe_idx, learned_prob=None, nbhd_idx=None, nbhd_mask=None):
+    """weights [b, n_out, m, ic] = weights_table[pe_idx] * (learned_prob[b, nbhd_idx] * nbhd_mask): the first
+    argument of CLUSTENWF as ClusterMerging builds it (models/aff_transformer.py:340-358 of the reference), in one
+    kernel.  weights_table [rows, ic]; learned_prob [b, n] or [b, n, 1] (None = 1); int64 [b, n_out, m] tables.
+    Table and scores are brought to their common dtype first, as the reference's product does."""
+    _chk("pe_idx", pe_idx, torch.int64, 3)
+    b, n_out, m = pe_idx.shape
+    dtype = weights_table.dtype
+    n = 1
+    if learned_prob is not None:
+        dtype = torch.promote_types(dtype, learned_prob.dtype)
+        learned_prob = learned_prob.reshape(b, -1).to(dtype).contiguous()
+        n = learned_prob.shape[1]
+        if nbhd_idx is None:
+            raise RuntimeError("clusten: merge_weights needs nbhd_idx with learned_prob")
+        _chk("nbhd_idx", nbhd_idx, torch.int64, 3)
+        if nbhd_idx.shape != pe_idx.shape:
+            raise RuntimeError("clusten: nbhd_idx must have pe_idx's shape")
+    weights_table = weights_table.to(dtype).contiguous()
+    _chk("weights_table", weights_table, None, 2)
+    rows, ic = weights_table.shape
+    if nbhd_mask is not None:
+        _chk("nbhd_mask", nbhd_mask, torch.int64, 3)
+        if nbhd_mask.shape != pe_idx.shape:
+            raise RuntimeError("clusten: nbhd_mask must have pe_idx's shape")
+    out = torch.empty((b, n_out, m, ic), dtype=dtype, device=pe_idx.device)
+    with torch.cuda.device_of(pe_idx):
+        _lib.check(_lib.load().clusten_merge_weights(
+            weights_table.data_ptr(), pe_idx.data_ptr(), learned_prob.data_ptr() if learned_prob is not None else None,
+            nbhd_idx.data_ptr() if learned_prob is not None else None,
+            nbhd_mask.data_ptr() if nbhd_mask is not None else None, out.data_ptr(), b, n_out, n, m, ic, rows,
+            _dt(out), _stream(pe_idx)))
+    return out
+
+
 # ----------------------------------------------------------------------------- QK
 def qk_forward(query, key, nbhd_idx):
     """attn[b,h,i,j] = <query[b,h,i], key[b,h,nbhd_idx[b,i,j]]>"""

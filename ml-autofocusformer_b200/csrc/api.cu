@@ -280,7 +280,7 @@ static bool view_ok(const void* p, const long long* st, int esize) {
     if (!aligned(p, 16)) return false;
     for (int i = 0; i < 3; ++i)
         if (st[i] < 0 || (st[i] * esize) % 16 != 0) return false;
-    return st[2] > 0;
+    return st[2] > 0 && st[2] <= (1ll << 30);            // the kernels keep the row stride in 32 bits
 }
 
 int clusten_qk_forward_strided(const void* query, const long long* query_strides, const void* key,
@@ -426,6 +426,41 @@ int clusten_knn2d(const float* query, const float* database, int b, int n_query,
     CLUSTEN_REQUIRE_PTR(nn_idx, 8);
     if (nn_dist && !aligned(nn_dist, 4)) return CLUSTEN_ERR_ALIGN;
     return launch_knn2d(query, database, b, n_query, n, k, nn_idx, nn_dist, (cudaStream_t)stream);
+}
+
+int clusten_nbhd_build(const float* pos, const int64_t* member_idx, const int64_t* cluster_mask,
+                       const int64_t* nearest_cluster, int64_t* nbhd_idx, int64_t* nbhd_mask, int64_t* pe_idx, int b,
+                       int n, int k, int cs, int nnc, int rel_pos_width, int table_width, void* stream) {
+    if (b <= 0 || n <= 0 || k <= 0 || cs <= 0 || nnc <= 0 || table_width <= 0) return CLUSTEN_ERR_SHAPE;
+    if ((long long)nnc * cs > 0x7fffffffLL || (long long)b * n > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    CLUSTEN_REQUIRE_PTR(pos, 8);
+    CLUSTEN_REQUIRE_PTR(member_idx, 8);
+    CLUSTEN_REQUIRE_PTR(nearest_cluster, 8);
+    CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    CLUSTEN_REQUIRE_PTR(pe_idx, 8);
+    if ((cluster_mask == nullptr) != (nbhd_mask == nullptr)) return CLUSTEN_ERR_NULL;
+    if (cluster_mask && (!aligned(cluster_mask, 8) || !aligned(nbhd_mask, 8))) return CLUSTEN_ERR_ALIGN;
+    return launch_nbhd_build(pos, member_idx, cluster_mask, nearest_cluster, nbhd_idx, nbhd_mask, pe_idx, b, n, k, cs,
+                             nnc, rel_pos_width, table_width, (cudaStream_t)stream);
+}
+
+int clusten_merge_weights(const void* weights_table, const int64_t* pe_idx, const void* learned_prob,
+                          const int64_t* nbhd_idx, const int64_t* nbhd_mask, void* weights, int b, int n_out, int n,
+                          int m, int ic, int table_rows, int dtype, void* stream) {
+    if (b <= 0 || n_out <= 0 || n <= 0 || m <= 0 || ic <= 0 || table_rows <= 0) return CLUSTEN_ERR_SHAPE;
+    if ((long long)b * n > 0x7fffffffLL || (long long)table_rows * ic > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    if (dtype != CLUSTEN_F32 && dtype != CLUSTEN_F16 && dtype != CLUSTEN_BF16) return CLUSTEN_ERR_DTYPE;
+    const size_t es = dtype_size(dtype);
+    CLUSTEN_REQUIRE_PTR(weights_table, es);
+    CLUSTEN_REQUIRE_PTR(pe_idx, 8);
+    CLUSTEN_REQUIRE_PTR(weights, es);
+    if (learned_prob) {
+        if (!aligned(learned_prob, es)) return CLUSTEN_ERR_ALIGN;
+        CLUSTEN_REQUIRE_PTR(nbhd_idx, 8);
+    }
+    if (nbhd_mask && !aligned(nbhd_mask, 8)) return CLUSTEN_ERR_ALIGN;
+    return launch_merge_weights(dtype, weights_table, pe_idx, learned_prob, nbhd_idx, nbhd_mask, weights, b, n_out, n,
+                                m, ic, table_rows, (cudaStream_t)stream);
 }
 
 size_t clusten_wf_order_bytes(int b, int n_out) {

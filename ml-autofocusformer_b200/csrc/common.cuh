@@ -167,6 +167,16 @@ int validate_av_backward(const void* d_feat, const void* attn, const void* value
 int launch_knn2d(const float* query, const float* db, int b, int nq, int n, int k, int64_t* idx_out, float* dist_out,
                  cudaStream_t s);
 
+// nbhd.cu
+int launch_nbhd_build(const float* pos, const int64_t* member_idx, const int64_t* cluster_mask,
+                      const int64_t* nearest_cluster, int64_t* nbhd_idx, int64_t* nbhd_mask, int64_t* pe_idx, int b,
+                      int n, int k, int cs, int nnc, int rel_pos_width, int table_width, cudaStream_t s);
+
+// merge.cu
+int launch_merge_weights(int dtype, const void* table, const int64_t* pe_idx, const void* prob, const int64_t* nbhd_idx,
+                         const int64_t* mask, void* out, int b, int n_out, int n, int m, int ic, int table_rows,
+                         cudaStream_t s);
+
 // inverse.cu
 int launch_inverse_build(const int64_t* idx, int b, int n_rows, int m, int nt, void* buf, cudaStream_t s);
 // inverse_struct.cu: the build for cluster- and run-structured tables; runs first, marks what it handled

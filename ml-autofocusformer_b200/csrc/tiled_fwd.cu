@@ -38,6 +38,7 @@ __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* W
                                                  int n, int m, int i0, int lane, const GatherStrides gs) {
     const int E = kT * m;
     const int4* ring4 = reinterpret_cast<const int4*>(ring);
+    const int x_row = (int)gs.x_row;                     // 32 x 32 -> 64-bit products below
     for (int g = 0; g < heads; ++g) {
         const long long bb = (long long)b * heads + g;
         const T* Xh = X + (long long)b * gs.x_batch + (long long)g * gs.x_head + lane;
@@ -63,7 +64,7 @@ __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* W
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const bool ok = th[e] == 0 && (unsigned)tl[e] < (unsigned)n;
-                        xv[e] = ok ? Xh[(long long)tl[e] * gs.x_row] : Elem<T>::down(0.f);
+                        xv[e] = ok ? Xh[(long long)tl[e] * x_row] : Elem<T>::down(0.f);
                     }
 #pragma unroll
                     for (int e = 0; e < 4; ++e) accq[q] += wv[e] * Elem<T>::up(xv[e]);
@@ -74,7 +75,7 @@ __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* W
             for (int q = 0; q < kT; ++q)
                 for (int j = 0; j < m; ++j) {
                     const long long t = ring[q * m + j];
-                    if (t >= 0 && t < n) accq[q] += Wd[q * m + j] * Elem<T>::up(Xh[t * gs.x_row]);
+                    if (t >= 0 && t < n) accq[q] += Wd[q * m + j] * Elem<T>::up(Xh[(long long)(int)t * x_row]);
                 }
         }
 #pragma unroll
@@ -411,9 +412,11 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const int z = lane + 32 * k;
-                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (i0 + (z >> 3) < n) v = ld4(Yt + (long long)(z >> 3) * gs.y_row + (z & 7) * 4);
-                        *reinterpret_cast<float4*>(Ys + (z >> 3) * kYLD + (z & 7) * 4) = v;
+                        float* dd = Ys + (z >> 3) * kYLD + (z & 7) * 4;
+                        const T* ys = Yt + (long long)(z >> 3) * gs.y_row + (z & 7) * 4;
+                        if (i0 + (z >> 3) >= n) *reinterpret_cast<float4*>(dd) = make_float4(0.f, 0.f, 0.f, 0.f);
+                        else if (kIsFloat) cp_async16_ca(dd, ys);          // lands together with the staged rows
+                        else *reinterpret_cast<float4*>(dd) = ld4(ys);
                     }
                 }
                 cp_async_commit();

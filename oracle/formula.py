@@ -60,3 +60,37 @@ def forward_backward(op, a, b_, nbhd_idx, grad_out, chunk=None):
         ga.append(x.grad)
         gb.append(y.grad)
     return torch.cat(outs, 0), torch.cat(ga, 0), torch.cat(gb, 0)
+
+
+def nbhd_tables(pos, member_idx, cluster_mask, nearest_cluster, rel_pos_width, table_width):
+    """(nbhd_idx, nbhd_mask or None, pe_idx): the neighbourhood tables of a stage as the reference's
+    BasicLayer.forward builds them (models/aff_transformer.py:476-487): members of the nearest clusters,
+    their mask bits, and the rows of their offsets in the position-embedding table."""
+    b, n, d = pos.shape
+    cs = member_idx.shape[2]
+    nnc = nearest_cluster.shape[2]
+    m = nnc * cs
+    pick = nearest_cluster.reshape(b, -1, 1).expand(-1, -1, cs)
+    nbhd_idx = member_idx.gather(index=pick, dim=1).reshape(b, n, m)
+    nbhd_mask = None if cluster_mask is None else cluster_mask.gather(index=pick, dim=1).reshape(b, n, m)
+    there = pos.gather(index=nbhd_idx.reshape(b, -1, 1).expand(-1, -1, d), dim=1).reshape(b, n, m, d)
+    rel = there - (pos.unsqueeze(2) - rel_pos_width)
+    pe_idx = (rel[..., 1] * table_width + rel[..., 0]).long()
+    return nbhd_idx, nbhd_mask, pe_idx
+
+
+def merge_weights(weights_table, pe_idx, learned_prob, nbhd_idx, nbhd_mask):
+    """weights [b, n_out, m, ic] as the reference's ClusterMerging.forward builds them before CLUSTENWF
+    (models/aff_transformer.py:340-358): table rows by pe_idx, times the neighbours' importance scores, times
+    the mask.  learned_prob [b, n, 1] or None, nbhd_mask int64 [b, n_out, m] or None."""
+    b, n_out, m = pe_idx.shape
+    ic = weights_table.shape[-1]
+    weights = weights_table.gather(index=pe_idx.reshape(-1, 1).expand(-1, ic), dim=0).reshape(b, n_out, m, ic)
+    if learned_prob is not None:
+        lp = learned_prob.gather(index=nbhd_idx.reshape(b, -1, 1), dim=1).reshape(b, n_out, m, 1)
+        if nbhd_mask is not None:
+            lp = lp * nbhd_mask.unsqueeze(3)
+        weights = weights * lp
+    elif nbhd_mask is not None:
+        weights = weights * nbhd_mask.unsqueeze(3)
+    return weights

@@ -89,3 +89,30 @@ def test_fused_attention_variant_of_the_model(lib, config, batch, dtype, tol, ca
     with capsys.disabled():
         print(f"\n{config} {dtype} fused attention: logits rel err {err:.2e}")
     assert err <= tol, err
+
+
+@pytest.mark.parametrize("config,batch,dtype", [("tiny224", 4, torch.float32), ("base384", 2, torch.bfloat16)],
+                         ids=["tiny224-fp32", "base384-bf16"])
+def test_neighbourhood_tables_variant_of_the_model(lib, config, batch, dtype, capsys):
+    """BasicLayer building its neighbourhood tables with clusten_nbhd_build (an opt-in that replaces one method
+    of the reference's model): the tables are integer work, so the blocks see the very same inputs; the logits
+    may differ only by what the feature reordering's different torch kernel rounds (nothing: it copies)."""
+    aff_harness.use_implementation("b200")
+    model = aff_harness.build_model(config, DEV, seed=0)
+    x = aff_harness.synthetic_images(config, batch, DEV, seed=1)
+    want = aff_harness.forward(model, x, dtype)
+    try:
+        aff_harness.use_fused_neighbourhood(True)
+        got = aff_harness.forward(model, x, dtype)
+        aff_harness.use_fused_merging(True)
+        both = aff_harness.forward(model, x, dtype)
+    finally:
+        aff_harness.use_fused_neighbourhood(False)
+        aff_harness.use_fused_merging(False)
+    err, err2 = _rel(got, want), _rel(both, want)
+    with capsys.disabled():
+        print(f"\n{config} {dtype} neighbourhood tables from one kernel: logits rel err {err:.2e}; "
+              f"merge weights too: {err2:.2e}")
+    assert err <= 1e-6, err
+    # the merge weights are rounded once where the reference's products round after every step (bf16 only)
+    assert err2 <= (1e-6 if dtype == torch.float32 else 2e-2), err2
