@@ -46,7 +46,7 @@ struct FusedParams {
 };
 
 template <typename T, bool M48>
-__global__ void __launch_bounds__(32 * kWarps, 4)
+__global__ void __launch_bounds__(32 * kWarps, sizeof(T) == 2 ? 5 : 4)     // 16-bit: 43 KB per CTA, five fit
 fused_attention_kernel(const FusedParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using WS = FusedSmem<T>;
@@ -144,6 +144,21 @@ fused_attention_kernel(const FusedParams p) {
         const int i0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
         const bool complete = i0 + kT <= n;
         const int64_t* src = p.idx + ((long long)b * n + i0) * m;
+        // ---- warm the L2: this tile's position-table indices and mask (wanted after the de-duplication) and the
+        //      index rows of this warp's next tile
+        {
+            const long long toff = ((long long)b * n + i0) * m;
+            if (lane * 16 < E) {
+                if (p.table) prefetch_l2(p.pe_idx + toff + lane * 16);
+                if (p.mask) prefetch_l2(p.mask + toff + lane * 16);
+            }
+            const unsigned nt = task + nwarps;
+            if (nt < total && lane * 16 < E) {
+                const int nb = (int)(nt / (unsigned)p.tiles);
+                const long long noff = ((long long)nb * n + (long long)(nt - (unsigned)nb * (unsigned)p.tiles) * kT) * m;
+                prefetch_l2(p.idx + noff + lane * 16);
+            }
+        }
         // ---- the tile's indices
         __syncwarp();
         {

@@ -32,16 +32,18 @@ namespace {
 // come from global memory (contiguous across the warp), the indices are still in the landing area, the
 // weights go through shared memory.  Kept out of line so that it does not weigh on the registers of the
 // staged path.
-template <typename T>
+// CONTIG: rows 32 elements apart (the [b, h, n, 32] layout), so that a row's offset is a shift
+template <typename T, bool CONTIG>
 __device__ __noinline__ void gather_sum_unstaged(const long long* ring, float* Wd, const T* __restrict__ A,
                                                  const T* __restrict__ X, T* __restrict__ out, int b, int heads,
-                                                 int n, int m, int i0, int lane, const GatherStrides gs) {
+                                                 int n, int m, int i0, int lane, long long x_batch, long long x_head,
+                                                 int x_row_arg) {
     const int E = kT * m;
     const int4* ring4 = reinterpret_cast<const int4*>(ring);
-    const int x_row = (int)gs.x_row;                     // 32 x 32 -> 64-bit products below
+    const int x_row = CONTIG ? kC : x_row_arg;           // 32 x 32 -> 64-bit products below
     for (int g = 0; g < heads; ++g) {
         const long long bb = (long long)b * heads + g;
-        const T* Xh = X + (long long)b * gs.x_batch + (long long)g * gs.x_head + lane;
+        const T* Xh = X + (long long)b * x_batch + (long long)g * x_head + lane;
         const T* Wt = A + (bb * n + i0) * m;
         __syncwarp();
         for (int x = lane; x < E; x += 32) {
@@ -221,7 +223,11 @@ gather_tiles_kernel(const T* __restrict__ A, const T* __restrict__ X, const int6
         const bool native16 = !kIsFloat && !rowdup;
 
         if (MODE == 0 && !identical && U > kDirectU) {
-            gather_sum_unstaged<T>(ring, Wd, A, X, out, b, heads, n, m, i0, lane, gs);
+            if (gs.x_row == kC)
+                gather_sum_unstaged<T, true>(ring, Wd, A, X, out, b, heads, n, m, i0, lane, gs.x_batch, gs.x_head, kC);
+            else
+                gather_sum_unstaged<T, false>(ring, Wd, A, X, out, b, heads, n, m, i0, lane, gs.x_batch, gs.x_head,
+                                              (int)gs.x_row);
             // advance to this warp's next (batch, tile)
             b = nb;
             tile = ntile;
