@@ -320,13 +320,7 @@ scatter_struct_kernel(const StructParams p) {
                         for (int h2 = 0; h2 < 2; ++h2) {
                             const int q = wq + 4 * h2;
                             const unsigned j = jmap[u * kT + q];
-                            if (kIsFloat) {
-                                T* dst = Wb + (8 * i + wr) * kT + q;
-                                if (j != 0xffu) cp_async4_ca(dst, wsrc + j);
-                                else *dst = Elem<T>::down(0.f);
-                            } else {
-                                wv[2 * i + h2] = j != 0xffu ? wsrc[j] : Elem<T>::down(0.f);
-                            }
+                            wv[2 * i + h2] = j != 0xffu ? wsrc[j] : Elem<T>::down(0.f);
                         }
                     } else if (8 * i < rows_pad) {
                         // 16-bit products run over multiples of 16 rows: an empty cluster slot is zero
@@ -359,7 +353,7 @@ scatter_struct_kernel(const StructParams p) {
                 cp_async_wait<0>();
             }
             const int rows_pad = padded(stage_rows(st));
-            if (!kIsFloat && kind == kTileClusters) {
+            if (kind == kTileClusters) {
                 T* Wb = Ws + buf * kWe;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
