@@ -27,8 +27,8 @@ namespace {
 constexpr int kSR = 32;                  // staged rows per stage (4 clusters)
 constexpr int kPairs = kStructMaxPairs;  // (cluster, slot) pairs of a clusters tile; entries kept of a runs tile
 
-// Per-warp shared memory.  Rows and weights are double-buffered: while one stage is multiplied the next
-// one (the next 32 rows, or the next head) is on its way.
+// Per-warp shared memory.  One buffer of rows and weights: a second one, filled while the first is multiplied,
+// measured slower than the extra resident warps that its 5 KB per warp pay for (7 CTAs per SM instead of 4).
 template <typename T> struct StructSmem {
     static constexpr bool kIsFloat = std::is_same<T, float>::value;
     static constexpr int kX = kSR * kC * (int)sizeof(T);      // staged rows, one buffer; de-duplication scratch before that
@@ -38,9 +38,9 @@ template <typename T> struct StructSmem {
     static constexpr int kSlotq = kPairs * 2;                 // clusters: slot of the pair's cluster | target << 12
     static constexpr int kUniq = kPairs * 2;                  // clusters: slot -> cluster
     static constexpr int kJmap = kPairs * kT;                 // clusters: [slot][target] -> neighbour slot j, 0xff = not named
-    static constexpr int kTotal = 2 * kX + 2 * kW + kOut + kCode + kSlotq + kUniq + kJmap;
+    static constexpr int kTotal = kX + kW + kOut + kCode + kSlotq + kUniq + kJmap;
 };
-static_assert(kPairs * 2 + kBMW * 4 + kBMW * 2 + 64 <= 2 * kSR * kC * 2, "de-duplication scratch must fit in the row buffers");
+static_assert(kPairs * 2 + kBMW * 4 + kBMW * 2 + 64 <= kSR * kC * 2, "de-duplication scratch must fit in the row buffers");
 static_assert(StructSmem<float>::kTotal % 128 == 0 && StructSmem<__half>::kTotal % 128 == 0, "warps stay 128-byte aligned");
 
 struct StructParams {
@@ -127,7 +127,7 @@ __device__ __forceinline__ void struct_product16(const T* Xraw, const T* Ws16, i
 }
 
 template <typename T, bool M48>
-__global__ void __launch_bounds__(32 * kWarps, 4)
+__global__ void __launch_bounds__(32 * kWarps, sizeof(T) == 4 ? 7 : 6)
 scatter_struct_kernel(const StructParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using WS = StructSmem<T>;
@@ -135,12 +135,11 @@ scatter_struct_kernel(const StructParams p) {
     constexpr int kPer = 16 / (int)sizeof(T);           // elements per 16-byte piece
     constexpr int kLanesPerRow = kC / kPer;             // 8 (fp32) or 4 (16-bit)
     constexpr int kRowsPerPass = 32 / kLanesPerRow;     // 4 or 8
-    constexpr int kXe = kSR * kC, kWe = kSR * kT;       // elements per buffer
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
-    T* Xs = reinterpret_cast<T*>(base);                                         // [2][kSR][32]
-    T* Ws = reinterpret_cast<T*>(base + 2 * WS::kX);                            // [2][kSR][8]
-    float* Ot = reinterpret_cast<float*>(base + 2 * WS::kX + 2 * WS::kW);
+    T* Xs = reinterpret_cast<T*>(base);                                         // [kSR][32]
+    T* Ws = reinterpret_cast<T*>(base + WS::kX);                                // [kSR][8]
+    float* Ot = reinterpret_cast<float*>(base + WS::kX + WS::kW);
     unsigned* code = reinterpret_cast<unsigned*>(Ot + kT * kOLD);
     unsigned short* slotq = reinterpret_cast<unsigned short*>(code + kPairs);
     unsigned short* uniq = slotq + kPairs;
@@ -268,14 +267,14 @@ scatter_struct_kernel(const StructParams p) {
         const int wr = lane & 7, wq = lane >> 3;
         const int xrow = kIsFloat ? (lane >> 3) : (lane >> 2);
 
-        // ---- loads of unit (head g, stage s) into buffer `buf`; 16-bit weights of a clusters tile come back in
-        //      wv and are stored by the caller once the previous product is done with the buffer
-        auto issue = [&](int g, int s, int buf, T (&wv)[8]) {
+        // ---- loads of unit (head g, stage s); the weights of a clusters tile come back in wv (plain loads, in
+        //      flight together with the asynchronous row copies) and are stored by the caller
+        auto issue = [&](int g, int s, T (&wv)[8]) {
             const long long bh = (long long)b * heads + g;
             const T* Wh = Wg + bh * n * m;
             const T* Xh = Xg + bh * n * kC;
-            T* Xb = Xs + buf * kXe;
-            T* Wb = Ws + buf * kWe;
+            T* Xb = Xs;
+            T* Wb = Ws;
             const int rows = stage_rows(s), rows_pad = padded(rows);
             if (kind == kTileRuns) {
                 const int k0 = s * kSR;
@@ -333,28 +332,19 @@ scatter_struct_kernel(const StructParams p) {
         };
 
         float acc[2][4];
-        T wnext[8];
-        if (units > 0) issue(0, 0, 0, wnext);
         int g = 0, st = 0;
         for (int u = 0; u < units; ++u) {
-            const int buf = u & 1;
             int ng = g, ns = st + 1;
             if (ns == nstages) {
                 ns = 0;
                 ++ng;
             }
             T wcur[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) wcur[i] = wnext[i];
-            if (u + 1 < units) {
-                issue(ng, ns, buf ^ 1, wnext);
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
-            }
+            issue(g, st, wcur);
+            cp_async_wait<0>();
             const int rows_pad = padded(stage_rows(st));
             if (kind == kTileClusters) {
-                T* Wb = Ws + buf * kWe;
+                T* Wb = Ws;
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                     if (8 * i < rows_pad) {
@@ -367,19 +357,9 @@ scatter_struct_kernel(const StructParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
             }
-            if (kIsFloat) {
-                StructAddr sa = sa0;
-                sa.w += buf * kWe * 4;
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    sa.x[mt][0] += buf * kXe * 4;
-                    sa.x[mt][1] += buf * kXe * 4;
-                }
-                struct_steps<0>(sa, rows_pad >> 3, acc);
-            } else {
-                struct_product16<T>(Xs + buf * kXe, Ws + buf * kWe, rows_pad >> 4, lane, acc);
-            }
-            __syncwarp();                                  // this buffer may be refilled by the next issue
+            if (kIsFloat) struct_steps<0>(sa0, rows_pad >> 3, acc);
+            else struct_product16<T>(Xs, Ws, rows_pad >> 4, lane, acc);
+            __syncwarp();                                  // the buffers are refilled by the next issue
             if (st == nstages - 1) {
                 // ---- D fragments -> output tile -> 16-byte stores
                 const int gg = lane >> 2, tt = lane & 3;

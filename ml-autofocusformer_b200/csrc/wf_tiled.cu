@@ -753,24 +753,26 @@ struct WfScatterParams {
     int batch, n_out, n, m, c, tiles;
     unsigned m_magic, m_shift;            // x / m = (umulhi(magic, x) + x) >> shift
 };
-constexpr int kEE = 256;                  // entries handled at a time
+constexpr int kEE = 192;                  // entries handled at a time (sized so that five CTAs fit on an SM)
+constexpr int kUD = 32;                   // gradient rows per stage (24 rows and six CTAs per SM measured slower)
 struct WfScatterSmem {
-    static constexpr int kX = kUW * kCG * 4;
+    static constexpr int kX = kUD * kCG * 4;
     static constexpr int kOp = kT * kWLD * 4;     // dense weights [8][kDL]; bitmap scratch before that
     static constexpr int kEnt = kEE * 4;          // row * m + slot of each entry (bit 31: the row repeats the target)
     static constexpr int kLut = kEE * 2;          // entry -> slot | tile row << 12;  slot -> merge row
     static constexpr int kTotal = kX + kOp + kEnt + 2 * kLut;
 };
 static_assert(kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= kT * kWLD * 4 && kT * kDL <= kT * kWLD, "scratch must fit in Op");
-static_assert(kEE * 2 <= kUW * kCG * 4, "token scratch must fit in the row buffer");
+static_assert(kEE * 4 <= kUD * kCG * 4 && kT * kGL * 4 <= kUD * kCG * 4 && ((kUD + 15) & ~15) * kCG * 2 <= kUD * kCG * 4,
+              "token scratch, output tile and padded 16-bit rows must fit in the row buffer");
 
 template <typename T, int ICT, bool M48, bool C64>
-__global__ void __launch_bounds__(32 * kWarps, 4)
+__global__ void __launch_bounds__(32 * kWarps, 5)
 wf_dfeat_kernel(const WfScatterParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     using WS = WfScatterSmem;
     constexpr bool kSplit = std::is_same<T, float>::value;
-    constexpr int kRowsPer = kUW / ICT;          // merge rows per stage
+    constexpr int kRowsPer = kUD / ICT;          // merge rows per stage
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
