@@ -63,4 +63,9 @@ int launch_tiled_wf_dfeat(const char* label, int dtype, const void* W, const voi
                           const InverseView& inv, void* d_feat, int b, int n_out, int n, int m, int ic, int c,
                           cudaStream_t s);
 
+// WF forward for fp32 inputs as a plain walk over the neighbours, half a warp per merge row (wf_direct.cu)
+bool wf_forward_direct_supported(int dtype, int n_out, int n, int m, int ic, int c);
+int launch_wf_forward_direct(const char* label, const void* W, const void* F, const int64_t* idx, const int* order,
+                             void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s);
+
 }  // namespace clusten

@@ -1,0 +1,149 @@
+// CLUSTENWF forward for fp32 inputs as a plain walk over the neighbours.
+//
+//   feat_new[b, i, k, :] = sum_j weights[b, i, j, k] * feat[b, nbhd_idx[b, i, j], :]
+//
+// Half a warp takes one merge row and every lane 4 channels of a 64-channel group: per neighbour the half
+// reads the ic weights (one address, broadcast), the neighbour's feature vector (16 bytes per lane, 256
+// contiguous bytes per row) and adds with fp32 FMAs in neighbour order -- the order of the reference's loop
+// (clusten/src/clustenwf_cuda_kernel.cu:41-47), which gathers every feature row ic times per output element.
+// Rows are taken in the row order, so the two rows of a warp and the rows of neighbouring warps share most of
+// their neighbours and find them in L1.  No shared memory and 60-odd registers: 32 warps per SM, against 12
+// for the tiled kernel (wf_tiles_kernel), whose staging, de-duplication and three-pass TF32 products cost more
+// instruction slots than these 16 FMAs per neighbour.  16-bit inputs stay on the tiled kernel: their products
+// are single tensor-core instructions there and conversions here.
+#include "tile_core.cuh"
+#include "tiled.cuh"
+
+namespace clusten {
+namespace {
+
+constexpr int kDirectWarps = 8;
+
+struct WfDirectParams {
+    const float* W;       // weights [b, n_out, m, ic]
+    const float* F;       // feat [b, n, c]
+    float* out;           // feat_new [b, n_out, ic, c]
+    const int64_t* idx;   // [b, n_out, m]
+    const int* order;     // [b, n_out] or nullptr
+    int batch, n_out, n, m, c;
+};
+
+template <int ICT, bool C64>
+__global__ void __launch_bounds__(32 * kDirectWarps, 4)
+wf_forward_direct_kernel(const WfDirectParams p) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4, hl = lane & 15;
+    const int m = p.m, c = C64 ? 64 : p.c, n = p.n, n_out = p.n_out;
+    const unsigned pairs = (unsigned)(n_out + 1) >> 1;
+    const unsigned total = (unsigned)p.batch * pairs;
+    const unsigned nwarps = gridDim.x * kDirectWarps;
+    for (unsigned task = blockIdx.x * kDirectWarps + warp; task < total; task += nwarps) {
+        const int b = (int)(task / pairs);
+        const int pos = (int)(task - (unsigned)b * pairs) * 2 + half;
+        const long long brow = (long long)b * n_out;
+        int rq = -1;
+        if (pos < n_out) {
+            rq = p.order ? p.order[brow + pos] : pos;
+            if ((unsigned)rq >= (unsigned)n_out) rq = -1;        // an entry that is no row number: treated as absent
+        }
+        const int64_t* irow = p.idx + (brow + max(rq, 0)) * m;
+        const float* wrow = p.W + (brow + max(rq, 0)) * m * ICT;
+        const float* Fb = p.F + (long long)b * n * c + 4 * hl;
+        for (int c0 = 0; c0 < c; c0 += 64) {
+            float4 acc[ICT];
+#pragma unroll
+            for (int k = 0; k < ICT; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j0 = 0; j0 < m; j0 += 16) {
+                // the half's next 16 neighbours, one per lane
+                long long my_t = -1;
+                if (rq >= 0 && j0 + hl < m) my_t = irow[j0 + hl];
+                const int mine = (my_t >= 0 && my_t < n) ? (int)my_t : -1;
+                const int cnt = min(16, m - j0);
+                // ... and their weights, one neighbour per lane: the row's 16 m bytes are contiguous
+                float my_w[ICT];
+#pragma unroll
+                for (int k = 0; k < ICT; ++k) my_w[k] = 0.f;
+                if (rq >= 0 && j0 + hl < m) {
+                    if constexpr (ICT == 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(wrow + (j0 + hl) * 4);
+                        my_w[0] = v.x;  my_w[1] = v.y;  my_w[2] = v.z;  my_w[3] = v.w;
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < ICT; ++k) my_w[k] = wrow[(j0 + hl) * ICT + k];
+                    }
+                }
+                // four feature vectors in flight at a time (L1 / L2), summed in neighbour order
+                for (int jj = 0; jj < cnt; jj += 4) {
+                    float4 f[4];
+                    bool ok[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int t = __shfl_sync(kFull, mine, jj + u, 16);
+                        ok[u] = jj + u < cnt && t >= 0;
+                        if (ok[u]) f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t * (unsigned)c + c0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        float w[ICT];
+#pragma unroll
+                        for (int k = 0; k < ICT; ++k) w[k] = __shfl_sync(kFull, my_w[k], jj + u, 16);
+                        if (ok[u]) {
+#pragma unroll
+                            for (int k = 0; k < ICT; ++k) {
+                                acc[k].x += w[k] * f[u].x;
+                                acc[k].y += w[k] * f[u].y;
+                                acc[k].z += w[k] * f[u].z;
+                                acc[k].w += w[k] * f[u].w;
+                            }
+                        }
+                    }
+                }
+            }
+            if (rq >= 0) {
+#pragma unroll
+                for (int k = 0; k < ICT; ++k)
+                    *reinterpret_cast<float4*>(p.out + ((brow + rq) * ICT + k) * c + c0 + 4 * hl) = acc[k];
+            }
+        }
+    }
+}
+
+template <int ICT>
+int wf_forward_direct_t(const char* label, const WfDirectParams& p, cudaStream_t s) {
+    auto kernel = p.c == 64 ? wf_forward_direct_kernel<ICT, true> : wf_forward_direct_kernel<ICT, false>;
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kDirectWarps, 0);
+    if (per_sm < 0) return per_sm;
+    const long long tasks = (long long)p.batch * ((p.n_out + 1) / 2);
+    long long grid = (long long)sm_count() * per_sm;
+    const long long need = (tasks + kDirectWarps - 1) / kDirectWarps;
+    if (grid > need) grid = need;
+    ScopedKernelTimer timer(label, s);
+    kernel<<<(int)grid, 32 * kDirectWarps, 0, s>>>(p);
+    note_launch();
+    return check_launch();
+}
+
+}  // namespace
+
+bool wf_forward_direct_supported(int dtype, int n_out, int n, int m, int ic, int c) {
+    // element offsets inside a batch element are kept in 32 bits
+    return dtype == CLUSTEN_F32 && (ic == 1 || ic == 2 || ic == 4) && c % 64 == 0 &&
+           (long long)n * c <= 0xffffffffLL && (long long)n_out * m * ic <= 0x7fffffffLL;
+}
+
+int launch_wf_forward_direct(const char* label, const void* W, const void* F, const int64_t* idx, const int* order,
+                             void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s) {
+    WfDirectParams p{};
+    p.W = static_cast<const float*>(W);  p.F = static_cast<const float*>(F);  p.out = static_cast<float*>(out);
+    p.idx = idx;  p.order = order;
+    p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;
+    if ((long long)b * ((n_out + 1) / 2) > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    switch (ic) {
+        case 1: return wf_forward_direct_t<1>(label, p, s);
+        case 2: return wf_forward_direct_t<2>(label, p, s);
+        case 4: return wf_forward_direct_t<4>(label, p, s);
+        default: return CLUSTEN_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace clusten
