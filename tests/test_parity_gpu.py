@@ -129,6 +129,30 @@ def test_wf_forward_backward(ops, shape, regime, dtype):
     assert_close(df, rf, dtype, "d_feat")
 
 
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+@pytest.mark.parametrize("shape", [(2, 98, 392, 48, 4, 64), (1, 50, 200, 24, 1, 128), (2, 73, 368, 48, 4, 128)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_wf_forward_fp32_both_kernels(ops, shape, regime, monkeypatch):
+    """fp32 WF forward has two kernels: the walk over the neighbours (default) and the tiled one that 16-bit
+    inputs use (selected for fp32 by CLUSTEN_WF_FORWARD_TILED, which the library reads at every call).  Both
+    against the oracle, and the walk twice for bit-reproducibility."""
+    b, n_out, n, m, ic, c = shape
+    if regime == "random":
+        idx = workloads.random_rows(b, n_out, n, m, 7).to(DEV)
+    else:
+        idx = workloads.select_rows(workloads.make_index(regime, b, n, m, 9), n_out, 10).to(DEV)
+    w, feat, _ = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, torch.float32, 11))
+    want = exact("wf", "forward", w, feat, idx)
+    walk = ops.wf_forward(w, feat, idx)
+    assert torch.equal(walk, ops.wf_forward(w, feat, idx))
+    assert_close(walk, want, torch.float32, "wf forward (walk)")
+    assert_close(ops.wf_forward(w, feat, idx, row_order=False), want, torch.float32, "wf forward (walk, storage order)")
+    monkeypatch.setenv("CLUSTEN_WF_FORWARD_TILED", "1")
+    tiled = ops.wf_forward(w, feat, idx)
+    monkeypatch.delenv("CLUSTEN_WF_FORWARD_TILED")
+    assert_close(tiled, want, torch.float32, "wf forward (tiled)")
+
+
 # (n, m, n_targets): one warp per chunk of rows with m <= 32, <= 64 and > 64; few rows; and a target count
 # whose per-chunk counters do not fit in shared memory (32 rows at a time instead)
 INVERSE_SHAPES = [(203, 48, 203), (203, 24, 203), (77, 80, 77), (5, 12, 5), (203, 48, 17500)]
