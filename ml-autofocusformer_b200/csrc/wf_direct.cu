@@ -72,7 +72,32 @@ wf_forward_direct_kernel(const WfDirectParams p) {
                         for (int k = 0; k < ICT; ++k) my_w[k] = wrow[(j0 + hl) * ICT + k];
                     }
                 }
-                // four feature vectors in flight at a time (L1 / L2), summed in neighbour order
+                // four feature vectors in flight at a time (L1 / L2), summed in neighbour order.  A full chunk of
+                // valid neighbours -- the rule -- runs without a test per neighbour.
+                const bool clean = cnt == 16 && __all_sync(kFull, mine >= 0);
+                if (clean) {
+#pragma unroll
+                    for (int jj = 0; jj < 16; jj += 4) {
+                        float4 f[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int t = __shfl_sync(kFull, mine, jj + u, 16);
+                            f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t * (unsigned)c + c0);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                            for (int k = 0; k < ICT; ++k) {
+                                const float w = __shfl_sync(kFull, my_w[k], jj + u, 16);
+                                acc[k].x += w * f[u].x;
+                                acc[k].y += w * f[u].y;
+                                acc[k].z += w * f[u].z;
+                                acc[k].w += w * f[u].w;
+                            }
+                        }
+                    }
+                    continue;
+                }
                 for (int jj = 0; jj < cnt; jj += 4) {
                     float4 f[4];
                     bool ok[4];
