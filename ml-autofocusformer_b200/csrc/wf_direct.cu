@@ -133,6 +133,112 @@ wf_forward_direct_kernel(const WfDirectParams p) {
     }
 }
 
+// d_weights the same way:  d_weights[b, i, j, k] = <feat[b, nbhd_idx[b, i, j], :], d_feat_new[b, i, k, :]>.
+// Half a warp per merge row, 4 channels per lane: the row's ic gradient vectors stay in registers, four
+// neighbours' feature vectors are in flight at a time, every lane forms its 4-channel share of the 4 x ic dot
+// products, and a butterfly over the 16 lanes (each step halves the values a lane keeps) leaves lane l with
+// the complete product number l -- neighbour l / ic of the four, weight l % ic -- so that the 16 results of the
+// four neighbours are one contiguous 64-byte store (ic = 4).
+struct WfDwDirectParams {
+    const float* F;       // feat [b, n, c]
+    const float* G;       // d_feat_new [b, n_out, ic, c]
+    float* out;           // d_weights [b, n_out, m, ic]
+    const int64_t* idx;   // [b, n_out, m]
+    const int* order;     // [b, n_out] or nullptr
+    int batch, n_out, n, m, c;
+};
+
+template <bool C64>
+__global__ void __launch_bounds__(32 * kDirectWarps, 4)
+wf_dweights_direct_kernel(const WfDwDirectParams p) {
+    constexpr int ICT = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4, hl = lane & 15;
+    const int m = p.m, c = C64 ? 64 : p.c, n = p.n, n_out = p.n_out;
+    const unsigned pairs = (unsigned)(n_out + 1) >> 1;
+    const unsigned total = (unsigned)p.batch * pairs;
+    const unsigned nwarps = gridDim.x * kDirectWarps;
+    for (unsigned task = blockIdx.x * kDirectWarps + warp; task < total; task += nwarps) {
+        const int b = (int)(task / pairs);
+        const int pos = (int)(task - (unsigned)b * pairs) * 2 + half;
+        const long long brow = (long long)b * n_out;
+        int rq = -1;
+        if (pos < n_out) {
+            rq = p.order ? p.order[brow + pos] : pos;
+            if ((unsigned)rq >= (unsigned)n_out) rq = -1;
+        }
+        const int64_t* irow = p.idx + (brow + max(rq, 0)) * m;
+        const float* grow = p.G + (brow + max(rq, 0)) * ICT * c + 4 * hl;
+        const float* Fb = p.F + (long long)b * n * c + 4 * hl;
+        float* orow = p.out + (brow + max(rq, 0)) * m * ICT;
+        float4 g[ICT];
+        if (C64) {
+#pragma unroll
+            for (int k = 0; k < ICT; ++k) g[k] = *reinterpret_cast<const float4*>(grow + k * c);
+        }
+        for (int j0 = 0; j0 < m; j0 += 16) {
+            long long my_t = -1;
+            if (rq >= 0 && j0 + hl < m) my_t = irow[j0 + hl];
+            const int mine = (my_t >= 0 && my_t < n) ? (int)my_t : -1;
+            const int cnt = min(16, m - j0);
+            for (int jj = 0; jj < cnt; jj += 4) {
+                float v[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                int t[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) t[u] = __shfl_sync(kFull, mine, (jj + u) & 15, 16);
+                for (int c0 = 0; c0 < c; c0 += 64) {
+                    if (!C64) {
+#pragma unroll
+                        for (int k = 0; k < ICT; ++k) g[k] = *reinterpret_cast<const float4*>(grow + k * c + c0);
+                    }
+                    float4 f[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (t[u] >= 0) f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t[u] * (unsigned)c + c0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int k = 0; k < ICT; ++k)
+                            v[u * 4 + k] += f[u].x * g[k].x + f[u].y * g[k].y + f[u].z * g[k].z + f[u].w * g[k].w;
+                }
+                // butterfly: after the step with mask s a lane keeps the half of its values that its bit s selects
+#pragma unroll
+                for (int s = 8, cntv = 16; s > 0; s >>= 1, cntv >>= 1) {
+                    const bool upper = (hl & s) != 0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        if (i < cntv / 2) {
+                            const float lo = v[i], hi = v[i + cntv / 2];
+                            const float send = upper ? lo : hi, keep = upper ? hi : lo;
+                            v[i] = keep + __shfl_xor_sync(kFull, send, s, 16);
+                        }
+                    }
+                }
+                // lane l holds product l: neighbour jj + l / 4, weight l % 4
+                if (rq >= 0 && jj + (hl >> 2) < cnt) orow[(j0 + jj) * ICT + hl] = v[0];
+            }
+        }
+    }
+}
+
+int wf_dweights_direct(const char* label, const WfDwDirectParams& p, cudaStream_t s) {
+    auto kernel = p.c == 64 ? wf_dweights_direct_kernel<true> : wf_dweights_direct_kernel<false>;
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kDirectWarps, 0);
+    if (per_sm < 0) return per_sm;
+    const long long tasks = (long long)p.batch * ((p.n_out + 1) / 2);
+    long long grid = (long long)sm_count() * per_sm;
+    const long long need = (tasks + kDirectWarps - 1) / kDirectWarps;
+    if (grid > need) grid = need;
+    ScopedKernelTimer timer(label, s);
+    kernel<<<(int)grid, 32 * kDirectWarps, 0, s>>>(p);
+    note_launch();
+    return check_launch();
+}
+
 template <int ICT>
 int wf_forward_direct_t(const char* label, const WfDirectParams& p, cudaStream_t s) {
     auto kernel = p.c == 64 ? wf_forward_direct_kernel<ICT, true> : wf_forward_direct_kernel<ICT, false>;
@@ -169,6 +275,16 @@ int launch_wf_forward_direct(const char* label, const void* W, const void* F, co
         case 4: return wf_forward_direct_t<4>(label, p, s);
         default: return CLUSTEN_ERR_UNSUPPORTED;
     }
+}
+
+int launch_wf_dweights_direct(const char* label, const void* F, const void* G, const int64_t* idx, const int* order,
+                              void* d_weights, int b, int n_out, int n, int m, int c, cudaStream_t s) {
+    WfDwDirectParams p{};
+    p.F = static_cast<const float*>(F);  p.G = static_cast<const float*>(G);  p.out = static_cast<float*>(d_weights);
+    p.idx = idx;  p.order = order;
+    p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;
+    if ((long long)b * ((n_out + 1) / 2) > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
+    return wf_dweights_direct(label, p, s);
 }
 
 }  // namespace clusten
