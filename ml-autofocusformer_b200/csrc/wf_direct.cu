@@ -181,7 +181,10 @@ wf_dweights_direct_kernel(const WfDwDirectParams p) {
             if (rq >= 0 && j0 + hl < m) my_t = irow[j0 + hl];
             const int mine = (my_t >= 0 && my_t < n) ? (int)my_t : -1;
             const int cnt = min(16, m - j0);
-            for (int jj = 0; jj < cnt; jj += 4) {
+            // four neighbours: shares of the 4 x ic products, butterfly, one store.  CHECK: some neighbour of the
+            // chunk may be absent or out of range
+            auto four = [&](int jj, auto check) {
+                constexpr bool CHECK = decltype(check)::value;
                 float v[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) v[i] = 0.f;
@@ -196,8 +199,12 @@ wf_dweights_direct_kernel(const WfDwDirectParams p) {
                     float4 f[4];
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
-                        f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (t[u] >= 0) f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t[u] * (unsigned)c + c0);
+                        if (CHECK) {
+                            f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (t[u] >= 0) f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t[u] * (unsigned)c + c0);
+                        } else {
+                            f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t[u] * (unsigned)c + c0);
+                        }
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
@@ -219,7 +226,18 @@ wf_dweights_direct_kernel(const WfDwDirectParams p) {
                     }
                 }
                 // lane l holds product l: neighbour jj + l / 4, weight l % 4
-                if (rq >= 0 && jj + (hl >> 2) < cnt) orow[(j0 + jj) * ICT + hl] = v[0];
+                if (CHECK) {
+                    if (rq >= 0 && jj + (hl >> 2) < cnt) orow[(j0 + jj) * ICT + hl] = v[0];
+                } else {
+                    orow[(j0 + jj) * ICT + hl] = v[0];
+                }
+            };
+            const bool clean = cnt == 16 && __all_sync(kFull, mine >= 0);      // both rows present, all neighbours valid
+            if (clean) {
+#pragma unroll
+                for (int jj = 0; jj < 16; jj += 4) four(jj, std::false_type{});
+            } else {
+                for (int jj = 0; jj < cnt; jj += 4) four(jj, std::true_type{});
             }
         }
     }
