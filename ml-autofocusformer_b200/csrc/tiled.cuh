@@ -63,10 +63,11 @@ int launch_tiled_wf_dfeat(const char* label, int dtype, const void* W, const voi
                           const InverseView& inv, void* d_feat, int b, int n_out, int n, int m, int ic, int c,
                           cudaStream_t s);
 
-// WF forward for fp32 inputs as a plain walk over the neighbours, half a warp per merge row (wf_direct.cu)
+// WF forward as a plain walk over the neighbours, half a warp per merge row (wf_direct.cu)
 bool wf_forward_direct_supported(int dtype, int n_out, int n, int m, int ic, int c);
-int launch_wf_forward_direct(const char* label, const void* W, const void* F, const int64_t* idx, const int* order,
-                             void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s);
+int launch_wf_forward_direct(const char* label, int dtype, const void* W, const void* F, const int64_t* idx,
+                             const int* order, void* out, int b, int n_out, int n, int m, int ic, int c,
+                             cudaStream_t s);
 // d_weights for fp32 inputs and ic = 4 the same way
 int launch_wf_dweights_direct(const char* label, const void* F, const void* G, const int64_t* idx, const int* order,
                               void* d_weights, int b, int n_out, int n, int m, int c, cudaStream_t s);

@@ -20,15 +20,15 @@ namespace {
 constexpr int kDirectWarps = 8;
 
 struct WfDirectParams {
-    const float* W;       // weights [b, n_out, m, ic]
-    const float* F;       // feat [b, n, c]
-    float* out;           // feat_new [b, n_out, ic, c]
+    const void* W;        // weights [b, n_out, m, ic]
+    const void* F;        // feat [b, n, c]
+    void* out;            // feat_new [b, n_out, ic, c]
     const int64_t* idx;   // [b, n_out, m]
     const int* order;     // [b, n_out] or nullptr
     int batch, n_out, n, m, c;
 };
 
-template <int ICT, bool C64>
+template <typename T, int ICT, bool C64>
 __global__ void __launch_bounds__(32 * kDirectWarps, 4)
 wf_forward_direct_kernel(const WfDirectParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -47,8 +47,8 @@ wf_forward_direct_kernel(const WfDirectParams p) {
             if ((unsigned)rq >= (unsigned)n_out) rq = -1;        // an entry that is no row number: treated as absent
         }
         const int64_t* irow = p.idx + (brow + max(rq, 0)) * m;
-        const float* wrow = p.W + (brow + max(rq, 0)) * m * ICT;
-        const float* Fb = p.F + (long long)b * n * c + 4 * hl;
+        const T* wrow = static_cast<const T*>(p.W) + (brow + max(rq, 0)) * m * ICT;
+        const T* Fb = static_cast<const T*>(p.F) + (long long)b * n * c + 4 * hl;
         for (int c0 = 0; c0 < c; c0 += 64) {
             float4 acc[ICT];
 #pragma unroll
@@ -65,11 +65,11 @@ wf_forward_direct_kernel(const WfDirectParams p) {
                 for (int k = 0; k < ICT; ++k) my_w[k] = 0.f;
                 if (rq >= 0 && j0 + hl < m) {
                     if constexpr (ICT == 4) {
-                        const float4 v = *reinterpret_cast<const float4*>(wrow + (j0 + hl) * 4);
+                        const float4 v = ld4(wrow + (j0 + hl) * 4);
                         my_w[0] = v.x;  my_w[1] = v.y;  my_w[2] = v.z;  my_w[3] = v.w;
                     } else {
 #pragma unroll
-                        for (int k = 0; k < ICT; ++k) my_w[k] = wrow[(j0 + hl) * ICT + k];
+                        for (int k = 0; k < ICT; ++k) my_w[k] = Elem<T>::up(wrow[(j0 + hl) * ICT + k]);
                     }
                 }
                 // four feature vectors in flight at a time (L1 / L2), summed in neighbour order.  A full chunk of
@@ -82,7 +82,7 @@ wf_forward_direct_kernel(const WfDirectParams p) {
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             const int t = __shfl_sync(kFull, mine, jj + u, 16);
-                            f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t * (unsigned)c + c0);
+                            f[u] = ld4(Fb + (unsigned)t * (unsigned)c + c0);
                         }
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
@@ -105,7 +105,7 @@ wf_forward_direct_kernel(const WfDirectParams p) {
                     for (int u = 0; u < 4; ++u) {
                         const int t = __shfl_sync(kFull, mine, jj + u, 16);
                         ok[u] = jj + u < cnt && t >= 0;
-                        if (ok[u]) f[u] = *reinterpret_cast<const float4*>(Fb + (unsigned)t * (unsigned)c + c0);
+                        if (ok[u]) f[u] = ld4(Fb + (unsigned)t * (unsigned)c + c0);
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -127,7 +127,7 @@ wf_forward_direct_kernel(const WfDirectParams p) {
             if (rq >= 0) {
 #pragma unroll
                 for (int k = 0; k < ICT; ++k)
-                    *reinterpret_cast<float4*>(p.out + ((brow + rq) * ICT + k) * c + c0 + 4 * hl) = acc[k];
+                    st4(static_cast<T*>(p.out) + ((brow + rq) * ICT + k) * c + c0 + 4 * hl, acc[k]);
             }
         }
     }
@@ -257,9 +257,9 @@ int wf_dweights_direct(const char* label, const WfDwDirectParams& p, cudaStream_
     return check_launch();
 }
 
-template <int ICT>
+template <typename T, int ICT>
 int wf_forward_direct_t(const char* label, const WfDirectParams& p, cudaStream_t s) {
-    auto kernel = p.c == 64 ? wf_forward_direct_kernel<ICT, true> : wf_forward_direct_kernel<ICT, false>;
+    auto kernel = p.c == 64 ? wf_forward_direct_kernel<T, ICT, true> : wf_forward_direct_kernel<T, ICT, false>;
     const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kDirectWarps, 0);
     if (per_sm < 0) return per_sm;
     const long long tasks = (long long)p.batch * ((p.n_out + 1) / 2);
@@ -276,22 +276,33 @@ int wf_forward_direct_t(const char* label, const WfDirectParams& p, cudaStream_t
 
 bool wf_forward_direct_supported(int dtype, int n_out, int n, int m, int ic, int c) {
     // element offsets inside a batch element are kept in 32 bits
-    return dtype == CLUSTEN_F32 && (ic == 1 || ic == 2 || ic == 4) && c % 64 == 0 &&
+    return (dtype == CLUSTEN_F32 || dtype == CLUSTEN_F16 || dtype == CLUSTEN_BF16) && (ic == 1 || ic == 2 || ic == 4) &&
+           c % 64 == 0 &&
            (long long)n * c <= 0xffffffffLL && (long long)n_out * m * ic <= 0x7fffffffLL;
 }
 
-int launch_wf_forward_direct(const char* label, const void* W, const void* F, const int64_t* idx, const int* order,
-                             void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s) {
+template <typename T>
+static int wf_forward_direct_ic(const char* label, int ic, const WfDirectParams& p, cudaStream_t s) {
+    switch (ic) {
+        case 1: return wf_forward_direct_t<T, 1>(label, p, s);
+        case 2: return wf_forward_direct_t<T, 2>(label, p, s);
+        case 4: return wf_forward_direct_t<T, 4>(label, p, s);
+        default: return CLUSTEN_ERR_UNSUPPORTED;
+    }
+}
+
+int launch_wf_forward_direct(const char* label, int dtype, const void* W, const void* F, const int64_t* idx,
+                             const int* order, void* out, int b, int n_out, int n, int m, int ic, int c,
+                             cudaStream_t s) {
     WfDirectParams p{};
-    p.W = static_cast<const float*>(W);  p.F = static_cast<const float*>(F);  p.out = static_cast<float*>(out);
-    p.idx = idx;  p.order = order;
+    p.W = W;  p.F = F;  p.out = out;  p.idx = idx;  p.order = order;
     p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;
     if ((long long)b * ((n_out + 1) / 2) > 0x7fffffffLL) return CLUSTEN_ERR_SHAPE;
-    switch (ic) {
-        case 1: return wf_forward_direct_t<1>(label, p, s);
-        case 2: return wf_forward_direct_t<2>(label, p, s);
-        case 4: return wf_forward_direct_t<4>(label, p, s);
-        default: return CLUSTEN_ERR_UNSUPPORTED;
+    switch (dtype) {
+        case CLUSTEN_F32: return wf_forward_direct_ic<float>(label, ic, p, s);
+        case CLUSTEN_F16: return wf_forward_direct_ic<__half>(label, ic, p, s);
+        case CLUSTEN_BF16: return wf_forward_direct_ic<__nv_bfloat16>(label, ic, p, s);
+        default: return CLUSTEN_ERR_DTYPE;
     }
 }
 

@@ -1120,7 +1120,7 @@ bool tiled_wf_gather_supported(int dtype, const void* W, const void* F, const vo
 int launch_tiled_wf_sum(const char* label, int dtype, const void* W, const void* F, const int64_t* idx,
                         const int* order, void* out, int b, int n_out, int n, int m, int ic, int c, cudaStream_t s) {
     if (wf_forward_direct_supported(dtype, n_out, n, m, ic, c) && getenv("CLUSTEN_WF_FORWARD_TILED") == nullptr)
-        return launch_wf_forward_direct(label, W, F, idx, order, out, b, n_out, n, m, ic, c, s);
+        return launch_wf_forward_direct(label, dtype, W, F, idx, order, out, b, n_out, n, m, ic, c, s);
     WfParams p{};
     p.W = W;  p.F = F;  p.G = nullptr;  p.out = out;  p.idx = idx;  p.order = order;
     p.batch = b;  p.n_out = n_out;  p.n = n;  p.m = m;  p.c = c;  p.tiles = (n_out + kT - 1) / kT;
@@ -1160,7 +1160,8 @@ int launch_tiled_wf_dfeat(const char* label, int dtype, const void* W, const voi
 int launch_tiled_wf_dot(const char* label, int dtype, const void* F, const void* G, const int64_t* idx,
                         const int* order, void* d_weights, int b, int n_out, int n, int m, int ic, int c,
                         cudaStream_t s) {
-    if (ic == 4 && wf_forward_direct_supported(dtype, n_out, n, m, ic, c) && getenv("CLUSTEN_WF_DWEIGHTS_TILED") == nullptr)
+    if (ic == 4 && dtype == CLUSTEN_F32 && wf_forward_direct_supported(dtype, n_out, n, m, ic, c) &&
+        getenv("CLUSTEN_WF_DWEIGHTS_TILED") == nullptr)
         return launch_wf_dweights_direct(label, F, G, idx, order, d_weights, b, n_out, n, m, c, s);
     WfParams p{};
     p.W = nullptr;  p.F = F;  p.G = G;  p.out = d_weights;  p.idx = idx;  p.order = order;

@@ -129,28 +129,56 @@ def test_wf_forward_backward(ops, shape, regime, dtype):
     assert_close(df, rf, dtype, "d_feat")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
 @pytest.mark.parametrize("regime", ["shared", "model", "random"])
 @pytest.mark.parametrize("shape", [(2, 98, 392, 48, 4, 64), (1, 50, 200, 24, 1, 128), (2, 73, 368, 48, 4, 128)],
                          ids=lambda s: "x".join(map(str, s)))
-def test_wf_forward_fp32_both_kernels(ops, shape, regime, monkeypatch):
-    """fp32 WF forward has two kernels: the walk over the neighbours (default) and the tiled one that 16-bit
-    inputs use (selected for fp32 by CLUSTEN_WF_FORWARD_TILED, which the library reads at every call).  Both
-    against the oracle, and the walk twice for bit-reproducibility."""
+def test_wf_forward_both_kernels(ops, shape, regime, dtype, monkeypatch):
+    """WF forward has two kernels: the walk over the neighbours (default) and the tiled one (selected by
+    CLUSTEN_WF_FORWARD_TILED, which the library reads at every call).  Both against the oracle, and the walk
+    twice for bit-reproducibility."""
     b, n_out, n, m, ic, c = shape
     if regime == "random":
         idx = workloads.random_rows(b, n_out, n, m, 7).to(DEV)
     else:
         idx = workloads.select_rows(workloads.make_index(regime, b, n, m, 9), n_out, 10).to(DEV)
-    w, feat, _ = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, torch.float32, 11))
+    w, feat, _ = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, dtype, 11))
     want = exact("wf", "forward", w, feat, idx)
     walk = ops.wf_forward(w, feat, idx)
     assert torch.equal(walk, ops.wf_forward(w, feat, idx))
-    assert_close(walk, want, torch.float32, "wf forward (walk)")
-    assert_close(ops.wf_forward(w, feat, idx, row_order=False), want, torch.float32, "wf forward (walk, storage order)")
+    assert_close(walk, want, dtype, "wf forward (walk)")
+    assert_close(ops.wf_forward(w, feat, idx, row_order=False), want, dtype, "wf forward (walk, storage order)")
     monkeypatch.setenv("CLUSTEN_WF_FORWARD_TILED", "1")
     tiled = ops.wf_forward(w, feat, idx)
     monkeypatch.delenv("CLUSTEN_WF_FORWARD_TILED")
-    assert_close(tiled, want, torch.float32, "wf forward (tiled)")
+    assert_close(tiled, want, dtype, "wf forward (tiled)")
+
+
+@pytest.mark.parametrize("regime", ["shared", "model", "random"])
+def test_wf_d_weights_fp32_both_kernels(ops, regime, monkeypatch):
+    """fp32 d_weights with ic = 4: the walk with the 16-lane butterfly (default) and the tiled kernel
+    (CLUSTEN_WF_DWEIGHTS_TILED), both against the oracle; a row with absent neighbours takes the checked path."""
+    b, n_out, n, m, ic, c = 2, 99, 392, 48, 4, 128
+    if regime == "random":
+        idx = workloads.random_rows(b, n_out, n, m, 7).to(DEV)
+    else:
+        idx = workloads.select_rows(workloads.make_index(regime, b, n, m, 9), n_out, 10).to(DEV)
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, torch.float32, 11))
+    rw, _ = exact("wf", "backward", g, w, feat, idx)
+    dw, _ = ops.wf_backward(g, w, feat, idx)
+    assert_close(dw, rw, torch.float32, "d_weights (walk)")
+    assert torch.equal(dw, ops.wf_backward(g, w, feat, idx)[0])
+    monkeypatch.setenv("CLUSTEN_WF_DWEIGHTS_TILED", "1")
+    dw_t, _ = ops.wf_backward(g, w, feat, idx)
+    monkeypatch.delenv("CLUSTEN_WF_DWEIGHTS_TILED")
+    assert_close(dw_t, rw, torch.float32, "d_weights (tiled)")
+    bad = idx.clone()
+    bad[0, 3, 5] = -1
+    bad[1, 7, 40] = n + 3
+    mask = ((bad >= 0) & (bad < n)).float().unsqueeze(-1)
+    dw_b, _ = ops.wf_backward(g, w, feat, bad)
+    _, rw_b, _ = formula.forward_backward("wf", w * mask, feat, bad.clamp(0, n - 1), g)
+    assert_close(dw_b, rw_b * mask, torch.float32, "d_weights (walk) with bad indices")
 
 
 # (n, m, n_targets): one warp per chunk of rows with m <= 32, <= 64 and > 64; few rows; and a target count
