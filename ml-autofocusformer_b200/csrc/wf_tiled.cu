@@ -1029,6 +1029,247 @@ wf_dfeat_kernel(const WfScatterParams p) {
     }
 }
 
+// The same reduction without staging the gradient rows: a warp still takes 8 consecutive targets, lists their
+// entries and de-duplicates the merge rows (about 18 per tile on AutoFocusFormer's tables), but then every lane
+// owns 2 of the 64 channels for ALL 8 targets: per distinct merge row it reads its share of the ic gradient rows
+// once (ic loads of 256 contiguous bytes per warp) and adds it into the 8 targets' accumulators with the row's
+// weights, which sit in a dense [8 targets][32 rows][ic] fp32 tile in shared memory and are read as broadcasts.
+// Plain FMAs in merge-row order: no tensor cores (nothing to split into TF32 passes), 5.5 KB of shared memory per
+// warp instead of 11.4, 32 warps per SM instead of 20.
+constexpr int kUR = 32;                   // distinct merge rows per pass of the dense weight tile
+struct WfRowsSmem {
+    static constexpr int kWd = kT * kUR * 4 * 4;  // dense weights [8][kUR][ic <= 4]; de-duplication scratch before that
+    static constexpr int kEnt = kEE * 4;
+    static constexpr int kLut = kEE * 2;
+    static constexpr int kTotal = kWd + kEnt + 2 * kLut;
+};
+static_assert(kEE * 4 + kBMW * 4 + kBMW * 2 + (kE / 32) * 4 <= WfRowsSmem::kWd, "scratch must fit in the weight tile");
+
+template <typename T, int ICT, bool M48, bool C64>
+__global__ void __launch_bounds__(32 * kWarps, 8)
+wf_dfeat_rows_kernel(const WfScatterParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    using WS = WfRowsSmem;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char* base = smem_raw + size_t(warp) * WS::kTotal;
+    float* Wd = reinterpret_cast<float*>(base);
+    unsigned* ent = reinterpret_cast<unsigned*>(base + WS::kWd);
+    unsigned short* lut = reinterpret_cast<unsigned short*>(base + WS::kWd + WS::kEnt);
+    unsigned short* uniq = lut + kEE;
+    DedupScratch ds;
+    ds.tok = reinterpret_cast<unsigned short*>(base);
+    ds.uniq = uniq;
+    ds.bm = reinterpret_cast<unsigned*>(base + kEE * 4);
+    ds.pre = reinterpret_cast<unsigned short*>(ds.bm + kBMW);
+    ds.rowbm = reinterpret_cast<unsigned*>(ds.pre + kBMW);
+    const int m = M48 ? kMmax : p.m, c = C64 ? kCG : p.c, n_out = p.n_out, n_tgt = p.n;
+    auto div_m = [&](unsigned x) { return M48 ? x / 48u : fast_div_u(x, p.m_magic, p.m_shift); };
+    const T* Wg = static_cast<const T*>(p.W);
+    const T* Gg = static_cast<const T*>(p.G);
+    T* Og = static_cast<T*>(p.out);
+
+    const unsigned total = (unsigned)p.batch * (unsigned)p.tiles;
+    const unsigned nwarps = gridDim.x * kWarps;
+    auto load_segment = [&](unsigned task, int& len, int& start) {
+        len = 0;
+        start = 0;
+        if (task < total) {
+            const int b = (int)(task / (unsigned)p.tiles);
+            const int tt = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT + lane;
+            if (lane < kT && tt < n_tgt) {
+                len = p.inv.seglen[(long long)b * n_tgt + tt];
+                start = p.inv.rowptr[(long long)b * (n_tgt + 1) + tt];
+            }
+        }
+    };
+    int next_len, next_start;
+    load_segment(blockIdx.x * kWarps + warp, next_len, next_start);
+    for (unsigned task = blockIdx.x * kWarps + warp; task < total; task += nwarps) {
+        const int b = (int)(task / (unsigned)p.tiles);
+        const int t0 = (int)(task - (unsigned)b * (unsigned)p.tiles) * kT;
+        const long long brow = (long long)b * n_out;
+        const int64_t* idx_b = p.idx + brow * m;
+        const int* entries = p.inv.entries + brow * m;
+        const T* Wb = Wg + brow * m * ICT;
+        const T* Gb = Gg + brow * ICT * c + 2 * lane;
+        T* Ob = Og + (long long)b * n_tgt * c + 2 * lane;
+        const int len = next_len, start = next_start;
+        load_segment(task + nwarps, next_len, next_start);
+        int incl = len;
+#pragma unroll
+        for (int o = 1; o < kT; o <<= 1) {
+            const int y = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += y;
+        }
+        const int E_total = __shfl_sync(kFull, incl, kT - 1);
+        int off[kT], st[kT];
+#pragma unroll
+        for (int r = 0; r < kT; ++r) {
+            off[r] = __shfl_sync(kFull, incl - len, r);
+            st[r] = __shfl_sync(kFull, start, r);
+        }
+        unsigned pk[kT];                                        // (segment start - offset) << 3 | tile row
+#pragma unroll
+        for (int r = 0; r < kT; ++r) pk[r] = ((unsigned)(st[r] - off[r]) << 3) | (unsigned)r;
+        for (int e0 = 0; e0 == 0 || e0 < E_total; e0 += kEE) {
+            const int E = max(0, min(kEE, E_total - e0));
+            int lo = INT_MAX, hi = -1;
+            __syncwarp();
+#pragma unroll 4
+            for (int x = lane; x < E; x += 32) {
+                const int pe = e0 + x;
+                unsigned v = pk[0];
+#pragma unroll
+                for (int j = 1; j < kT; ++j) v = pe >= off[j] ? pk[j] : v;
+                const int r = (int)(v & 7u);
+                const unsigned e = (unsigned)__ldg(entries + (int)(v >> 3) + pe);
+                const int row = (int)div_m(e & ~kDupFlag);
+                ent[x] = e;
+                ds.tok[x] = (unsigned short)row;
+                lut[x] = (unsigned short)(r << 12);
+                lo = min(lo, row);
+                hi = max(hi, row);
+            }
+            int U = 0;
+            if (E > 0) {
+                bool unused = false;
+                unsigned short* slots = ds.tok + kEE;
+                U = dedup_tokens(ds, slots, E, m, false, &unused, lane, lo, hi);
+                for (int x = lane; x < E; x += 32) lut[x] = (unsigned short)(lut[x] | slots[x]);
+            }
+            __syncwarp();
+            for (int c0 = 0; c0 < c; c0 += kCG) {
+                float acc[kT][2];
+#pragma unroll
+                for (int q = 0; q < kT; ++q) acc[q][0] = acc[q][1] = 0.f;
+                for (int u0 = 0; u0 < U; u0 += kUR) {
+                    const int Uc = min(kUR, U - u0);
+                    __syncwarp();
+                    // ---- dense weights of this pass: zero, then every entry whose merge row is in the pass
+                    for (int z = lane; z < kT * kUR * ICT / 4; z += 32)
+                        reinterpret_cast<float4*>(Wd)[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    __syncwarp();
+#pragma unroll 2
+                    for (int x = lane; x < E; x += 32) {
+                        const unsigned lr = lut[x];
+                        const int rel = (int)(lr & 0xfffu) - u0;
+                        if (rel >= 0 && rel < Uc) {
+                            const unsigned e = ent[x];
+                            float w[ICT];
+                            if (!(e & kDupFlag)) {
+                                load_w<T, ICT>(Wb + (size_t)e * ICT, w);
+                            } else {
+                                // the merge row names the target several times: add its slots in order
+                                const unsigned row = div_m(e & ~kDupFlag);
+                                const int64_t* irow = idx_b + (long long)row * m;
+#pragma unroll
+                                for (int k = 0; k < ICT; ++k) w[k] = 0.f;
+#pragma unroll 1
+                                for (int j = 0; j < m; ++j)
+                                    if (irow[j] == t0 + (int)(lr >> 12)) {
+#pragma unroll
+                                        for (int k = 0; k < ICT; ++k)
+                                            w[k] += Elem<T>::up(Wb[((size_t)row * m + j) * ICT + k]);
+                                    }
+                            }
+                            float* dst = Wd + ((lr >> 12) * kUR + rel) * ICT;
+#pragma unroll
+                            for (int k = 0; k < ICT; ++k) dst[k] = w[k];
+                        }
+                    }
+                    __syncwarp();
+                    // ---- the pass's merge rows, two in flight
+                    auto fetch = [&](int u, float (&g)[ICT][2]) {
+                        const T* gp = Gb + (long long)uniq[u0 + u] * (ICT * c) + c0;
+#pragma unroll
+                        for (int k = 0; k < ICT; ++k) {
+                            if constexpr (std::is_same<T, float>::value) {
+                                const float2 v = *reinterpret_cast<const float2*>(gp + k * c);
+                                g[k][0] = v.x;  g[k][1] = v.y;
+                            } else {
+                                // two 16-bit channels in one word
+                                const unsigned v = *reinterpret_cast<const unsigned*>(gp + k * c);
+                                const unsigned short lo16 = (unsigned short)(v & 0xffffu), hi16 = (unsigned short)(v >> 16);
+                                g[k][0] = Elem<T>::up(*reinterpret_cast<const T*>(&lo16));
+                                g[k][1] = Elem<T>::up(*reinterpret_cast<const T*>(&hi16));
+                            }
+                        }
+                    };
+                    auto add = [&](int u, const float (&g)[ICT][2]) {
+#pragma unroll
+                        for (int q = 0; q < kT; ++q) {
+                            float w[ICT];
+                            const float* wp = Wd + (q * kUR + u) * ICT;
+                            if constexpr (ICT == 4) {
+                                const float4 v = *reinterpret_cast<const float4*>(wp);
+                                w[0] = v.x;  w[1] = v.y;  w[2] = v.z;  w[3] = v.w;
+                            } else if constexpr (ICT == 2) {
+                                const float2 v = *reinterpret_cast<const float2*>(wp);
+                                w[0] = v.x;  w[1] = v.y;
+                            } else {
+                                w[0] = wp[0];
+                            }
+#pragma unroll
+                            for (int k = 0; k < ICT; ++k) {
+                                acc[q][0] += w[k] * g[k][0];
+                                acc[q][1] += w[k] * g[k][1];
+                            }
+                        }
+                    };
+                    float ga[ICT][2], gb[ICT][2];
+                    int u = 0;
+                    for (; u + 2 <= Uc; u += 2) {
+                        fetch(u, ga);
+                        fetch(u + 1, gb);
+                        add(u, ga);
+                        add(u + 1, gb);
+                    }
+                    if (u < Uc) {
+                        fetch(u, ga);
+                        add(u, ga);
+                    }
+                }
+                // ---- the tile's outputs (added to what earlier chunks of a long entry list wrote)
+#pragma unroll
+                for (int q = 0; q < kT; ++q) {
+                    if (t0 + q < n_tgt) {
+                        T* dstp = Ob + (long long)(t0 + q) * c + c0;
+                        float v0 = acc[q][0], v1 = acc[q][1];
+                        if (e0 > 0) {
+                            v0 += Elem<T>::up(dstp[0]);
+                            v1 += Elem<T>::up(dstp[1]);
+                        }
+                        if constexpr (std::is_same<T, float>::value) {
+                            *reinterpret_cast<float2*>(dstp) = make_float2(v0, v1);
+                        } else {
+                            const T a = Elem<T>::down(v0), bq = Elem<T>::down(v1);
+                            const unsigned word = (unsigned)*reinterpret_cast<const unsigned short*>(&a) |
+                                                  ((unsigned)*reinterpret_cast<const unsigned short*>(&bq) << 16);
+                            *reinterpret_cast<unsigned*>(dstp) = word;
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int ICT>
+int wf_dfeat_rows_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
+    const size_t smem = size_t(kWarps) * WfRowsSmem::kTotal;
+    auto kernel = p.m != kMmax ? wf_dfeat_rows_kernel<T, ICT, false, false>
+                               : (p.c == kCG ? wf_dfeat_rows_kernel<T, ICT, true, true> : wf_dfeat_rows_kernel<T, ICT, true, false>);
+    const int per_sm = resident_ctas(reinterpret_cast<const void*>(kernel), 32 * kWarps, smem);
+    if (per_sm < 0) return per_sm;
+    long long grid = (long long)sm_count() * per_sm;
+    const long long need = ((long long)p.batch * p.tiles + kWarps - 1) / kWarps;
+    if (grid > need) grid = need;
+    ScopedKernelTimer timer(label, s);
+    kernel<<<(int)grid, 32 * kWarps, smem, s>>>(p);
+    note_launch();
+    return check_launch();
+}
+
 template <typename T, int ICT>
 int wf_dfeat_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
     const size_t smem = size_t(kWarps) * WfScatterSmem::kTotal;
@@ -1047,10 +1288,15 @@ int wf_dfeat_t(const char* label, const WfScatterParams& p, cudaStream_t s) {
 
 template <typename T>
 int wf_dfeat_ic(const char* label, int ic, const WfScatterParams& p, cudaStream_t s) {
+    // fp32: the unstaged kernel (0.290 -> 0.221 ms on the benchmark step); 16-bit inputs: the staged one, whose
+    // products are single tensor-core instructions (0.221 against 0.226 ms).  CLUSTEN_WF_DFEAT = staged | rows
+    // overrides the choice (read at every call).
+    bool staged = !std::is_same<T, float>::value;
+    if (const char* v = getenv("CLUSTEN_WF_DFEAT")) staged = v[0] == 's';
     switch (ic) {
-        case 1: return wf_dfeat_t<T, 1>(label, p, s);
-        case 2: return wf_dfeat_t<T, 2>(label, p, s);
-        case 4: return wf_dfeat_t<T, 4>(label, p, s);
+        case 1: return staged ? wf_dfeat_t<T, 1>(label, p, s) : wf_dfeat_rows_t<T, 1>(label, p, s);
+        case 2: return staged ? wf_dfeat_t<T, 2>(label, p, s) : wf_dfeat_rows_t<T, 2>(label, p, s);
+        case 4: return staged ? wf_dfeat_t<T, 4>(label, p, s) : wf_dfeat_rows_t<T, 4>(label, p, s);
         default: return CLUSTEN_ERR_UNSUPPORTED;
     }
 }

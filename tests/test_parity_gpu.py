@@ -154,6 +154,33 @@ def test_wf_forward_both_kernels(ops, shape, regime, dtype, monkeypatch):
     assert_close(tiled, want, dtype, "wf forward (tiled)")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+@pytest.mark.parametrize("regime", ["shared", "model", "random", "shared-hot"])
+@pytest.mark.parametrize("shape", [(2, 99, 392, 48, 4, 128), (1, 200, 800, 48, 1, 64), (2, 50, 200, 24, 2, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_wf_d_feat_both_kernels(ops, shape, regime, dtype, monkeypatch):
+    """d_feat has two kernels: gradient rows staged in shared memory and multiplied on the tensor cores, or read
+    straight into registers and added with FMAs (CLUSTEN_WF_DFEAT = staged | rows, read at every call).  Both
+    against the oracle, for both dtypes; "shared-hot" makes one token a neighbour of every row, so that its entry
+    list spans several chunks."""
+    b, n_out, n, m, ic, c = shape
+    if regime == "random":
+        idx = workloads.random_rows(b, n_out, n, m, 7).to(DEV)
+    else:
+        idx = workloads.select_rows(workloads.make_index(regime.split("-")[0], b, n, m, 9), n_out, 10).to(DEV)
+    if regime.endswith("hot"):
+        idx[:, :, -1] = 5
+        idx[:, ::2, -2] = 5          # ... twice in every other row
+    w, feat, g = (x.to(DEV) for x in workloads.merge_operands(b, n_out, n, m, ic, c, dtype, 11))
+    _, rf = exact("wf", "backward", g, w, feat, idx)
+    for kind in ("rows", "staged"):
+        monkeypatch.setenv("CLUSTEN_WF_DFEAT", kind)
+        _, df = ops.wf_backward(g, w, feat, idx)
+        assert_close(df, rf, dtype, f"d_feat ({kind})")
+        assert torch.equal(df, ops.wf_backward(g, w, feat, idx)[1])
+    monkeypatch.delenv("CLUSTEN_WF_DFEAT")
+
+
 @pytest.mark.parametrize("regime", ["shared", "model", "random"])
 def test_wf_d_weights_fp32_both_kernels(ops, regime, monkeypatch):
     """fp32 d_weights with ic = 4: the walk with the 16-lane butterfly (default) and the tiled kernel
