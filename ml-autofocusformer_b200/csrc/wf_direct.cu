@@ -1,16 +1,17 @@
-// CLUSTENWF forward for fp32 inputs as a plain walk over the neighbours.
+// CLUSTENWF forward (and, further down, d_weights) as a plain walk over the neighbours.
 //
 //   feat_new[b, i, k, :] = sum_j weights[b, i, j, k] * feat[b, nbhd_idx[b, i, j], :]
 //
-// Half a warp takes one merge row and every lane 4 channels of a 64-channel group: per neighbour the half
-// reads the ic weights (one address, broadcast), the neighbour's feature vector (16 bytes per lane, 256
-// contiguous bytes per row) and adds with fp32 FMAs in neighbour order -- the order of the reference's loop
-// (clusten/src/clustenwf_cuda_kernel.cu:41-47), which gathers every feature row ic times per output element.
-// Rows are taken in the row order, so the two rows of a warp and the rows of neighbouring warps share most of
-// their neighbours and find them in L1.  No shared memory and 60-odd registers: 32 warps per SM, against 12
+// Half a warp takes one merge row and every lane 4 channels of a 64-channel group: the half fetches the next 16
+// neighbours' indices and ic weights one per lane (contiguous, all in flight together) and hands them round by
+// shuffles; per neighbour it reads the feature vector (16 bytes per lane in fp32, 256 contiguous bytes per
+// row), four in flight at a time, and adds with fp32 FMAs in neighbour order -- the order of the reference's
+// loop (clusten/src/clustenwf_cuda_kernel.cu:41-47), which gathers every feature row ic times per output
+// element.  Rows are taken in the row order, so the two rows of a warp and the rows of neighbouring warps share
+// most of their neighbours and find them in L1.  No shared memory and 64 registers: 32 warps per SM, against 12
 // for the tiled kernel (wf_tiles_kernel), whose staging, de-duplication and three-pass TF32 products cost more
-// instruction slots than these 16 FMAs per neighbour.  16-bit inputs stay on the tiled kernel: their products
-// are single tensor-core instructions there and conversions here.
+// instruction slots than these 16 FMAs per neighbour.  Measured faster for 16-bit inputs as well, although
+// their products are single tensor-core instructions in the tiled kernel.
 #include "tile_core.cuh"
 #include "tiled.cuh"
 
