@@ -63,13 +63,13 @@ CPU_SAMPLE_BATCH = 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture at b=32, scaled x4 to the
 # benchmark's b=128 (traffic grows with the batch); see profiles/.  NCU_CAPTURE_BUILD names the commit whose
 # kernels were captured: the figure describes that build, not necessarily the one being timed.
-NCU_CAPTURE_BUILD = "0b9e340"
+NCU_CAPTURE_BUILD = "c73042a"
 NCU_DRAM_BYTES_PER_LAUNCH = {("av_d_value", "fp32"): 4 * (84390144 + 9697024),
                              ("av_forward", "fp32"): 4 * (103208448 + 11935744),
                              ("av_d_attn", "fp32"): 4 * (89984256 + 16303872),
                              ("wf_forward", "fp32"): 4 * (54714368 + 3070464),
                              ("wf_d_weights", "fp32"): 4 * (61138688 + 3995136),
-                             ("wf_d_feat", "fp32"): 4 * (50615808 + 3492608)}
+                             ("wf_d_feat", "fp32"): 4 * (50619904 + 4648704)}
 
 
 def _peaks():
