@@ -102,6 +102,10 @@ WF_SHAPES = [
     (1, 20, 100, 80, 4, 64),
     (1, 20, 100, 16, 3, 32),
     (1, 12, 60, 24, 16, 32),
+    # odd row counts (the walks take rows two at a time), one neighbour, 17 neighbours, 192 channels, a single row
+    (3, 5, 40, 1, 4, 64),
+    (1, 7, 30, 17, 4, 192),
+    (2, 1, 16, 48, 4, 64),
     # the merges of the 384 x 384 model at 1/5 retention: 1843 -> 368 and 368 -> 73 rows
     (1, 368, 1843, 48, 4, 64),
     (2, 73, 368, 48, 4, 128),
