@@ -374,11 +374,12 @@ def use_fused(on=True):
     use_fused_merging(on)
 
 
-def build_model(config, device, seed=0):
-    """AutoFocusFormer(**CONFIGS[config]).eval() with seeded random weights on `device`."""
+def build_model(config, device, seed=0, **overrides):
+    """AutoFocusFormer(**CONFIGS[config]).eval() with seeded random weights on `device`; keyword arguments
+    replace entries of the configuration (e.g. reserve_on=False)."""
     aff = model_module()
     torch.manual_seed(seed)
-    model = aff.AutoFocusFormer(**CONFIGS[config])
+    model = aff.AutoFocusFormer(**dict(CONFIGS[config], **overrides))
     return model.to(device).eval()
 
 

@@ -116,3 +116,21 @@ def test_neighbourhood_tables_variant_of_the_model(lib, config, batch, dtype, ca
     assert err <= 1e-6, err
     # the merge weights are rounded once where the reference's products round after every step (bf16 only)
     assert err2 <= (1e-6 if dtype == torch.float32 else 2e-2), err2
+
+
+def test_all_hooks_without_reserved_tokens(lib, capsys):
+    """reserve_on=False takes the other branch of the merge-centre selection (models/aff_transformer.py:312-326);
+    all three opt-in hooks together against the unmodified model."""
+    aff_harness.use_implementation("b200")
+    model = aff_harness.build_model("tiny224", DEV, seed=0, reserve_on=False)
+    x = aff_harness.synthetic_images("tiny224", 3, DEV, seed=2)
+    want = aff_harness.forward(model, x, torch.float32)
+    try:
+        aff_harness.use_fused(True)
+        got = aff_harness.forward(model, x, torch.float32)
+    finally:
+        aff_harness.use_fused(False)
+    err = _rel(got, want)
+    with capsys.disabled():
+        print(f"\ntiny224 fp32, reserve_on=False, all hooks: logits rel err {err:.2e}")
+    assert err <= 1e-4, err
